@@ -1,0 +1,262 @@
+// Shared device helpers for the tfp8b kernels (sm_100a): FP8 bit decode/encode, mbarrier /
+// bulk-copy / TMA / tcgen05 PTX wrappers, and the host-side error plumbing of the C ABI.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/tfp8b.h"
+
+namespace tfp8b {
+
+// ------------------------------------------------------------------ host-side error plumbing
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define TFP8B_REQUIRE(cond, code, ...)      \
+    do {                                    \
+        if (!(cond)) {                      \
+            ::tfp8b::set_error(__VA_ARGS__); \
+            return (code);                  \
+        }                                   \
+    } while (0)
+
+#define TFP8B_LAUNCH_CHECK(what)                                      \
+    do {                                                              \
+        cudaError_t e__ = cudaGetLastError();                         \
+        if (e__ != cudaSuccess) return ::tfp8b::cuda_fail(e__, what); \
+    } while (0)
+
+// Device-side status word, one per translation unit (the library is built without relocatable
+// device code): kernels OR a bit in when a bounded wait runs out; each .cu file that has such
+// waits exports a reader that tfp8b_device_status() combines.
+static __device__ unsigned int g_status;
+constexpr unsigned STATUS_GEMV_WAIT = 1u, STATUS_GEMM_WAIT = 2u;
+int read_and_clear_status(unsigned int* word_on_device, unsigned int* out, cudaStream_t st);
+
+// ------------------------------------------------------------------ small utilities
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+template <typename T> struct dtype_of;
+template <> struct dtype_of<__half> { static constexpr int id = TFP8B_F16; };
+template <> struct dtype_of<__nv_bfloat16> { static constexpr int id = TFP8B_BF16; };
+template <> struct dtype_of<float> { static constexpr int id = TFP8B_F32; };
+
+__host__ __device__ __forceinline__ int dtype_size(int dt) { return dt == TFP8B_F32 ? 4 : 2; }
+
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(float v) { return v; }
+
+__device__ __forceinline__ void store_as(__half* p, float v) { *p = __float2half_rn(v); }
+__device__ __forceinline__ void store_as(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void store_as(float* p, float v) { *p = v; }
+
+// y[i] = v in a runtime-selected element type (used by epilogues that are not templated on it).
+__device__ __forceinline__ void store_dt(void* y, size_t i, float v, int dt) {
+    if (dt == TFP8B_F16) reinterpret_cast<__half*>(y)[i] = __float2half_rn(v);
+    else if (dt == TFP8B_BF16) reinterpret_cast<__nv_bfloat16*>(y)[i] = __float2bfloat16_rn(v);
+    else reinterpret_cast<float*>(y)[i] = v;
+}
+
+// Weight scale -> float. UE8M0 byte b is 2^(b-127): the float32 bit pattern b<<23, except b == 0
+// (2^-127, a float32 subnormal) and b == 255 (NaN).
+__device__ __forceinline__ float ue8m0_to_f32(uint32_t b) {
+    uint32_t u = b << 23;
+    if (b == 0u) u = 0x00400000u;
+    if (b == 255u) u = 0x7FC00000u;
+    return __uint_as_float(u);
+}
+__device__ __forceinline__ float load_scale(const void* s, size_t i, int kind) {
+    return kind == TFP8B_SCALE_UE8M0 ? ue8m0_to_f32(reinterpret_cast<const uint8_t*>(s)[i])
+                                     : reinterpret_cast<const float*>(s)[i];
+}
+
+// ------------------------------------------------------------------ FP8 decode by bit moves
+// Input: a 32-bit word with one code in the HIGH byte of each 16-bit lane (c << 8), low bytes 0.
+// Output: the two values as a packed f16x2 / bf16x2 bit pattern. Exact for every code:
+// subnormals go through the multiply (an fp16/bf16 subnormal times a power of two is exact), NaN
+// and inf codes get an all-ones exponent before it.
+//
+//   E4M3FN -> f16 : s eeee mmm        -> s 0eeee mmm0000000 (shift 1)  * 2^8
+//   E5M2   -> f16 : s eeeee mm        -> the same bits (bias 15 in both)
+//   E4M3FN -> bf16: s 0000eeee mmm0000 (shift 4)                        * 2^120
+//   E5M2   -> bf16: s 000eeeee mm00000 (shift 3)                        * 2^112
+template <int FMT>
+__device__ __forceinline__ uint32_t dec2_f16(uint32_t q) {
+    if (FMT == TFP8B_E5M2) return q;
+    uint32_t mag = (q >> 1) & 0x3F803F80u;
+    // 0x7F (all magnitude bits set) is NaN: mag + 0x80 carries into bit 14 only then.
+    uint32_t nan = (mag + 0x00800080u) & 0x40004000u;
+    mag |= nan;                                      // exponent 11111, mantissa != 0
+    __half2 h = __hmul2(*reinterpret_cast<__half2*>(&mag), __half2half2(__ushort_as_half(0x5C00)));  // * 256
+    return *reinterpret_cast<uint32_t*>(&h) | (q & 0x80008000u);
+}
+
+template <int FMT>
+__device__ __forceinline__ uint32_t dec2_bf16(uint32_t q) {
+    uint32_t mag, mul;
+    if (FMT == TFP8B_E4M3FN) {
+        mag = (q >> 4) & 0x07F007F0u;
+        uint32_t nan = (mag + 0x00100010u) & 0x08000800u;   // bit 11 iff all seven bits set
+        mag += nan * 15u;                                    // exponent field 0xFF, mantissa != 0
+        mul = 0x7B807B80u;                                   // 2^120
+    } else {
+        mag = (q >> 3) & 0x0FE00FE0u;
+        uint32_t top = (mag + 0x00800080u) & 0x10001000u;    // bit 12 iff e == 31 (inf / NaN)
+        mag += top * 7u;                                     // exponent field 0xFF, mantissa kept
+        mul = 0x77807780u;                                   // 2^112
+    }
+    __nv_bfloat162 h = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&mag),
+                               *reinterpret_cast<__nv_bfloat162*>(&mul));
+    return *reinterpret_cast<uint32_t*>(&h) | (q & 0x80008000u);
+}
+
+// Four codes of one 32-bit word (c0 in the low byte) -> two packed pairs {c0,c1}, {c2,c3}.
+template <int FMT, bool BF16>
+__device__ __forceinline__ void dec4(uint32_t w, uint32_t& p01, uint32_t& p23) {
+    uint32_t q01 = __byte_perm(w, 0u, 0x1404);   // (c1 << 24) | (c0 << 8)
+    uint32_t q23 = __byte_perm(w, 0u, 0x3424);   // (c3 << 24) | (c2 << 8)
+    if (BF16) { p01 = dec2_bf16<FMT>(q01); p23 = dec2_bf16<FMT>(q23); }
+    else      { p01 = dec2_f16<FMT>(q01);  p23 = dec2_f16<FMT>(q23); }
+}
+
+// Single code -> float (scalar paths: quantizer checks, tails).
+__device__ __forceinline__ float dec1_f32(uint32_t c, int fmt) {
+    uint32_t q = (c & 0xFFu) << 8;
+    uint32_t h = fmt == TFP8B_E5M2 ? dec2_f16<TFP8B_E5M2>(q) : dec2_f16<TFP8B_E4M3FN>(q);
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(h & 0xFFFFu)));
+}
+
+// ------------------------------------------------------------------ FP8 encode (exact, integer)
+// float -> code: round to nearest even on the float's bit fields, saturate to the largest finite
+// code (also for +-inf), NaN -> sign|0x7F (nan_mode CAST) or the format's canonical NaN.
+//   EB/MB: exponent / mantissa bits, BIAS: exponent bias, TOP: largest finite code (0x7E / 0x7B).
+template <int FMT>
+__host__ __device__ __forceinline__ uint32_t encode1(float x, int nan_mode) {
+    constexpr int MB = FMT == TFP8B_E4M3FN ? 3 : 2;
+    constexpr int BIAS = FMT == TFP8B_E4M3FN ? 7 : 15;
+    constexpr uint32_t TOP = FMT == TFP8B_E4M3FN ? 0x7Eu : 0x7Bu;
+    constexpr uint32_t NAN_CANON = FMT == TFP8B_E4M3FN ? 0x7Fu : 0x7Eu;
+    constexpr int EMIN = 1 - BIAS;                       // exponent of the smallest normal
+#ifdef __CUDA_ARCH__
+    const uint32_t u = __float_as_uint(x);
+#else
+    union { float f; uint32_t u; } cvt_; cvt_.f = x; const uint32_t u = cvt_.u;
+#endif
+    const uint32_t sign = (u >> 24) & 0x80u;
+    const uint32_t ax = u & 0x7FFFFFFFu;
+    if (ax > 0x7F800000u) return nan_mode == TFP8B_NAN_CANONICAL ? NAN_CANON : (sign | 0x7Fu);
+    const int e = static_cast<int>(ax >> 23) - 127;      // unbiased float exponent (-127 for 0/sub)
+    uint32_t code;
+    if (e >= EMIN) {
+        // normal target: keep MB mantissa bits, RNE on the 23-MB dropped bits; a mantissa carry
+        // walks into the exponent field because the fields are adjacent.
+        const uint32_t keep = ax >> (23 - MB);                        // exponent|mantissa, float bias
+        const uint32_t rest = ax & ((1u << (23 - MB)) - 1u);
+        const uint32_t half = 1u << (22 - MB);
+        const uint32_t up = (rest > half) || (rest == half && (keep & 1u));
+        const uint32_t r = keep + up;
+        const int re = static_cast<int>(r >> MB) - 127 + BIAS;        // target exponent field
+        code = (static_cast<uint32_t>(re) << MB) | (r & ((1u << MB) - 1u));
+        if (re <= 0) code = 0;                                        // cannot happen for e >= EMIN
+        if (code > TOP || re >= (1 << (7 - MB))) code = TOP;          // saturate (inf included)
+    } else {
+        // subnormal target: value = m * 2^(EMIN-MB); m = RNE(|x| * 2^(MB-EMIN)), 0 <= m <= 2^MB
+        // (m == 2^MB is the smallest normal: the same bit pattern).
+        const int shift = (EMIN - MB) - (e - 23);                     // bits to drop from the 24-bit significand
+        if (e == -127 || shift > 25) {
+            code = 0;                                                 // zero / float subnormal / far below half a step
+        } else {
+            const uint32_t sig = (ax & 0x7FFFFFu) | 0x800000u;
+            const uint32_t keep = sig >> shift;
+            const uint32_t rest = sig & ((1u << shift) - 1u);
+            const uint32_t half = 1u << (shift - 1);
+            code = keep + ((rest > half) || (rest == half && (keep & 1u)));
+        }
+    }
+    return sign | code;
+}
+
+__host__ __device__ __forceinline__ uint32_t encode1(float x, int fmt, int nan_mode) {
+    return fmt == TFP8B_E5M2 ? encode1<TFP8B_E5M2>(x, nan_mode) : encode1<TFP8B_E4M3FN>(x, nan_mode);
+}
+
+// ------------------------------------------------------------------ mbarrier / bulk copy
+#ifdef __CUDACC__
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls (each poll may itself block for a short,
+// hardware-chosen time), records `status_bit` in the device status word and returns false.
+// No wait in this library is unbounded, so a protocol error ends the kernel instead of hanging.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned status_bit,
+                                          uint32_t limit = (1u << 22)) {
+    for (uint32_t i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicOr(&g_status, status_bit);
+    return false;
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+// 1-D bulk copy global -> shared of this CTA, completion counted in bytes on `bar`.
+// dst, src 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar,
+                                         uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1], %2, [%3], %4;"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+}
+// 2-D tiled TMA load (no multicast), coordinates in elements: c0 innermost.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                            uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3}], [%4], %5;"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+#endif  // __CUDACC__
+
+}  // namespace tfp8b

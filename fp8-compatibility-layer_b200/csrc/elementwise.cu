@@ -1,0 +1,411 @@
+// Bandwidth-bound elementwise kernels of the FP8Linear path: the RNE/saturating encoder, the
+// exact decoder, the one-pass weight quantizer, the reference-layout dequantizer, the activation
+// row-scale prep and the windowed epilogue. All are plain streaming kernels: 128-bit coalesced
+// loads and stores, 16 elements per thread per step, grids sized in multiples of the SM count.
+#include <float.h>
+
+#include "common.cuh"
+
+namespace tfp8b {
+
+constexpr int EW_THREADS = 256;
+
+static int sm_count() {
+    int dev = 0, n = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n > 0 ? n : 148;
+}
+
+// ------------------------------------------------------------------ 16-element loads per dtype
+template <typename T>
+__device__ __forceinline__ void load16(const T* p, float v[16]);
+template <>
+__device__ __forceinline__ void load16<__half>(const __half* p, float v[16]) {
+    uint4 a = reinterpret_cast<const uint4*>(p)[0], b = reinterpret_cast<const uint4*>(p)[1];
+    const __half2* h = reinterpret_cast<const __half2*>(&a);
+    const __half2* g = reinterpret_cast<const __half2*>(&b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        float2 e = __half22float2(g[i]); v[8 + 2 * i] = e.x; v[9 + 2 * i] = e.y;
+    }
+}
+template <>
+__device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, float v[16]) {
+    uint4 a = reinterpret_cast<const uint4*>(p)[0], b = reinterpret_cast<const uint4*>(p)[1];
+    const uint32_t* u = reinterpret_cast<const uint32_t*>(&a);
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(u[i] << 16); v[2 * i + 1] = __uint_as_float(u[i] & 0xFFFF0000u);
+        v[8 + 2 * i] = __uint_as_float(w[i] << 16); v[9 + 2 * i] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+template <>
+__device__ __forceinline__ void load16<float>(const float* p, float v[16]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float4 f = reinterpret_cast<const float4*>(p)[i];
+        v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void store16(T* p, const float v[16]);
+template <>
+__device__ __forceinline__ void store16<__half>(__half* p, const float v[16]) {
+    uint4 o[2];
+    __half2* h = reinterpret_cast<__half2*>(o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    reinterpret_cast<uint4*>(p)[0] = o[0];
+    reinterpret_cast<uint4*>(p)[1] = o[1];
+}
+template <>
+__device__ __forceinline__ void store16<__nv_bfloat16>(__nv_bfloat16* p, const float v[16]) {
+    uint4 o[2];
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    reinterpret_cast<uint4*>(p)[0] = o[0];
+    reinterpret_cast<uint4*>(p)[1] = o[1];
+}
+template <>
+__device__ __forceinline__ void store16<float>(float* p, const float v[16]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        reinterpret_cast<float4*>(p)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+}
+
+template <int FMT>
+__device__ __forceinline__ uint4 encode16(const float v[16], int nan_mode) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        w[i] = encode1<FMT>(v[4 * i], nan_mode) | (encode1<FMT>(v[4 * i + 1], nan_mode) << 8) |
+               (encode1<FMT>(v[4 * i + 2], nan_mode) << 16) | (encode1<FMT>(v[4 * i + 3], nan_mode) << 24);
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// 16 codes -> 16 floats (exact) through the fp16 bit decode.
+template <int FMT>
+__device__ __forceinline__ void decode16(uint4 raw, float v[16]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t p01, p23;
+        dec4<FMT, false>(w[i], p01, p23);
+        float2 a = __half22float2(*reinterpret_cast<__half2*>(&p01));
+        float2 b = __half22float2(*reinterpret_cast<__half2*>(&p23));
+        v[4 * i] = a.x; v[4 * i + 1] = a.y; v[4 * i + 2] = b.x; v[4 * i + 3] = b.y;
+    }
+}
+
+// ------------------------------------------------------------------ encode
+template <typename T, int FMT>
+__global__ void __launch_bounds__(EW_THREADS) encode_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
+                                                            int64_t n, int nan_mode, int vec_ok) {
+    const int64_t nvec = vec_ok ? n / 16 : 0;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        float v[16];
+        load16<T>(x + i * 16, v);
+        reinterpret_cast<uint4*>(out)[i] = encode16<FMT>(v, nan_mode);
+    }
+    for (int64_t i = nvec * 16 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+        out[i] = static_cast<uint8_t>(encode1<FMT>(to_f32(x[i]), nan_mode));
+}
+
+// ------------------------------------------------------------------ decode (no scale)
+template <typename T, int FMT>
+__global__ void __launch_bounds__(EW_THREADS) decode_kernel(const uint8_t* __restrict__ codes, T* __restrict__ out,
+                                                            int64_t n, int vec_ok) {
+    const int64_t nvec = vec_ok ? n / 16 : 0;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        float v[16];
+        decode16<FMT>(reinterpret_cast<const uint4*>(codes)[i], v);
+        store16<T>(out + i * 16, v);
+    }
+    for (int64_t i = nvec * 16 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+        store_as(out + i, dec1_f32(codes[i], FMT));
+}
+
+// ------------------------------------------------------------------ dequant with scales
+template <typename T, int FMT>
+__global__ void __launch_bounds__(EW_THREADS) dequant_kernel(const uint8_t* __restrict__ codes,
+                                                             const void* __restrict__ scale, int scale_kind,
+                                                             T* __restrict__ out, int N, int K, int G) {
+    const int chunks_per_row = K / 16;
+    const int64_t total = static_cast<int64_t>(N) * chunks_per_row;
+    const int ng = K / G;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int n = static_cast<int>(i / chunks_per_row);
+        const int k = static_cast<int>(i % chunks_per_row) * 16;
+        const float s = load_scale(scale, static_cast<size_t>(n) * ng + k / G, scale_kind);
+        float v[16];
+        decode16<FMT>(reinterpret_cast<const uint4*>(codes)[i], v);
+#pragma unroll
+        for (int t = 0; t < 16; ++t) v[t] *= s;
+        store16<T>(out + i * 16, v);
+    }
+}
+
+// ------------------------------------------------------------------ one-pass weight quantizer
+// One CTA per weight row. Pass 1: per-group amax into shared memory (non-negative floats order
+// like their bit patterns, so an integer atomicMax does it). Pass 2 re-reads the row (now in
+// L1/L2), divides by the group scale and encodes. 16 contiguous elements per thread per step.
+__device__ __forceinline__ float scale_from_amax(float amax, float fmax, int pow2) {
+    if (amax == 0.f) return 1.f;
+    float s = fmaxf(__fdiv_rn(amax, fmax), FLT_MIN);
+    if (pow2) {
+        uint32_t u = __float_as_uint(s);
+        if (u & 0x007FFFFFu) u = (u & 0x7F800000u) + 0x00800000u;   // next power of two
+        s = __uint_as_float(u);
+    }
+    return s;
+}
+
+template <typename T, int FMT>
+__global__ void __launch_bounds__(EW_THREADS) quantize_kernel(const T* __restrict__ w, uint8_t* __restrict__ q,
+                                                              void* __restrict__ scale, int scale_kind,
+                                                              int K, int G, int pow2) {
+    extern __shared__ uint32_t s_amax[];           // K/G entries: amax bits, then the scale bits
+    const int n = blockIdx.x;
+    const int ng = K / G;
+    const float fmax = FMT == TFP8B_E4M3FN ? 448.f : 57344.f;
+    const T* row = w + static_cast<size_t>(n) * K;
+    for (int g = threadIdx.x; g < ng; g += blockDim.x) s_amax[g] = 0u;
+    __syncthreads();
+    for (int k = threadIdx.x * 16; k < K; k += blockDim.x * 16) {
+        float v[16];
+        load16<T>(row + k, v);
+        float m = 0.f;
+#pragma unroll
+        for (int t = 0; t < 16; ++t) m = fmaxf(m, fabsf(v[t]));
+        atomicMax(&s_amax[k / G], __float_as_uint(m));
+    }
+    __syncthreads();
+    for (int g = threadIdx.x; g < ng; g += blockDim.x) {
+        const float s = scale_from_amax(__uint_as_float(s_amax[g]), fmax, pow2);
+        s_amax[g] = __float_as_uint(s);
+        const size_t si = static_cast<size_t>(n) * ng + g;
+        if (scale_kind == TFP8B_SCALE_UE8M0) reinterpret_cast<uint8_t*>(scale)[si] = static_cast<uint8_t>(__float_as_uint(s) >> 23);
+        else reinterpret_cast<float*>(scale)[si] = s;
+    }
+    __syncthreads();
+    for (int k = threadIdx.x * 16; k < K; k += blockDim.x * 16) {
+        const float s = __uint_as_float(s_amax[k / G]);
+        float v[16];
+        load16<T>(row + k, v);
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+            float r = __fdiv_rn(v[t], s);
+            v[t] = r > fmax ? fmax : (r < -fmax ? -fmax : r);     // keeps NaN, like torch.clamp
+        }
+        *reinterpret_cast<uint4*>(q + static_cast<size_t>(n) * K + k) = encode16<FMT>(v, TFP8B_NAN_CAST);
+    }
+}
+
+// ------------------------------------------------------------------ activation row prep
+// One CTA per row: row amax -> e = ceil(log2 amax) - 8 (read off the float's bit fields, so a power
+// of two maps to itself) clamped below like the reference's clamp_min(2^-100) -> x16 = x * 2^-e.
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS) prep_kernel(const T* __restrict__ x, __half* __restrict__ x16,
+                                                          float* __restrict__ xs, int K) {
+    constexpr int VEC = 16 / sizeof(T);
+    const int m = blockIdx.x;
+    const T* row = x + static_cast<size_t>(m) * K;
+    float amax = 0.f;
+    bool bad = false;                                   // NaN anywhere in the row
+    for (int k = threadIdx.x * VEC; k < K; k += blockDim.x * VEC) {
+        uint4 raw = *reinterpret_cast<const uint4*>(row + k);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int t = 0; t < VEC; ++t) {
+            float f = fabsf(to_f32(e[t]));
+            bad |= (f != f);
+            amax = fmaxf(amax, f);
+        }
+    }
+    __shared__ float s_max[EW_THREADS / 32];
+    __shared__ int s_bad;
+    if (threadIdx.x == 0) s_bad = 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = amax;
+    if (bad) s_bad = 1;
+    __syncthreads();
+    amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < EW_THREADS / 32; ++i) amax = fmaxf(amax, s_max[i]);
+    float scale = 1.f, inv = 1.f;
+    if (s_bad || amax > FLT_MAX) {                      // NaN / inf row: as torch, the scale is not finite
+        scale = s_bad ? __uint_as_float(0x7FC00000u) : __uint_as_float(0x7F800000u);
+        inv = s_bad ? scale : 0.f;
+    } else if (amax > 0.f) {
+        float a = fmaxf(amax, 7.888609052210118e-31f);  // 2^-100
+        uint32_t u = __float_as_uint(a);
+        int e = static_cast<int>(u >> 23) - 127 + ((u & 0x007FFFFFu) ? 1 : 0) - 8;   // ceil(log2 a) - 8
+        scale = __uint_as_float(static_cast<uint32_t>(e + 127) << 23);               // e in [-108, 120]
+        inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+    }
+    for (int k = threadIdx.x * VEC; k < K; k += blockDim.x * VEC) {
+        uint4 raw = *reinterpret_cast<const uint4*>(row + k);
+        const T* e = reinterpret_cast<const T*>(&raw);
+        __half o[VEC];
+#pragma unroll
+        for (int t = 0; t < VEC; ++t) o[t] = __float2half_rn(to_f32(e[t]) * inv);
+        if (VEC == 8) *reinterpret_cast<uint4*>(x16 + static_cast<size_t>(m) * K + k) = *reinterpret_cast<uint4*>(o);
+        else *reinterpret_cast<uint2*>(x16 + static_cast<size_t>(m) * K + k) = *reinterpret_cast<uint2*>(o);
+    }
+    if (threadIdx.x == 0) xs[m] = scale;
+}
+
+// ------------------------------------------------------------------ windowed epilogue
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS) epilogue_kernel(const float* __restrict__ acc, const float* __restrict__ xs,
+                                                              const float* __restrict__ bias, T* __restrict__ y,
+                                                              int M, int n, int ldy) {
+    const int64_t total = static_cast<int64_t>(M) * n;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int m = static_cast<int>(i / n), c = static_cast<int>(i % n);
+        store_as(y + static_cast<size_t>(m) * ldy + c, fmaf(acc[i], xs[m], bias ? bias[c] : 0.f));
+    }
+}
+
+static int grid_for(int64_t work_items) {
+    const int64_t per_wave = static_cast<int64_t>(sm_count()) * 8;      // 8 CTAs of 256 threads per SM
+    int64_t blocks = (work_items + EW_THREADS - 1) / EW_THREADS;
+    if (blocks < 1) blocks = 1;
+    if (blocks > per_wave) blocks = per_wave;
+    return static_cast<int>(blocks);
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace tfp8b
+
+using namespace tfp8b;
+
+#define DISPATCH_DT_FMT(dt, fmt, CALL)                                                  \
+    do {                                                                                \
+        if (fmt == TFP8B_E4M3FN) {                                                      \
+            if (dt == TFP8B_F16) { CALL(__half, TFP8B_E4M3FN); }                        \
+            else if (dt == TFP8B_BF16) { CALL(__nv_bfloat16, TFP8B_E4M3FN); }           \
+            else { CALL(float, TFP8B_E4M3FN); }                                         \
+        } else {                                                                        \
+            if (dt == TFP8B_F16) { CALL(__half, TFP8B_E5M2); }                          \
+            else if (dt == TFP8B_BF16) { CALL(__nv_bfloat16, TFP8B_E5M2); }             \
+            else { CALL(float, TFP8B_E5M2); }                                           \
+        }                                                                               \
+    } while (0)
+
+static bool valid_dt(int dt) { return dt == TFP8B_F16 || dt == TFP8B_BF16 || dt == TFP8B_F32; }
+static bool valid_fmt(int f) { return f == TFP8B_E4M3FN || f == TFP8B_E5M2; }
+
+extern "C" int tfp8b_encode(const void* x, int x_dtype, uint8_t* codes, int64_t n, int fmt, int nan_mode,
+                            tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(n >= 0 && valid_dt(x_dtype) && valid_fmt(fmt), TFP8B_ERR_INVALID, "tfp8b_encode: bad argument");
+    TFP8B_REQUIRE(nan_mode == TFP8B_NAN_CAST || nan_mode == TFP8B_NAN_CANONICAL, TFP8B_ERR_INVALID,
+                  "tfp8b_encode: bad nan_mode %d", nan_mode);
+    if (n == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(x && codes, TFP8B_ERR_INVALID, "tfp8b_encode: null pointer");
+    const int vec = aligned16(x) && aligned16(codes);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = grid_for((n + 15) / 16);
+#define CALL(T, F) encode_kernel<T, F><<<grid, EW_THREADS, 0, st>>>(static_cast<const T*>(x), codes, n, nan_mode, vec)
+    DISPATCH_DT_FMT(x_dtype, fmt, CALL);
+#undef CALL
+    TFP8B_LAUNCH_CHECK("tfp8b_encode");
+    return TFP8B_OK;
+}
+
+extern "C" int tfp8b_decode(const uint8_t* codes, void* out, int out_dtype, int64_t n, int fmt,
+                            tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(n >= 0 && valid_dt(out_dtype) && valid_fmt(fmt), TFP8B_ERR_INVALID, "tfp8b_decode: bad argument");
+    if (n == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(codes && out, TFP8B_ERR_INVALID, "tfp8b_decode: null pointer");
+    const int vec = aligned16(codes) && aligned16(out);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = grid_for((n + 15) / 16);
+#define CALL(T, F) decode_kernel<T, F><<<grid, EW_THREADS, 0, st>>>(codes, static_cast<T*>(out), n, vec)
+    DISPATCH_DT_FMT(out_dtype, fmt, CALL);
+#undef CALL
+    TFP8B_LAUNCH_CHECK("tfp8b_decode");
+    return TFP8B_OK;
+}
+
+extern "C" int tfp8b_dequant(const uint8_t* codes, const void* scale, int scale_kind, void* out, int out_dtype,
+                             int N, int K, int G, int fmt, tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(N >= 0 && K >= 0 && G > 0 && valid_dt(out_dtype) && valid_fmt(fmt), TFP8B_ERR_INVALID,
+                  "tfp8b_dequant: bad argument");
+    TFP8B_REQUIRE(scale_kind == TFP8B_SCALE_F32 || scale_kind == TFP8B_SCALE_UE8M0, TFP8B_ERR_INVALID,
+                  "tfp8b_dequant: bad scale_kind %d", scale_kind);
+    if (N == 0 || K == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(codes && scale && out, TFP8B_ERR_INVALID, "tfp8b_dequant: null pointer");
+    TFP8B_REQUIRE(K % 16 == 0 && G % 16 == 0 && K % G == 0, TFP8B_ERR_UNSUPPORTED,
+                  "tfp8b_dequant: need K %% 16 == 0, G %% 16 == 0, K %% G == 0 (K=%d G=%d)", K, G);
+    TFP8B_REQUIRE(aligned16(codes) && aligned16(out), TFP8B_ERR_INVALID, "tfp8b_dequant: pointers must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = grid_for(static_cast<int64_t>(N) * (K / 16));
+#define CALL(T, F) dequant_kernel<T, F><<<grid, EW_THREADS, 0, st>>>(codes, scale, scale_kind, static_cast<T*>(out), N, K, G)
+    DISPATCH_DT_FMT(out_dtype, fmt, CALL);
+#undef CALL
+    TFP8B_LAUNCH_CHECK("tfp8b_dequant");
+    return TFP8B_OK;
+}
+
+extern "C" int tfp8b_quantize(const void* w, int w_dtype, uint8_t* codes, void* scale, int scale_kind, int N, int K,
+                              int G, int fmt, int pow2, tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(N >= 0 && K >= 0 && G > 0 && valid_dt(w_dtype) && valid_fmt(fmt), TFP8B_ERR_INVALID,
+                  "tfp8b_quantize: bad argument");
+    TFP8B_REQUIRE(scale_kind == TFP8B_SCALE_F32 || (scale_kind == TFP8B_SCALE_UE8M0 && pow2), TFP8B_ERR_INVALID,
+                  "tfp8b_quantize: UE8M0 scales need pow2 != 0");
+    if (N == 0 || K == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(w && codes && scale, TFP8B_ERR_INVALID, "tfp8b_quantize: null pointer");
+    TFP8B_REQUIRE(K % G == 0, TFP8B_ERR_INVALID, "tfp8b_quantize: K=%d not divisible by group_size=%d", K, G);
+    TFP8B_REQUIRE(K % 16 == 0 && G % 16 == 0, TFP8B_ERR_UNSUPPORTED,
+                  "tfp8b_quantize: need K %% 16 == 0 and G %% 16 == 0 (K=%d G=%d)", K, G);
+    TFP8B_REQUIRE(aligned16(w) && aligned16(codes), TFP8B_ERR_INVALID, "tfp8b_quantize: pointers must be 16-byte aligned");
+    const size_t smem = static_cast<size_t>(K / G) * sizeof(uint32_t);
+    TFP8B_REQUIRE(smem <= 48 * 1024, TFP8B_ERR_UNSUPPORTED, "tfp8b_quantize: more than 12288 groups per row");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define CALL(T, F) quantize_kernel<T, F><<<N, EW_THREADS, smem, st>>>(static_cast<const T*>(w), codes, scale, scale_kind, K, G, pow2)
+    DISPATCH_DT_FMT(w_dtype, fmt, CALL);
+#undef CALL
+    TFP8B_LAUNCH_CHECK("tfp8b_quantize");
+    return TFP8B_OK;
+}
+
+extern "C" int tfp8b_prep(const void* x, int x_dtype, void* x16, float* xs, int M, int K, tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(M >= 0 && K >= 0 && valid_dt(x_dtype), TFP8B_ERR_INVALID, "tfp8b_prep: bad argument");
+    if (M == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(x && x16 && xs, TFP8B_ERR_INVALID, "tfp8b_prep: null pointer");
+    TFP8B_REQUIRE(K % 8 == 0 && K > 0, TFP8B_ERR_UNSUPPORTED, "tfp8b_prep: need K %% 8 == 0 (K=%d)", K);
+    TFP8B_REQUIRE(aligned16(x) && aligned16(x16), TFP8B_ERR_INVALID, "tfp8b_prep: pointers must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    __half* o = static_cast<__half*>(x16);
+    if (x_dtype == TFP8B_F16) prep_kernel<__half><<<M, EW_THREADS, 0, st>>>(static_cast<const __half*>(x), o, xs, K);
+    else if (x_dtype == TFP8B_BF16) prep_kernel<__nv_bfloat16><<<M, EW_THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(x), o, xs, K);
+    else prep_kernel<float><<<M, EW_THREADS, 0, st>>>(static_cast<const float*>(x), o, xs, K);
+    TFP8B_LAUNCH_CHECK("tfp8b_prep");
+    return TFP8B_OK;
+}
+
+extern "C" int tfp8b_epilogue(const float* acc, const float* xs, const float* bias, void* y, int y_dtype, int M, int n,
+                              int ldy, tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(M >= 0 && n >= 0 && ldy >= n && valid_dt(y_dtype), TFP8B_ERR_INVALID, "tfp8b_epilogue: bad argument");
+    if (M == 0 || n == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(acc && xs && y, TFP8B_ERR_INVALID, "tfp8b_epilogue: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = grid_for(static_cast<int64_t>(M) * n);
+    if (y_dtype == TFP8B_F16) epilogue_kernel<__half><<<grid, EW_THREADS, 0, st>>>(acc, xs, bias, static_cast<__half*>(y), M, n, ldy);
+    else if (y_dtype == TFP8B_BF16) epilogue_kernel<__nv_bfloat16><<<grid, EW_THREADS, 0, st>>>(acc, xs, bias, static_cast<__nv_bfloat16*>(y), M, n, ldy);
+    else epilogue_kernel<float><<<grid, EW_THREADS, 0, st>>>(acc, xs, bias, static_cast<float*>(y), M, n, ldy);
+    TFP8B_LAUNCH_CHECK("tfp8b_epilogue");
+    return TFP8B_OK;
+}

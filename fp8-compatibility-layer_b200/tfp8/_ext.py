@@ -1,0 +1,313 @@
+"""Operator layer: ctypes bindings of the sm_100a C-ABI library (libtfp8b.so) behind the same
+Python functions the reference's launcher exposes (tfp8/_ext.py there: `available`, `last_error`,
+`GemvLaunch`, `prepare_activations`, `w8a16`, `gemm_prepared`, `dequant_into`, `epilogue_into`,
+`GEMV_MAXM`, `FMT_ID`, `_TAG`), plus `encode`, `decode_codes` and `quantize_weight_cuda`.
+
+The reference compiles its kernels with NVRTC at first use and launches them with
+cuLaunchKernel; here the kernels are built ahead of time by nvcc for sm_100a and every call is one
+C function call on torch's current stream. There is no torch fallback in this module: if the
+library is missing, every operator raises.
+"""
+import ctypes
+import os
+import threading
+
+import torch
+
+GEMV_MAXM = 8                      # rows served by the decode GEMV; larger M goes to the tile GEMM
+GEMV_MT = (8,)                     # one kernel serves every M <= 8 (the reference had a 1/4/8 ladder)
+FMT_ID = {"e4m3fn": 0, "e5m2": 1}
+_TAG = {torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32"}
+_DT = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+SCALE_F32, SCALE_UE8M0 = 0, 1
+
+_LIB_PATH = os.environ.get("TFP8B_LIBRARY") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libtfp8b.so")
+_lock = threading.Lock()
+_lib = None
+_error = None
+
+_P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+_SIGNATURES = {
+    "tfp8b_version": ([], _I),
+    "tfp8b_last_error_string": ([], ctypes.c_char_p),
+    "tfp8b_device_status": ([_P, _P], _I),
+    "tfp8b_encode": ([_P, _I, _P, _L, _I, _I, _P], _I),
+    "tfp8b_decode": ([_P, _P, _I, _L, _I, _P], _I),
+    "tfp8b_quantize": ([_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
+    "tfp8b_dequant": ([_P, _P, _I, _P, _I, _I, _I, _I, _I, _P], _I),
+    "tfp8b_prep": ([_P, _I, _P, _P, _I, _I, _P], _I),
+    "tfp8b_gemv": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
+    "tfp8b_gemm": ([_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
+    "tfp8b_epilogue": ([_P, _P, _P, _P, _I, _I, _I, _I, _P], _I),
+}
+
+
+def library_path() -> str:
+    return _LIB_PATH
+
+
+def load():
+    """The loaded library (ctypes.CDLL). Raises RuntimeError when it is missing or broken."""
+    global _lib, _error
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            try:
+                lib = ctypes.CDLL(_LIB_PATH)
+                for name, (args, res) in _SIGNATURES.items():
+                    fn = getattr(lib, name)
+                    fn.argtypes, fn.restype = args, res
+                _lib = lib
+            except (OSError, AttributeError) as e:
+                _error = e
+                raise RuntimeError(
+                    f"tfp8: the CUDA kernel library could not be loaded from {_LIB_PATH} ({e}). "
+                    "Build it with `python -c 'import __graft_entry__ as g; g.build()'` or "
+                    "`make -C fp8-compatibility-layer_b200/csrc`.") from e
+    return _lib
+
+
+def available() -> bool:
+    """True when a CUDA device is present and the kernel library loads. Never prints and never
+    downgrades anything: callers that hold CUDA tensors and get False must raise."""
+    global _error
+    if not torch.cuda.is_available():
+        return False
+    try:
+        load()
+        return True
+    except RuntimeError as e:
+        _error = _error or e
+        return False
+
+
+def last_error():
+    return _error
+
+
+def _stream(dev: int) -> int:
+    return torch._C._cuda_getCurrentRawStream(dev)
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        msg = load().tfp8b_last_error_string().decode("utf-8", "replace")
+        if rc == -2:
+            raise NotImplementedError(f"{what}: {msg}")
+        raise RuntimeError(f"{what} failed ({rc}): {msg}")
+
+
+def _need_cuda(*tensors):
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise ValueError("tfp8 kernels take CUDA tensors; CPU tensors belong to FP8Linear's torch path")
+        d = t.get_device()
+        if dev is None:
+            dev = d
+        elif d != dev:
+            raise ValueError(f"tensors on different devices (cuda:{dev} and cuda:{d})")
+    return dev
+
+
+def _scale_kind(ws: torch.Tensor) -> int:
+    if ws.dtype == torch.float32:
+        return SCALE_F32
+    if ws.dtype == torch.uint8:
+        return SCALE_UE8M0
+    raise ValueError(f"weight scale must be float32 or uint8 (UE8M0), got {ws.dtype}")
+
+
+def device_status(device=None) -> int:
+    """Status word of the kernels' bounded waits on the current device (0 = all fine).
+    Synchronises. Raises RuntimeError if a kernel gave up on a wait."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    word = ctypes.c_uint(0)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_device_status(ctypes.byref(word), _stream(dev))
+    _check(rc, "tfp8b_device_status")
+    return word.value
+
+
+# ------------------------------------------------------------------ codecs
+def encode(x: torch.Tensor, fmt="e4m3fn", canonical_nan=False) -> torch.Tensor:
+    """uint8 codes of x (f16 / bf16 / f32), RNE + saturate. NaN -> sign|0x7F, or the format's
+    canonical NaN with canonical_nan=True."""
+    dev = _need_cuda(x)
+    x = x.contiguous()
+    if x.dtype not in _DT:
+        x = x.float()
+    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_encode(x.data_ptr(), _DT[x.dtype], out.data_ptr(), x.numel(), FMT_ID[fmt],
+                                 int(canonical_nan), _stream(dev))
+    _check(rc, "tfp8b_encode")
+    return out
+
+
+def decode_codes(codes: torch.Tensor, fmt="e4m3fn", dtype=torch.float16) -> torch.Tensor:
+    """Values of uint8 codes in `dtype` (exact)."""
+    dev = _need_cuda(codes)
+    codes = codes.contiguous()
+    out = torch.empty(codes.shape, dtype=dtype, device=codes.device)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_decode(codes.data_ptr(), out.data_ptr(), _DT[dtype], codes.numel(), FMT_ID[fmt], _stream(dev))
+    _check(rc, "tfp8b_decode")
+    return out
+
+
+def quantize_weight_cuda(w: torch.Tensor, fmt="e4m3fn", group_size=None, pow2_scale=True, ue8m0=False):
+    """One-pass quantizer: w [N,K] -> (codes u8 [N,K], scale [N,K/G] f32 or UE8M0 u8, G)."""
+    dev = _need_cuda(w)
+    N, K = w.shape
+    G = K if group_size is None else group_size
+    if K % G:
+        raise ValueError(f"K={K} not divisible by group_size={G}")
+    w = w.contiguous()
+    if w.dtype not in _DT:
+        w = w.float()
+    q = torch.empty(N, K, dtype=torch.uint8, device=w.device)
+    s = torch.empty(N, K // G, dtype=torch.uint8 if ue8m0 else torch.float32, device=w.device)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_quantize(w.data_ptr(), _DT[w.dtype], q.data_ptr(), s.data_ptr(), int(ue8m0), N, K, G,
+                                   FMT_ID[fmt], int(pow2_scale), _stream(dev))
+    _check(rc, "tfp8b_quantize")
+    return q, s, G
+
+
+def dequant_into(out16, qweight, lut16, wscale, group_size, fmt="e4m3fn"):
+    """out16[n,k] = decode(qweight[n,k]) * wscale[n, k/G], into a caller-provided [n,K] buffer
+    (f16, bf16 or f32). `lut16` is accepted for signature compatibility and unused: the kernels
+    decode by bit arithmetic."""
+    dev = _need_cuda(out16, qweight, wscale)
+    N, K = qweight.shape
+    if not (out16.is_contiguous() and qweight.is_contiguous() and wscale.is_contiguous()):
+        raise ValueError("dequant_into needs contiguous tensors")
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_dequant(qweight.data_ptr(), wscale.data_ptr(), _scale_kind(wscale), out16.data_ptr(),
+                                  _DT[out16.dtype], N, K, group_size, FMT_ID[fmt], _stream(dev))
+    _check(rc, "tfp8b_dequant")
+    return out16
+
+
+# ------------------------------------------------------------------ activations
+def prepare_activations(x):
+    """(x16 fp16 [M,K], xs f32 [M]) in one launch: exact power-of-two row scale that maps the row
+    amax into [2^7, 2^8). Unlike the torch twin, fp16 input is rescaled too (as in the reference's
+    kernel)."""
+    dev = _need_cuda(x)
+    M, K = x.shape
+    x = x.contiguous()
+    x16 = torch.empty(M, K, dtype=torch.float16, device=x.device)
+    xs = torch.empty(M, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_prep(x.data_ptr(), _DT[x.dtype], x16.data_ptr(), xs.data_ptr(), M, K, _stream(dev))
+    _check(rc, "tfp8b_prep")
+    return x16, xs
+
+
+# ------------------------------------------------------------------ GEMV / GEMM
+class GemvLaunch:
+    """A decode-GEMV call for one layer with everything but (x, y, M) bound once.
+
+    Per call: one `torch.empty`, three ctypes values, one C call. The bound tensors are referenced
+    here so their storage outlives the launch; FP8Linear rebuilds the object when a buffer object
+    is replaced. Same constructor and call signature as the reference's class of this name.
+    """
+    __slots__ = ("fn", "dev", "device", "args", "q", "ws", "bias", "lut", "out_dtype", "N", "_stream")
+
+    def __init__(self, x_dtype, qweight, lut16, wscale, bias, out_dtype, group_size, fmt):
+        lib = load()
+        self.dev = _need_cuda(qweight, wscale, bias)
+        self.device = qweight.device
+        N, K = qweight.shape
+        self.N = N
+        self.fn = lib.tfp8b_gemv
+        self._stream = torch._C._cuda_getCurrentRawStream
+        self.args = [_P(0), _I(_DT[x_dtype]), _P(qweight.data_ptr()), _P(wscale.data_ptr()), _I(_scale_kind(wscale)),
+                     _P(bias.data_ptr() if bias is not None else 0), _P(0), _I(_DT[out_dtype]), _I(0), _I(N), _I(K),
+                     _I(group_size), _I(FMT_ID[fmt]), _P(0)]
+        self.q, self.ws, self.bias, self.lut, self.out_dtype = qweight, wscale, bias, lut16, out_dtype
+
+    def __call__(self, x, M, out_shape=None):
+        """x: contiguous CUDA tensor of the bound dtype on this layer's device holding M rows of K
+        (any rank: only its data pointer is used). out_shape: shape of y, default (M, N)."""
+        y = torch.empty(out_shape or (M, self.N), dtype=self.out_dtype, device=self.device)
+        a = self.args
+        a[0].value = x.data_ptr()
+        a[6].value = y.data_ptr()
+        a[8].value = M
+        a[13].value = self._stream(self.dev)
+        rc = self.fn(*a)
+        if rc != 0:
+            _check(rc, "tfp8b_gemv")
+        return y
+
+
+def _gemv(x, qweight, wscale, bias, y, M, N, K, group_size, fmt, dev):
+    rc = load().tfp8b_gemv(x.data_ptr(), _DT[x.dtype], qweight.data_ptr(), wscale.data_ptr(), _scale_kind(wscale),
+                           bias.data_ptr() if bias is not None else 0, y.data_ptr(), _DT[y.dtype], M, N, K,
+                           group_size, FMT_ID[fmt], _stream(dev))
+    _check(rc, "tfp8b_gemv")
+
+
+def _gemm(x16, xs, qweight, wscale, bias, y, M, N, K, group_size, fmt, dev):
+    rc = load().tfp8b_gemm(x16.data_ptr(), xs.data_ptr(), qweight.data_ptr(), wscale.data_ptr(), _scale_kind(wscale),
+                           bias.data_ptr() if bias is not None else 0, y.data_ptr(), _DT[y.dtype], M, N, K,
+                           group_size, FMT_ID[fmt], _stream(dev))
+    _check(rc, "tfp8b_gemm")
+
+
+def w8a16(x, qweight, lut16, wscale, bias, out_dtype, group_size, fmt="e4m3fn"):
+    """y = x @ dequant(qweight).T + bias.
+
+    M <= 8   decode GEMV on x in its own dtype (FP32 accumulate, no prep pass)
+    M > 8    activation prep (fp16 + power-of-two row scale) and the tcgen05 tile GEMM
+    `lut16` is accepted for signature compatibility and unused.
+    """
+    dev = _need_cuda(x, qweight, wscale, bias)
+    M, K = x.shape
+    N = qweight.shape[0]
+    y = torch.empty(M, N, dtype=out_dtype, device=x.device)
+    if M == 0:
+        return y
+    x = x.contiguous()
+    with torch.cuda.device(dev):
+        if M <= GEMV_MAXM:
+            _gemv(x, qweight, wscale, bias, y, M, N, K, group_size, fmt, dev)
+        else:
+            x16, xs = prepare_activations(x)
+            _gemm(x16, xs, qweight, wscale, bias, y, M, N, K, group_size, fmt, dev)
+    return y
+
+
+def gemm_prepared(x16, xs, qweight, lut16, wscale, bias, out_dtype, group_size, fmt="e4m3fn"):
+    """Tile GEMM on an already prepared fp16 activation (any M >= 1)."""
+    dev = _need_cuda(x16, xs, qweight, wscale, bias)
+    M, K = x16.shape
+    N = qweight.shape[0]
+    y = torch.empty(M, N, dtype=out_dtype, device=x16.device)
+    if M:
+        with torch.cuda.device(dev):
+            _gemm(x16.contiguous(), xs, qweight, wscale, bias, y, M, N, K, group_size, fmt, dev)
+    return y
+
+
+def epilogue_into(y, acc, xs, bias, n0=0):
+    """y[:, n0:n0+n] = (acc * xs[:, None] + bias[n0:n0+n]).to(y.dtype) in one launch; acc is a
+    contiguous FP32 [M, n] block, y a contiguous [M, N] output."""
+    dev = _need_cuda(y, acc, xs, bias)
+    M, n = acc.shape
+    if M == 0 or n == 0:
+        return y
+    bview = bias[n0:n0 + n] if bias is not None else None
+    yv = y[:, n0:] if n0 else y
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_epilogue(acc.data_ptr(), xs.data_ptr(), bview.data_ptr() if bview is not None else 0,
+                                   yv.data_ptr(), _DT[y.dtype], M, n, y.shape[1], _stream(dev))
+    _check(rc, "tfp8b_epilogue")
+    return y

@@ -1,0 +1,134 @@
+/*
+ * tfp8b -- C ABI of the B200 (sm_100a) FP8Linear kernels.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues work on the given CUDA
+ * stream of the CURRENT device and returns immediately: 0 on success, a negative TFP8B_ERR_*
+ * code otherwise (tfp8b_last_error_string() holds the detail for the calling thread). Unless
+ * its comment says otherwise an entry point never allocates or frees device memory, never
+ * synchronises and keeps no mutable global state, so calls may be captured in a CUDA graph and
+ * issued from several threads or streams at once. All buffers are owned by the caller and must
+ * stay alive until the stream has passed the call.
+ *
+ * Each declaration names the interface of the reference project (tfp8, Turing NVRTC kernels
+ * launched with cuLaunchKernel from tfp8/_ext.py) that it replaces, as file:line inside that
+ * project.
+ *
+ * Layouts (all row-major, contiguous):
+ *   codes  uint8  [N, K]      FP8 bit patterns, E4M3FN or E5M2
+ *   scale  f32    [N, K/G]    or uint8 [N, K/G] (UE8M0: value 2^(b-127), 255 = NaN); G == K means
+ *                             one scale per output channel
+ *   bias   f32    [N]         or NULL
+ *   x      f16 | bf16 | f32 [M, K]
+ *   y      f16 | bf16 | f32 [M, N]
+ */
+#ifndef TFP8B_H_
+#define TFP8B_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TFP8B_VERSION 100
+
+#if defined(__GNUC__)
+#define TFP8B_API __attribute__((visibility("default")))
+#else
+#define TFP8B_API
+#endif
+
+/* element types of activations / outputs; the numbering is the reference's DT_F16/DT_BF16/DT_F32
+ * (tfp8/csrc/tfp8_kernels.cu:127) */
+enum { TFP8B_F16 = 0, TFP8B_BF16 = 1, TFP8B_F32 = 2 };
+/* FP8 formats; the numbering is FMT_ID (tfp8/_ext.py:41) */
+enum { TFP8B_E4M3FN = 0, TFP8B_E5M2 = 1 };
+/* weight-scale storage */
+enum { TFP8B_SCALE_F32 = 0, TFP8B_SCALE_UE8M0 = 1 };
+/* what a NaN input encodes to: CAST = sign|0x7F in both formats (what quantize_weight's
+ * clamp-then-cast produces, tfp8/quantize.py:33-35); CANONICAL = 0x7F (E4M3FN) / 0x7E (E5M2)
+ * without sign (tfp8/formats.py:93-95) */
+enum { TFP8B_NAN_CAST = 0, TFP8B_NAN_CANONICAL = 1 };
+
+enum {
+    TFP8B_OK = 0,
+    TFP8B_ERR_INVALID = -1,     /* null pointer, bad enum, negative size, misaligned pointer */
+    TFP8B_ERR_UNSUPPORTED = -2, /* shape outside what the kernels serve (K % 32, G % 32, ...) */
+    TFP8B_ERR_CUDA = -3,        /* a CUDA runtime / driver call failed */
+    TFP8B_ERR_DEVICE = -4       /* a kernel gave up on a bounded wait (see tfp8b_device_status) */
+};
+
+typedef void* tfp8b_stream_t; /* a cudaStream_t */
+
+/* Library version (TFP8B_VERSION at build time). No reference counterpart. */
+TFP8B_API int tfp8b_version(void);
+
+/* Text of the last error on the calling thread ("" if none). Replaces the RuntimeError text built
+ * from cuLaunchKernel's return code (tfp8/_ext.py:156-157, 215-216). */
+TFP8B_API const char* tfp8b_last_error_string(void);
+
+/* Reads and clears the device-side status word of the current device: 0 = no kernel has given up
+ * on a bounded wait since the last call. SYNCHRONISES the stream. out_status may be NULL.
+ * Returns TFP8B_ERR_DEVICE when the word was non-zero. No reference counterpart (its kernels
+ * have no waits). */
+TFP8B_API int tfp8b_device_status(unsigned int* out_status, tfp8b_stream_t stream);
+
+/* codes[i] = FP8(x[i]): round to nearest even, saturate to +-max finite, never inf.
+ * Replaces the device encoder m_enc16_f16/f32 + enc_e4m3 (tests/bench_transcode.py:206-225,
+ * 319-343) and the elementwise part of quantize_weight (tfp8/quantize.py:33-35). */
+TFP8B_API int tfp8b_encode(const void* x, int x_dtype, uint8_t* codes, int64_t n, int fmt, int nan_mode,
+                 tfp8b_stream_t stream);
+
+/* out[i] = value of codes[i] in out_dtype (exact; NaN, inf and -0 kept).
+ * Replaces m_dec16_* (tests/bench_transcode.py:228-317) / lut(fmt)[codes] (tfp8/formats.py:63). */
+TFP8B_API int tfp8b_decode(const uint8_t* codes, void* out, int out_dtype, int64_t n, int fmt,
+                 tfp8b_stream_t stream);
+
+/* One-pass weight quantizer: per (row, K-group) amax -> scale -> codes.
+ *   s = max(amax / fmax, FLT_MIN); pow2 != 0: s = 2^ceil(log2 s); s = 1 where amax == 0;
+ *   codes = FP8(clamp(w / s, +-fmax)).  scale_kind UE8M0 needs pow2 != 0.
+ * Replaces quantize_weight (tfp8/quantize.py:15-36). K % G == 0, G % 16 == 0. */
+TFP8B_API int tfp8b_quantize(const void* w, int w_dtype, uint8_t* codes, void* scale, int scale_kind,
+                   int N, int K, int G, int fmt, int pow2, tfp8b_stream_t stream);
+
+/* out[n,k] = out_dtype(decode(codes[n,k]) * scale[n, k/G]); out_dtype f16 (the reference's
+ * workspace type), bf16 or f32. Replaces tfp8_dequant_f16 / dequant_into
+ * (tfp8/csrc/tfp8_kernels.cu:435-456, tfp8/_ext.py:305-315). K % 16 == 0, G % 16 == 0. */
+TFP8B_API int tfp8b_dequant(const uint8_t* codes, const void* scale, int scale_kind, void* out,
+                  int out_dtype, int N, int K, int G, int fmt, tfp8b_stream_t stream);
+
+/* Activation rows -> fp16 with an exact power-of-two row scale: e = ceil(log2 amax) - 8
+ * (0 for an all-zero row), x16 = fp16(x / 2^e), xs = 2^e. Replaces tfp8_prep_{f16,bf16,f32} /
+ * prepare_activations (tfp8/csrc/tfp8_kernels.cu:513-539, tfp8/_ext.py:220-227). K % 8 == 0. */
+TFP8B_API int tfp8b_prep(const void* x, int x_dtype, void* x16, float* xs, int M, int K,
+               tfp8b_stream_t stream);
+
+/* Decode GEMV, 1 <= M <= 8:  y[m,n] = sum_g scale[n,g] * sum_{k in g} x[m,k]*dec(codes[n,k]) + bias[n]
+ * with x consumed in its own dtype and FP32 accumulation. Replaces the 27 tfp8_gemv_in_*_m*_*
+ * kernels and their launcher (tfp8/csrc/tfp8_kernels.cu:171-269, 414-425; tfp8/_ext.py:163-217,
+ * 230-250). K % 32 == 0, G % 32 == 0, x / codes 16-byte aligned. */
+TFP8B_API int tfp8b_gemv(const void* x, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind,
+               const float* bias, void* y, int y_dtype, int M, int N, int K, int G, int fmt,
+               tfp8b_stream_t stream);
+
+/* Tile GEMM for any M >= 1 on prepared activations (tfp8b_prep):
+ *   y[m,n] = xs[m] * sum_k x16[m,k] * dec(codes[n,k]) * scale[n,k/G] + bias[n]
+ * FP8 tiles are decoded to fp16 in shared memory (group scales folded in as scale/rowmax),
+ * multiplied by tcgen05.mma with FP32 accumulators in tensor memory. Replaces tfp8_gemm_* /
+ * gemm_prepared and the chunked dequant+cuBLAS+epilogue path (tfp8/csrc/tfp8_kernels.cu:288-411,
+ * 428-430; tfp8/_ext.py:259-275; tfp8/linear.py:107-128). K % 32 == 0, G % 32 == 0,
+ * x16 / codes 16-byte aligned. Builds two tensor maps on the host per call (no allocation). */
+TFP8B_API int tfp8b_gemm(const void* x16, const float* xs, const uint8_t* codes, const void* scale,
+               int scale_kind, const float* bias, void* y, int y_dtype, int M, int N, int K, int G,
+               int fmt, tfp8b_stream_t stream);
+
+/* y[m, 0:n] = y_dtype(acc[m, 0:n] * xs[m] + bias[0:n]) into a column window of a wider output
+ * (row pitch ldy elements). Replaces tfp8_epilogue_* / epilogue_into
+ * (tfp8/csrc/tfp8_kernels.cu:478-503, tfp8/_ext.py:282-302). */
+TFP8B_API int tfp8b_epilogue(const float* acc, const float* xs, const float* bias, void* y, int y_dtype,
+                   int M, int n, int ldy, tfp8b_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TFP8B_H_ */
