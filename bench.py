@@ -1,0 +1,388 @@
+"""Benchmark of the FP8Linear hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            this build (CUDA kernels through the C ABI)
+    python bench.py --impl reference --gpus N ...            the reference's CPU path, timed on the host cores
+
+Headline metric (BASELINE.json, configs[1]): weight-streaming bandwidth of the M = 1 decode GEMV
+over Llama-7B-shaped FP8 E4M3FN layers with per-channel scales. One "step" is one pass over
+DECODE_COPIES x the four layer shapes -- 314 MB of distinct codes, more than twice the L2, so
+every pass streams from HBM. `value` is algorithmic bytes / time with everything resident in
+HBM and the launches replayed from a CUDA graph; `e2e` is the same pass through
+`FP8Linear.forward` with pinned HOST activations copied in and results copied out every layer.
+With N > 1 ranks (torchrun) every rank streams its own copy of the layer set (independent
+layers, no data-path collective: weak scaling); extra keys report the tensor-parallel GEMM.
+
+One JSON line is printed by rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (os.path.join(ROOT, "fp8-compatibility-layer_b200"), ROOT):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+DECODE_COPIES = 2
+METRIC = "fp8linear_gemv_m1_weight_stream_bandwidth"
+UNIT = "GB/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def gemv_bytes(M, N, K, G, xsz=2, ysz=2, scale_bytes=4, bias=False):
+    """Algorithmic bytes of one GEMV: codes + scales + activations in + results out (+ bias)."""
+    return N * K + scale_bytes * N * (K // G) + M * K * xsz + M * N * ysz + (4 * N if bias else 0)
+
+
+# ---------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()          # the exact child this object started
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------- CPU baseline
+def cpu_baseline(budget_s=12.0):
+    """The reference's CPU path (dequantize the whole weight to float32, then a float32 matmul;
+    tfp8/linear.py:179-181 in the reference) restated in C with OpenMP, on all host threads.
+    Sample: the M = 1 forward of the 4096x4096 and 11008x4096 layers, repeated for ~budget_s."""
+    from oracle import c_port
+    from tfp8 import synth
+    lib = c_port.load()
+    shapes = [(4096, 4096), (11008, 4096)]
+    layers = []
+    for i, (N, K) in enumerate(shapes):
+        q = synth.random_codes(N, K, torch.float8_e4m3fn, seed=i).numpy()
+        s = np.full((N, 1), 2.0 ** -13, np.float32)
+        x = synth.activations(1, K, seed=7).float().numpy()
+        layers.append((x, q, s, np.empty((N, K), np.float32)))
+    for x, q, s, work in layers:                       # warm-up, page in
+        c_port.linear_forward(x, q, s, None, "e4m3fn", q.shape[1], work, lib)
+    nbytes, t0, reps = 0, time.perf_counter(), 0
+    while time.perf_counter() - t0 < budget_s:
+        for x, q, s, work in layers:
+            c_port.linear_forward(x, q, s, None, "e4m3fn", q.shape[1], work, lib)
+            nbytes += gemv_bytes(1, q.shape[0], q.shape[1], q.shape[1], xsz=4, ysz=4)
+        reps += 1
+    dt = time.perf_counter() - t0
+    return {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{reps} x M=1 forward of FP8 layers 4096x4096 and 11008x4096 (dequantize to f32 + f32 matmul, "
+                      f"C/OpenMP restatement of the reference's torch CPU path), {dt:.1f} s",
+            "threads": int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))}
+
+
+# ---------------------------------------------------------------------------------- workloads
+def build_decode_layers(device, fmt="e4m3fn", copies=DECODE_COPIES, seed=0):
+    """copies x the four Llama-7B projection shapes as FP8Linear layers (config 2): Gaussian
+    N(0, 0.02^2) weights, per-channel power-of-two scales, quantized on the GPU by the fused kernel."""
+    from tfp8 import FP8Linear, synth
+    layers = []
+    g = torch.Generator(device=device).manual_seed(seed)
+    for c in range(copies):
+        for (N, K) in synth.DECODE_SHAPES:
+            w = (torch.randn(N, K, generator=g, device=device) * 0.02).half()
+            lin = torch.nn.Linear(K, N, bias=False, device=device, dtype=torch.float16)
+            lin.weight.data = w
+            layers.append(FP8Linear.from_linear(lin, fmt=fmt, nan_check=False))
+            del lin, w
+    return layers
+
+
+def time_graph(fn, steps, warmup):
+    """Capture fn() (one step) in a CUDA graph, replay warmup + steps times, return seconds per step
+    measured with CUDA events on the replay stream."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fn()                                   # warm (allocations, lazy module state)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            fn()
+        for _ in range(warmup):
+            g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record(s)
+        for _ in range(steps):
+            g.replay()
+        e1.record(s)
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / 1e3 / steps
+
+
+def time_eager(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / 1e3 / steps
+
+
+def barrier(world):
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x, world, device):
+    if world == 1:
+        return x
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t.item())
+
+
+# ---------------------------------------------------------------------------------- main arms
+def run_ours(args, rank, world, local_rank):
+    from tfp8 import _ext, synth
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    _ext.load()
+    peaks = measured_peaks()
+    layers = build_decode_layers(device)
+    xs = [synth.activations(1, l.in_features, seed=11 + i).to(device) for i, l in enumerate(layers)]
+    launches = [_ext.GemvLaunch(torch.float16, l.qweight, None, l.weight_scale, None, torch.float16,
+                                l.group_size, l.fmt) for l in layers]
+    outs = [torch.empty(1, l.out_features, dtype=torch.float16, device=device) for l in layers]
+    step_bytes = sum(gemv_bytes(1, l.out_features, l.in_features, l.group_size) for l in layers)
+    weight_bytes = sum(l.out_features * l.in_features for l in layers)
+    lib = _ext.load()
+
+    def step_resident():
+        # the C-ABI entry point itself, outputs preallocated: nothing but kernels in the timed region
+        st = torch.cuda.current_stream().cuda_stream
+        for l, x, y in zip(layers, xs, outs):
+            rc = lib.tfp8b_gemv(x.data_ptr(), 0, l.qweight.data_ptr(), l.weight_scale.data_ptr(), 0, None,
+                                y.data_ptr(), 0, 1, l.out_features, l.in_features, l.group_size, 0, st)
+            assert rc == 0, lib.tfp8b_last_error_string()
+
+    barrier(world)
+    with ClockSampler(local_rank) as clk:
+        barrier(world)
+        sec = time_graph(step_resident, args.steps, args.warmup)
+        barrier(world)
+    sec = max_over_ranks(sec, world, device)
+    value = world * step_bytes / sec / 1e9
+
+    # end to end: pinned host activations in, results out, through FP8Linear.forward
+    hx = [x.cpu().pin_memory() for x in xs]
+    hy = [torch.empty(1, l.out_features, dtype=torch.float16).pin_memory() for l in layers]
+    dx = [torch.empty_like(x) for x in xs]
+
+    def step_e2e():
+        for l, h, d, o in zip(layers, hx, dx, hy):
+            d.copy_(h, non_blocking=True)
+            o.copy_(l(d), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    barrier(world)
+    e2e_sec = max_over_ranks(time_eager(step_e2e, args.steps, args.warmup), world, device)
+    e2e = {"value": world * step_bytes / e2e_sec / 1e9, "unit": UNIT,
+           "h2d_bytes_per_step": sum(h.numel() * 2 for h in hx), "d2h_bytes_per_step": sum(h.numel() * 2 for h in hy),
+           "ms_per_step": e2e_sec * 1e3}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "impl": "tfp8_b200",
+        "config": {"workload": "decode GEMV sweep (BASELINE configs[1]): M=1 fp16 activations x FP8 E4M3FN weights, "
+                               "per-channel pow2 f32 scales, (N,K) in (4096,4096),(12288,4096),(11008,4096),(4096,11008), "
+                               f"{DECODE_COPIES} distinct copies per rank", "layers_per_step": len(layers),
+                   "weight_bytes_per_step": weight_bytes, "algorithmic_bytes_per_step": step_bytes,
+                   "l2": "inputs larger than L2: 314 MB of distinct codes per pass", "launch": "CUDA graph replay"},
+        "gpu_launches": args.steps * len(layers),
+        "e2e": e2e,
+        "clocks": clk.summary(),
+        "roofline": {"bound": "hbm", "achieved": step_bytes / sec / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": step_bytes / sec / 1e9 / peaks["hbm_gbs"], "traffic": None,
+                     "peak_source": peaks["source"], "kernel": "gemv_kernel<__half, E4M3FN, per-channel>",
+                     "avg_launch_us": sec / len(layers) * 1e6,
+                     "weights_only_gbs": weight_bytes / sec / 1e9},
+    }
+    if not args.quick and world == 1:
+        line["extra"] = extra_measurements(args, device, peaks, world)
+    if rank == 0 and world == 1:
+        line["cpu_baseline"] = cpu_baseline(args.cpu_seconds)
+    return line
+
+
+def extra_measurements(args, device, peaks, world):
+    """Per-shape GEMV table (M = 1..8, both formats), the group-scaled and prefill GEMMs
+    (configs 3 and 4) and the encoder, each timed with CUDA events over inputs larger than L2 or
+    rotated over distinct buffers."""
+    from tfp8 import FP8Linear, _ext, synth
+    lib = _ext.load()
+    out = {"gemv": [], "gemm": [], "codec": []}
+    st = lambda: torch.cuda.current_stream().cuda_stream
+    # --- GEMV per shape / M / format: rotate over enough copies to exceed 2x L2
+    for fmt_id, fmt in ((0, "e4m3fn"), (1, "e5m2")):
+        for (N, K) in synth.DECODE_SHAPES:
+            copies = max(2, int(np.ceil(2.2 * 126e6 / (N * K))))
+            qs = [synth.random_codes(N, K, torch.float8_e4m3fn if fmt_id == 0 else torch.float8_e5m2, seed=c).to(device)
+                  for c in range(copies)]
+            sc = torch.full((N, 1), 2.0 ** -13, device=device)
+            for M in synth.DECODE_M:
+                x = synth.activations(M, K).to(device)
+                y = torch.empty(M, N, dtype=torch.float16, device=device)
+
+                def step():
+                    for q in qs:
+                        lib.tfp8b_gemv(x.data_ptr(), 0, q.data_ptr(), sc.data_ptr(), 0, None, y.data_ptr(), 0, M, N, K, K,
+                                       fmt_id, st())
+                sec = time_graph(step, 20, 3) / copies
+                b = gemv_bytes(M, N, K, K)
+                out["gemv"].append({"fmt": fmt, "N": N, "K": K, "M": M, "us": sec * 1e6, "gbs": b / sec / 1e9,
+                                    "frac_hbm": b / sec / 1e9 / peaks["hbm_gbs"]})
+            del qs
+    # --- tile GEMM: config 3 (G=128 UE8M0, fp16 x) and config 4 (G=32 UE8M0, bf16 x)
+    N, K = synth.GROUP_GEMM_SHAPE
+    q = synth.random_codes(N, K, torch.float8_e4m3fn, seed=3).to(device)
+    for G, Ms, xdt in ((128, synth.GROUP_GEMM_M, torch.float16), (32, synth.PREFILL_M, torch.bfloat16)):
+        e8 = torch.randint(110, 118, (N, K // G), dtype=torch.uint8, device=device)
+        for M in Ms:
+            x = synth.activations(M, K, dtype=xdt).to(device)
+            y = torch.empty(M, N, dtype=torch.float16, device=device)
+            x16 = torch.empty(M, K, dtype=torch.float16, device=device)
+            xsc = torch.empty(M, dtype=torch.float32, device=device)
+
+            def step(with_prep=True):
+                if with_prep:
+                    lib.tfp8b_prep(x.data_ptr(), 0 if xdt == torch.float16 else 1, x16.data_ptr(), xsc.data_ptr(), M, K, st())
+                rc = lib.tfp8b_gemm(x16.data_ptr(), xsc.data_ptr(), q.data_ptr(), e8.data_ptr(), 1, None, y.data_ptr(), 0,
+                                    M, N, K, G, 0, st())
+                assert rc == 0, lib.tfp8b_last_error_string()
+            iters = 10 if M <= 1024 else 4
+            sec = time_eager(step, iters, 3)
+            sec_mm = time_eager(lambda: step(False), iters, 2)
+            fl = 2.0 * M * N * K
+            byt = N * K + N * (K // G) + M * K * 2 + M * N * 2
+            bound_s = max(fl / (peaks["bf16_tflops"] * 1e12), byt / (peaks["hbm_gbs"] * 1e9))
+            out["gemm"].append({"M": M, "N": N, "K": K, "G": G, "x": str(xdt).replace("torch.", ""),
+                                "ms_prep_plus_gemm": sec * 1e3, "ms_gemm": sec_mm * 1e3, "tflops": fl / sec / 1e12,
+                                "tflops_gemm_only": fl / sec_mm / 1e12,
+                                "frac_tensor_peak": fl / sec_mm / 1e12 / peaks["bf16_tflops"],
+                                "frac_of_bound": bound_s / sec_mm})
+            del x, y, x16
+    del q
+    # --- encoder and fused quantizer on a 256 Mi-element fp16 tensor (512 MB in, 256 MB out)
+    n = 1 << 28
+    w = (torch.randn(n // 8192, 8192, device=device) * 0.02).half()
+    codes = torch.empty(w.shape, dtype=torch.uint8, device=device)
+    sec = time_eager(lambda: lib.tfp8b_encode(w.data_ptr(), 0, codes.data_ptr(), n, 0, 0, st()), 5, 3)
+    out["codec"].append({"op": "encode f16->e4m3fn", "elements": n, "gelem_s": n / sec / 1e9, "gbs": 3 * n / sec / 1e9,
+                         "frac_hbm": 3 * n / sec / 1e9 / peaks["hbm_gbs"]})
+    sc = torch.empty(w.shape[0], 1, device=device)
+    sec = time_eager(lambda: lib.tfp8b_quantize(w.data_ptr(), 0, codes.data_ptr(), sc.data_ptr(), 0, w.shape[0], 8192, 8192, 0, 1,
+                                                st()), 5, 3)
+    out["codec"].append({"op": "quantize_weight f16 per-channel", "elements": n, "gelem_s": n / sec / 1e9,
+                         "gbs": 3 * n / sec / 1e9, "frac_hbm": 3 * n / sec / 1e9 / peaks["hbm_gbs"]})
+    sec = time_eager(lambda: lib.tfp8b_decode(codes.data_ptr(), w.data_ptr(), 0, n, 0, st()), 5, 3)
+    out["codec"].append({"op": "decode e4m3fn->f16", "elements": n, "gelem_s": n / sec / 1e9, "gbs": 3 * n / sec / 1e9,
+                         "frac_hbm": 3 * n / sec / 1e9 / peaks["hbm_gbs"]})
+    return out
+
+
+def run_reference(args, rank, world):
+    """The reference's own CPU implementation of the path on the host cores, same metric."""
+    if rank != 0:
+        return None
+    steps = max(1, args.steps)
+    base = cpu_baseline(budget_s=min(60.0, max(5.0, 1.0 * steps)))
+    return {"metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "impl": "reference",
+            "config": {"workload": "decode GEMV sweep (BASELINE configs[1]), bounded sample on the host cores"},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--quick", action="store_true", help="headline only: skip the per-shape / GEMM / codec tables")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        line = run_reference(args, rank, world)
+        if line is not None:
+            print(json.dumps(line))
+        return
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    line = run_ours(args, rank, world, local_rank)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -19,15 +19,21 @@ static int sm_count() {
 // ------------------------------------------------------------------ 16-element loads per dtype
 template <typename T>
 __device__ __forceinline__ void load16(const T* p, float v[16]);
+// fp16 bits -> float. The hardware conversion turns every NaN into the positive canonical NaN;
+// the encoders and torch keep a NaN's sign, so it is put back here.
+__device__ __forceinline__ float half_bits_to_f32(uint32_t h) {
+    float f = __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
+    if ((h & 0x7FFFu) > 0x7C00u) f = __uint_as_float(0x7FC00000u | ((h & 0x8000u) << 16));
+    return f;
+}
 template <>
 __device__ __forceinline__ void load16<__half>(const __half* p, float v[16]) {
     uint4 a = reinterpret_cast<const uint4*>(p)[0], b = reinterpret_cast<const uint4*>(p)[1];
-    const __half2* h = reinterpret_cast<const __half2*>(&a);
-    const __half2* g = reinterpret_cast<const __half2*>(&b);
+    const uint32_t u[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y;
-        float2 e = __half22float2(g[i]); v[8 + 2 * i] = e.x; v[9 + 2 * i] = e.y;
+    for (int i = 0; i < 8; ++i) {
+        v[2 * i] = half_bits_to_f32(u[i] & 0xFFFFu);
+        v[2 * i + 1] = half_bits_to_f32(u[i] >> 16);
     }
 }
 template <>
@@ -77,6 +83,10 @@ __device__ __forceinline__ void store16<float>(float* p, const float v[16]) {
         reinterpret_cast<float4*>(p)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
 }
 
+__device__ __forceinline__ float scalar_f32(__half v) { return half_bits_to_f32(__half_as_ushort(v)); }
+__device__ __forceinline__ float scalar_f32(__nv_bfloat16 v) { return __uint_as_float(static_cast<uint32_t>(__bfloat16_as_ushort(v)) << 16); }
+__device__ __forceinline__ float scalar_f32(float v) { return v; }
+
 template <int FMT>
 __device__ __forceinline__ uint4 encode16(const float v[16], int nan_mode) {
     uint32_t w[4];
@@ -95,9 +105,8 @@ __device__ __forceinline__ void decode16(uint4 raw, float v[16]) {
     for (int i = 0; i < 4; ++i) {
         uint32_t p01, p23;
         dec4<FMT, false>(w[i], p01, p23);
-        float2 a = __half22float2(*reinterpret_cast<__half2*>(&p01));
-        float2 b = __half22float2(*reinterpret_cast<__half2*>(&p23));
-        v[4 * i] = a.x; v[4 * i + 1] = a.y; v[4 * i + 2] = b.x; v[4 * i + 3] = b.y;
+        v[4 * i] = half_bits_to_f32(p01 & 0xFFFFu); v[4 * i + 1] = half_bits_to_f32(p01 >> 16);
+        v[4 * i + 2] = half_bits_to_f32(p23 & 0xFFFFu); v[4 * i + 3] = half_bits_to_f32(p23 >> 16);
     }
 }
 
@@ -113,7 +122,7 @@ __global__ void __launch_bounds__(EW_THREADS) encode_kernel(const T* __restrict_
         reinterpret_cast<uint4*>(out)[i] = encode16<FMT>(v, nan_mode);
     }
     for (int64_t i = nvec * 16 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
-        out[i] = static_cast<uint8_t>(encode1<FMT>(to_f32(x[i]), nan_mode));
+        out[i] = static_cast<uint8_t>(encode1<FMT>(scalar_f32(x[i]), nan_mode));
 }
 
 // ------------------------------------------------------------------ decode (no scale)
@@ -128,7 +137,7 @@ __global__ void __launch_bounds__(EW_THREADS) decode_kernel(const uint8_t* __res
         store16<T>(out + i * 16, v);
     }
     for (int64_t i = nvec * 16 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
-        store_as(out + i, dec1_f32(codes[i], FMT));
+        store_as(out + i, half_bits_to_f32(dec2_f16<FMT>((static_cast<uint32_t>(codes[i])) << 8) & 0xFFFFu));
 }
 
 // ------------------------------------------------------------------ dequant with scales

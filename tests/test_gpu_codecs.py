@@ -27,6 +27,8 @@ def test_decode_all_256_codes(ext, golden, fmt, dtype):
     got = ext.decode_codes(codes, fmt, dtype)
     want = t_f32(golden[f"decode32_{fmt}"])
     assert same_bits_or_nan(got, want)
+    if dtype == torch.float32:                                                # NaN codes keep their sign
+        assert np.array_equal(got.cpu().numpy().view(np.uint32) >> 31, golden[f"decode32_{fmt}"] >> 31)
     assert same_bits_or_nan(got, codes.view(TORCH_FP8[fmt]).float())          # torch.float8_* agrees
     # unaligned / ragged length: the scalar tail path
     rag = torch.arange(256, dtype=torch.uint8, device="cuda").repeat(3)[5:5 + 613]
@@ -95,12 +97,19 @@ def test_quantize_large_against_oracle(ext, G):
     q, s, Gr = ext.quantize_weight_cuda(w.cuda(), "e4m3fn", G)
     oq, os_, _ = O.quantize_weight(w.float().numpy(), "e4m3fn", G)
     assert np.array_equal(s.cpu().numpy(), os_) and np.array_equal(q.cpu().numpy(), oq)
-    # encode -> decode -> encode is idempotent, and dequantized values stay within half a step
+    # quantize -> dequantize -> quantize -> dequantize reproduces the same values (the second
+    # pass may pick a smaller power-of-two scale when a group's largest code is below half range,
+    # so the codes may shift by an exponent step, but every value is representable exactly)
     deq = torch.empty(512, 2048, dtype=torch.float32, device="cuda")
     ext.dequant_into(deq, q, None, s, Gr, "e4m3fn")
     assert np.array_equal(deq.cpu().numpy(), O.dequantize_weight(oq, os_, "e4m3fn", Gr))
     q2, s2, _ = ext.quantize_weight_cuda(deq, "e4m3fn", G)
-    assert torch.equal(q2, q) and torch.equal(s2, s)
+    deq2 = torch.empty_like(deq)
+    ext.dequant_into(deq2, q2, None, s2, Gr, "e4m3fn")
+    assert torch.equal(deq2, deq)
+    # half a quantization step at most: |w - deq| <= s * 2^(e-3) / 2 <= s * 16 for E4M3FN
+    err = (w.float().cuda() - deq).abs().reshape(512, -1, Gr)
+    assert bool((err <= s.unsqueeze(-1) * 16.0).all())
 
 
 @pytest.mark.parametrize("fmt", FMTS)

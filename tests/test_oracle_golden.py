@@ -125,3 +125,47 @@ def test_cpu_forward_matches_reference(golden):
         # same float32 arithmetic, different summation order inside the BLAS call
         eps = {"f16": 2.0 ** -10, "bf16": 2.0 ** -7, "f32": 2.0 ** -20}[od]
         assert np.all(np.abs(y - ref) <= eps * np.abs(ref) + 1e-5 * np.abs(ref).max()), case
+
+
+# ------------------------------------------------------------------ C restatement and the reference's fp8.h
+def test_c_port_matches_numpy_oracle(golden):
+    from oracle import c_port
+    for fmt in FMTS:
+        assert same_floats(c_port.decode_table(fmt), O.decode_table(fmt))
+        x = f32(golden[f"enc_x_{fmt}"])
+        assert np.array_equal(c_port.encode(x, fmt, "cast"), golden[f"enc_cast_{fmt}"])
+        assert np.array_equal(c_port.encode(x, fmt, "canonical"), golden[f"enc_formats_{fmt}"])
+    rng = np.random.default_rng(0)
+    q = rng.integers(0, 256, (96, 512), dtype=np.uint8)
+    q[np.isnan(O.decode_table("e4m3fn")[q])] = 0x10
+    s = np.exp2(rng.integers(-10, 2, (96, 4))).astype(np.float32)
+    x = rng.standard_normal((5, 512)).astype(np.float32)
+    b = rng.standard_normal(96).astype(np.float32)
+    y = c_port.linear_forward(x, q, s, b, "e4m3fn", 128)
+    ref = O.linear_forward_f64(x.astype(np.float64), q, s, b, "e4m3fn", 128)
+    assert np.abs(y - ref).max() <= 1e-5 * np.abs(ref).max()
+
+
+def test_reference_fp8_header_agrees():
+    """The reference's own C++ header (compiled where the checkout exists) against the oracle:
+    its LUT, its decode and its encoder on every finite code value, midpoint and saturation case."""
+    from oracle import c_port
+    ref = c_port.load_ref()
+    if ref is None:
+        pytest.skip("oracle/_ref was not built (no reference checkout at build time)")
+    for fi, fmt in enumerate(FMTS):
+        lut = np.empty(256, np.uint16)
+        ref.ref_fp8_build_lut(fi, lut.ctypes.data_as(__import__("ctypes").c_void_p))
+        mine = O.lut16_bits(fmt)
+        nan = np.isnan(mine.view(np.float16))
+        assert np.array_equal(lut[~nan], mine[~nan]) and np.all(np.isnan(lut.view(np.float16)[nan]))
+        table = O.decode_table(fmt)
+        for c in range(256):
+            v = ref.ref_fp8_decode(c, fi)
+            assert (np.isnan(v) and np.isnan(table[c])) or (v == table[c] and np.signbit(v) == np.signbit(table[c]))
+        pos = table[:128][np.isfinite(table[:128])].astype(np.float64)
+        pts = np.concatenate([pos, (pos[:-1] + pos[1:]) / 2, [1e9, O.FORMATS[fmt][4] * 1.5, np.inf]]).astype(np.float32)
+        pts = np.concatenate([pts, -pts])
+        want = O.encode(pts, fmt, "cast")
+        got = np.array([ref.ref_fp8_encode(float(p), fi) for p in pts], np.uint8)
+        assert np.array_equal(got, want)
