@@ -97,7 +97,9 @@ __device__ __forceinline__ uint4 encode16(const float v[16], int nan_mode) {
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// 16 codes -> 16 floats (exact) through the fp16 bit decode.
+// 16 codes -> 16 floats (exact) through the fp16 decode. The conversion instruction returns
+// the positive NaN for 0x7F and 0xFF alike; torch keeps the code's sign, so the (rare) E4M3FN
+// NaN bytes are patched afterwards.
 template <int FMT>
 __device__ __forceinline__ void decode16(uint4 raw, float v[16]) {
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -107,6 +109,13 @@ __device__ __forceinline__ void decode16(uint4 raw, float v[16]) {
         dec4<FMT, false>(w[i], p01, p23);
         v[4 * i] = half_bits_to_f32(p01 & 0xFFFFu); v[4 * i + 1] = half_bits_to_f32(p01 >> 16);
         v[4 * i + 2] = half_bits_to_f32(p23 & 0xFFFFu); v[4 * i + 3] = half_bits_to_f32(p23 >> 16);
+        if (FMT == TFP8B_E4M3FN && (((w[i] & 0x7F7F7F7Fu) + 0x01010101u) & 0x80808080u)) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const uint32_t c = (w[i] >> (8 * b)) & 0xFFu;
+                if ((c & 0x7Fu) == 0x7Fu) v[4 * i + b] = __uint_as_float(0x7FC00000u | (c << 24 & 0x80000000u));
+            }
+        }
     }
 }
 
@@ -137,7 +146,12 @@ __global__ void __launch_bounds__(EW_THREADS) decode_kernel(const uint8_t* __res
         store16<T>(out + i * 16, v);
     }
     for (int64_t i = nvec * 16 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
-        store_as(out + i, half_bits_to_f32(dec2_f16<FMT>((static_cast<uint32_t>(codes[i])) << 8) & 0xFFFFu));
+        {
+            const uint32_t c = codes[i];
+            float f = half_bits_to_f32(dec2_f16<FMT>(c) & 0xFFFFu);
+            if (FMT == TFP8B_E4M3FN && (c & 0x7Fu) == 0x7Fu) f = __uint_as_float(0x7FC00000u | (c << 24 & 0x80000000u));
+            store_as(out + i, f);
+        }
 }
 
 // ------------------------------------------------------------------ dequant with scales

@@ -6,28 +6,36 @@
 // decodes each FP8 tile once and multiplies it against up to 256 activation rows, and small M
 // (16..128) simply uses a narrower MMA instead of padding the 128-row dimension.
 //
-// Per CTA: 128 weight rows x BN activation rows (BN = 16..256), K walked in 64-wide blocks through
-// a ring of shared-memory stages:
-//   warp 0      TMA producer: one 2-D tiled load of the raw FP8 tile (128 x 64 bytes) and one of
-//               the activation tile (BN x 64 fp16, 128-byte swizzle) per stage, no multicast;
-//   warps 2..5  decode: 16 codes per thread per step by byte-permute/shift/mask bit moves to
-//               fp16, group-scale ratio folded in (FP32 multiply, one fp16 rounding -- exact for
-//               power-of-two scales), written in the 128-byte-swizzled K-major layout the MMA
-//               reads; fence.proxy.async, then an mbarrier arrive;
-//   warp 1      one thread issues tcgen05.mma (kind::f16, M=128, N=BN, K=16) four times per
-//               stage, accumulating in tensor memory, and tcgen05.commit frees the stage;
-//   warps 2..5  epilogue: tcgen05.ld the FP32 accumulators, apply smax[n], xs[m], bias[n], round
-//               once to the output type and store (32 lanes = 32 consecutive n per m).
-// No fp16 copy of the weights ever exists outside shared memory. Every mbarrier wait is bounded.
+// Persistent CTAs (one per SM) walk the list of 128 x BN output tiles; K flows in 64-wide blocks
+// through one ring of shared-memory stages that does not drain between tiles, and the FP32
+// accumulators are double-buffered in tensor memory so the epilogue of a tile overlaps the main
+// loop of the next one. Warp roles:
+//   warp 0       TMA producer: per stage one 2-D tiled load of the raw FP8 tile (128 x 64 bytes)
+//                and one of the activation tile (BN x 64 fp16, 128-byte swizzle); no multicast;
+//   warp 1       tensor-memory allocation; one thread issues tcgen05.mma (kind::f16, M = 128,
+//                N = BN, K = 16) four times per stage and tcgen05.commit's the stage free;
+//   warps 2..9   decode: 16 codes per thread per step to fp16 (two codes per conversion
+//                instruction), the K-group scale folded in as scale / rowmax (a packed fp16
+//                multiply when the ratio is a power of two, else an FP32 multiply with one fp16
+//                rounding), written in the 128-byte-swizzled K-major layout the MMA reads;
+//                fence.proxy.async, then an mbarrier arrive;
+//   warps 10..13 epilogue: tcgen05.ld the FP32 accumulators, apply smax[n], xs[m], bias[n], round
+//                once to the output type and store (32 lanes = 32 consecutive n per m).
+// No fp16 copy of the weights ever exists outside shared memory. Every mbarrier wait is bounded;
+// a wait that runs out sets a status bit, and the thread keeps walking its loops without waiting
+// so that every barrier is still met and the CTA ends.
 #include "common.cuh"
 
 namespace tfp8b {
 
-constexpr int GM_BM = 128;          // weight rows per CTA = UMMA M = TMEM lanes
+constexpr int GM_BM = 128;          // weight rows per tile = UMMA M = TMEM lanes
 constexpr int GM_BK = 64;           // K per stage: one 128-byte swizzle atom of fp16
-constexpr int GM_THREADS = 192;
+constexpr int GM_DEC_WARPS = 8;
+constexpr int GM_DEC_THREADS = GM_DEC_WARPS * 32;
+constexpr int GM_EPI_WARP0 = 2 + GM_DEC_WARPS;
+constexpr int GM_THREADS = (GM_EPI_WARP0 + 4) * 32;
 constexpr int GM_MAX_STAGES = 8;
-constexpr int GM_HEADER = 2048;     // barriers, TMEM base, per-row scale maxima
+constexpr int GM_HEADER = 2048;     // barriers, TMEM base, per-row scale reciprocals
 constexpr int GM_A_BYTES = GM_BM * GM_BK * 2;    // decoded fp16 tile
 constexpr int GM_RAW_BYTES = GM_BM * GM_BK;      // raw FP8 tile
 constexpr int GM_SMEM_MAX = 232448;              // 227 KB opt-in limit per CTA
@@ -38,18 +46,18 @@ struct GemmParams {
     const float* bias;
     void* y;
     int M, N, K, G, scale_kind, y_dt;
-    int BN, nstages, stage_bytes, tmem_cols;
+    int BN, nstages, stage_bytes, tmem_cols, m_tiles, ntiles;
 };
 
 struct GemmHeader {
     uint64_t full_raw[GM_MAX_STAGES];
     uint64_t full_a[GM_MAX_STAGES];
     uint64_t empty[GM_MAX_STAGES];
-    uint64_t acc_full;
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
     uint32_t tmem_base;
     uint32_t pad;
-    float smax[GM_BM];      // per weight row: max_g scale[n,g] (the scale itself for one group)
-    float binv[GM_BM];      // 1 / smax (0 when smax == 0)
+    float binv[2][GM_BM];   // per weight row: 1 / max_g scale[n,g], double-buffered by tile parity
 };
 static_assert(sizeof(GemmHeader) <= GM_HEADER, "header too large");
 
@@ -93,6 +101,13 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// max over one row's K-group scales, entries [g0, g1)
+__device__ __forceinline__ float row_scale_max(const void* scale, size_t row_off, int g0, int g1, int kind) {
+    float mx = 0.f;
+    for (int gi = g0; gi < g1; ++gi) mx = fmaxf(mx, load_scale(scale, row_off + gi, kind));
+    return mx;
+}
+
 // ------------------------------------------------------------------ the kernel
 template <int FMT>
 __global__ void __launch_bounds__(GM_THREADS, 1)
@@ -104,19 +119,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     uint8_t* stages = smem + GM_HEADER;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * p.BN;        // activation-row tile (fast grid dimension: CTAs that
-    const int n0 = blockIdx.y * GM_BM;       // run together share one weight stripe through L2)
     const int S = p.nstages;
     const int nkb = (p.K + GM_BK - 1) / GM_BK;
     const int x_bytes = p.BN * GM_BK * 2;
+    const int ng = p.K / p.G;
+    const int my_tiles = (p.ntiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+    // Tile i of this CTA is global tile blockIdx.x + i * gridDim.x; the activation-row tile is the
+    // fast index, so CTAs that run together share one weight stripe through L2.
+    auto tile_m0 = [&](int i) { return ((static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x)) % p.m_tiles) * p.BN; };
+    auto tile_n0 = [&](int i) { return ((static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x)) / p.m_tiles) * GM_BM; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(smem_u32(&hd->full_raw[s]), 1);
-            mbar_init(smem_u32(&hd->full_a[s]), 4);
+            mbar_init(smem_u32(&hd->full_a[s]), GM_DEC_WARPS);
             mbar_init(smem_u32(&hd->empty[s]), 1);
         }
-        mbar_init(smem_u32(&hd->acc_full), 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&hd->acc_full[b]), 1);
+            mbar_init(smem_u32(&hd->acc_empty[b]), 4);
+        }
         mbar_fence_init();
         fence_proxy_async_smem();
         tma_prefetch_desc(&tm_w);
@@ -129,23 +151,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_acc = hd->tmem_base;
+    const uint32_t tmem_base = hd->tmem_base;
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             // One activation tile only: the weight stripe is read once, keep it out of L2's way.
             // Several tiles: the CTAs of the other tiles read the same stripe from L2 next.
-            const uint64_t pol_w = gridDim.x == 1 ? l2_policy_evict_first() : l2_policy_evict_normal();
+            const uint64_t pol_w = p.m_tiles == 1 ? l2_policy_evict_first() : l2_policy_evict_normal();
             const uint64_t pol_x = l2_policy_evict_last();
-            for (int kb = 0; kb < nkb; ++kb) {
-                const int slot = kb % S;
-                if (kb >= S && !mbar_wait(smem_u32(&hd->empty[slot]), ((kb / S) - 1) & 1, STATUS_GEMM_WAIT)) break;
-                uint8_t* st = stages + static_cast<size_t>(slot) * p.stage_bytes;
-                const uint32_t bar = smem_u32(&hd->full_raw[slot]);
-                mbar_expect_tx(bar, static_cast<uint32_t>(GM_RAW_BYTES + x_bytes));
-                tma_load_2d(smem_u32(st + GM_A_BYTES), &tm_x, kb * GM_BK, m0, bar, pol_x);
-                tma_load_2d(smem_u32(st + GM_A_BYTES + x_bytes), &tm_w, kb * GM_BK, n0, bar, pol_w);
+            int it = 0;
+            bool ok = true;
+            for (int i = 0; i < my_tiles && ok; ++i) {
+                const int m0 = tile_m0(i), n0 = tile_n0(i);
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int slot = it % S;
+                    if (it >= S && !mbar_wait(smem_u32(&hd->empty[slot]), ((it / S) - 1) & 1, STATUS_GEMM_WAIT)) { ok = false; break; }
+                    uint8_t* st = stages + static_cast<size_t>(slot) * p.stage_bytes;
+                    const uint32_t bar = smem_u32(&hd->full_raw[slot]);
+                    mbar_expect_tx(bar, static_cast<uint32_t>(GM_RAW_BYTES + x_bytes));
+                    tma_load_2d(smem_u32(st + GM_A_BYTES), &tm_x, kb * GM_BK, m0, bar, pol_x);
+                    tma_load_2d(smem_u32(st + GM_A_BYTES + x_bytes), &tm_w, kb * GM_BK, n0, bar, pol_w);
+                }
             }
         }
         __syncwarp();
@@ -154,102 +181,127 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         if (lane == 0) {
             // D fp32, A/B fp16, both K-major, N = BN, M = 128
             const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(p.BN >> 3) << 17) | (static_cast<uint32_t>(GM_BM >> 4) << 24);
+            int it = 0;
             bool ok = true;
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int slot = kb % S;
-                const uint32_t par = (kb / S) & 1;
-                ok = mbar_wait(smem_u32(&hd->full_raw[slot]), par, STATUS_GEMM_WAIT) &&
-                     mbar_wait(smem_u32(&hd->full_a[slot]), par, STATUS_GEMM_WAIT);
+            for (int i = 0; i < my_tiles && ok; ++i) {
+                const int buf = i & 1;
+                // the accumulator buffer must have been drained by the epilogue of tile i - 2
+                if (i >= 2) ok = mbar_wait(smem_u32(&hd->acc_empty[buf]), ((i >> 1) - 1) & 1, STATUS_GEMM_WAIT);
                 if (!ok) break;
                 tc_fence_after();
-                uint8_t* st = stages + static_cast<size_t>(slot) * p.stage_bytes;
-                const uint64_t da = umma_desc_sw128(smem_u32(st));
-                const uint64_t db = umma_desc_sw128(smem_u32(st + GM_A_BYTES));
+                const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(buf * p.BN);
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int slot = it % S;
+                    const uint32_t par = (it / S) & 1;
+                    ok = mbar_wait(smem_u32(&hd->full_raw[slot]), par, STATUS_GEMM_WAIT) &&
+                         mbar_wait(smem_u32(&hd->full_a[slot]), par, STATUS_GEMM_WAIT);
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint8_t* st = stages + static_cast<size_t>(slot) * p.stage_bytes;
+                    const uint64_t da = umma_desc_sw128(smem_u32(st));
+                    const uint64_t db = umma_desc_sw128(smem_u32(st + GM_A_BYTES));
 #pragma unroll
-                for (int kk = 0; kk < GM_BK / 16; ++kk)
-                    tc_mma_f16(tmem_acc, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
-                tc_commit(smem_u32(&hd->empty[slot]));
+                    for (int kk = 0; kk < GM_BK / 16; ++kk)
+                        tc_mma_f16(tmem_acc, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                    tc_commit(smem_u32(&hd->empty[slot]));
+                }
+                if (ok) tc_commit(smem_u32(&hd->acc_full[buf]));
             }
-            if (ok) tc_commit(smem_u32(&hd->acc_full));
         }
         __syncwarp();
-    } else {
-        // ---------------------------------------------------------------- decode warps, then epilogue
-        const int td = threadIdx.x - 64;             // 0..127
-        const int ng = p.K / p.G;
-        {   // per-row scale maximum for TMEM lane td (row n0 + td)
-            const int n = min(n0 + td, p.N - 1);
-            float mx = 0.f;
-            if (ng == 1) {
-                mx = load_scale(p.scale, n, p.scale_kind);
-            } else {
-                for (int gi = 0; gi < ng; ++gi) mx = fmaxf(mx, load_scale(p.scale, static_cast<size_t>(n) * ng + gi, p.scale_kind));
-            }
-            hd->smax[td] = mx;
-            hd->binv[td] = mx > 0.f ? 1.f / mx : 0.f;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-
+    } else if (warp < GM_EPI_WARP0) {
+        // ---------------------------------------------------------------- decode warps
+        const int td = threadIdx.x - 64;             // 0..255
         const int c = td & 3;                        // 16-code chunk of the 64-wide K block
-        int rows[4];
-        size_t srow[4];
-        float binv[4];
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-            rows[it] = (td >> 2) + 32 * it;
-            srow[it] = static_cast<size_t>(min(n0 + rows[it], p.N - 1)) * ng;
-            binv[it] = hd->binv[rows[it]];
-        }
+        const int r0 = td >> 2;                      // rows r0 and r0 + 64
+        int it = 0;
         bool ok = true;
-        for (int kb = 0; kb < nkb; ++kb) {
-            const int slot = kb % S;
-            float ratio[4] = {1.f, 1.f, 1.f, 1.f};
+        for (int i = 0; i < my_tiles; ++i) {
+            const int n0 = tile_n0(i);
+            float binv[2] = {1.f, 1.f};
+            size_t srow[2];
+            srow[0] = static_cast<size_t>(min(n0 + r0, p.N - 1)) * ng;
+            srow[1] = static_cast<size_t>(min(n0 + r0 + 64, p.N - 1)) * ng;
             if (ng > 1) {
-                const int gi = min((kb * GM_BK + c * 16) / p.G, ng - 1);
-#pragma unroll
-                for (int it = 0; it < 4; ++it) ratio[it] = load_scale(p.scale, srow[it] + gi, p.scale_kind) * binv[it];
+                // row maxima of the K-group scales: thread pair (2r, 2r+1) scans row r in halves
+                const int row = td >> 1, half = td & 1;
+                const size_t off = static_cast<size_t>(min(n0 + row, p.N - 1)) * ng;
+                const int mid = ng >> 1;
+                float mx = row_scale_max(p.scale, off, half ? mid : 0, half ? ng : mid, p.scale_kind);
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                if (!half) hd->binv[i & 1][row] = mx > 0.f ? 1.f / mx : 0.f;
+                named_barrier_sync(1, GM_DEC_THREADS);
+                binv[0] = hd->binv[i & 1][r0];
+                binv[1] = hd->binv[i & 1][r0 + 64];
             }
-            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->full_raw[slot]), (kb / S) & 1, STATUS_GEMM_WAIT));
-            if (!ok) break;
-            uint8_t* st = stages + static_cast<size_t>(slot) * p.stage_bytes;
-            const uint8_t* raw = st + GM_A_BYTES + x_bytes;
-#pragma unroll
-            for (int it = 0; it < 4; ++it) {
-                const int r = rows[it];
-                const uint4 q = *reinterpret_cast<const uint4*>(raw + r * GM_BK + c * 16);
-                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-                uint32_t h[8];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) dec4<FMT, false>(w[j], h[2 * j], h[2 * j + 1]);
-                if (ratio[it] != 1.f) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float2 f = __half22float2(*reinterpret_cast<__half2*>(&h[j]));
-                        __half2 o = __floats2half2_rn(f.x * ratio[it], f.y * ratio[it]);
-                        h[j] = *reinterpret_cast<uint32_t*>(&o);
-                    }
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int slot = it % S;
+                float ratio[2] = {1.f, 1.f};
+                if (ng > 1) {
+                    const int gi = min((kb * GM_BK + c * 16) / p.G, ng - 1);
+                    ratio[0] = load_scale(p.scale, srow[0] + gi, p.scale_kind) * binv[0];
+                    ratio[1] = load_scale(p.scale, srow[1] + gi, p.scale_kind) * binv[1];
                 }
-                uint8_t* arow = st + r * 128;
-                *reinterpret_cast<uint4*>(arow + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-                *reinterpret_cast<uint4*>(arow + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->full_raw[slot]), (it / S) & 1, STATUS_GEMM_WAIT));
+                if (!ok) continue;
+                uint8_t* st = stages + static_cast<size_t>(slot) * p.stage_bytes;
+                const uint8_t* raw = st + GM_A_BYTES + x_bytes;
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    const int r = r0 + 64 * h2;
+                    const uint4 q = *reinterpret_cast<const uint4*>(raw + r * GM_BK + c * 16);
+                    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                    uint32_t h[8];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) dec4<FMT, false>(w[j], h[2 * j], h[2 * j + 1]);
+                    const float rt = ratio[h2];
+                    if (rt != 1.f) {
+                        const uint32_t rb = __float_as_uint(rt);
+                        if ((rb & 0x007FFFFFu) == 0u && rb >= 0x38800000u && rb <= 0x47000000u) {
+                            // power of two inside fp16's normal range: one packed multiply, same rounding
+                            const __half2 r2 = __float2half2_rn(rt);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                __half2 o = __hmul2(*reinterpret_cast<__half2*>(&h[j]), r2);
+                                h[j] = *reinterpret_cast<uint32_t*>(&o);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                float2 f = __half22float2(*reinterpret_cast<__half2*>(&h[j]));
+                                __half2 o = __floats2half2_rn(f.x * rt, f.y * rt);
+                                h[j] = *reinterpret_cast<uint32_t*>(&o);
+                            }
+                        }
+                    }
+                    uint8_t* arow = st + r * 128;
+                    *reinterpret_cast<uint4*>(arow + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(arow + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+                }
+                fence_proxy_async_smem();        // generic-proxy stores -> visible to the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&hd->full_a[slot]));
             }
-            fence_proxy_async_smem();        // generic-proxy stores -> visible to the tensor core
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&hd->full_a[slot]));
         }
-
-        // ---------------------------------------------------------------- epilogue
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->acc_full), 0, STATUS_GEMM_WAIT));
-        if (ok) {
-            tc_fence_after();
-            const int quarter = warp & 3;                       // TMEM lanes this warp may read
-            const int row = quarter * 32 + lane;
+    } else {
+        // ---------------------------------------------------------------- epilogue warps
+        const int quarter = warp & 3;                           // TMEM lanes this warp may read
+        const int row = quarter * 32 + lane;
+        bool ok = true;
+        for (int i = 0; i < my_tiles; ++i) {
+            const int buf = i & 1;
+            const int m0 = tile_m0(i), n0 = tile_n0(i);
             const int n = n0 + row;
-            const float sm = hd->smax[row];
+            const size_t off = static_cast<size_t>(min(n, p.N - 1)) * ng;
+            const float sm = ng == 1 ? load_scale(p.scale, off, p.scale_kind) : row_scale_max(p.scale, off, 0, ng, p.scale_kind);
             const float b = (p.bias && n < p.N) ? p.bias[n] : 0.f;
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->acc_full[buf]), (i >> 1) & 1, STATUS_GEMM_WAIT));
+            if (!ok) continue;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * p.BN);
             for (int col = 0; col < p.BN; col += 16) {
                 uint32_t v[16];
-                tmem_ld16(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + col, v);
+                tmem_ld16(taddr + col, v);
                 tmem_ld_wait();
                 if (n < p.N) {
 #pragma unroll
@@ -260,51 +312,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     }
                 }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&hd->acc_empty[buf]));
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_acc, static_cast<uint32_t>(p.tmem_cols));
+        tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
     }
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
-
 static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t inner,
                        uint64_t outer, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return TFP8B_ERR_CUDA; }
-    cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {inner * static_cast<uint64_t>(elem_bytes)};
-    cuuint32_t box[2] = {box_inner, box_outer};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r)); return TFP8B_ERR_CUDA; }
-    return TFP8B_OK;
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {inner * static_cast<uint64_t>(elem_bytes)};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    return encode_tensor_map(map, dt, 2, base, dims, strides, box, swz);
 }
 
 template <int FMT>
 static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, size_t smem, cudaStream_t st) {
     static unsigned long long configured = 0ull;
-    int dev = 0;
+    int dev = 0, sms = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (dev >= 64 || !((configured >> dev) & 1ull)) {
@@ -312,7 +345,8 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmP
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm)");
         if (dev < 64) __atomic_fetch_or(&configured, 1ull << dev, __ATOMIC_RELAXED);
     }
-    dim3 grid((p.M + p.BN - 1) / p.BN, (p.N + GM_BM - 1) / GM_BM);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    const int grid = p.ntiles < sms ? p.ntiles : sms;
     gemm_kernel<FMT><<<grid, GM_THREADS, smem, st>>>(tw, tx, p);
     TFP8B_LAUNCH_CHECK("tfp8b_gemm");
     return TFP8B_OK;
@@ -349,12 +383,12 @@ extern "C" int tfp8b_gemm(const void* x16, const float* xs, const uint8_t* codes
     int bn = 16;
     while (bn < M && bn < 256) bn <<= 1;
     p.BN = bn;
-    p.tmem_cols = bn < 32 ? 32 : bn;
+    p.tmem_cols = 2 * bn < 32 ? 32 : 2 * bn;                 // two accumulator buffers
+    p.m_tiles = (M + bn - 1) / bn;
+    p.ntiles = p.m_tiles * ((N + GM_BM - 1) / GM_BM);
     p.stage_bytes = GM_A_BYTES + bn * GM_BK * 2 + GM_RAW_BYTES;
-    const int nkb = (K + GM_BK - 1) / GM_BK;
     int S = (GM_SMEM_MAX - 1024 - GM_HEADER) / p.stage_bytes;
     S = S > GM_MAX_STAGES ? GM_MAX_STAGES : S;
-    if (S > nkb) S = nkb;
     p.nstages = S;
     const size_t smem = 1024 + GM_HEADER + static_cast<size_t>(S) * p.stage_bytes;
 

@@ -2,38 +2,54 @@
 //
 //   y[m,n] = sum_g scale[n,g] * sum_{k in g} x[m,k] * dec(codes[n,k]) + bias[n]
 //
-// The weight stream is the whole cost (N*K bytes against M*K + M*N elements of activations), so
-// the kernel is built around keeping HBM busy:
-//   * one CTA owns 16 consecutive weight rows and walks K in stages of 1024 codes;
-//   * a producer warp moves each stage with 1-D bulk async copies (cp.async.bulk, 16 row copies
-//     + M activation-row copies) into a ring of shared-memory stages, completion counted on an
-//     mbarrier -- no registers are held for data in flight, and every byte of a row is requested
-//     in large contiguous pieces with an evict-first L2 policy;
-//   * eight consumer warps each take a 128-code slice of the stage: 128-bit shared loads, four
-//     codes of a 32-bit word decoded with byte-permute / shift / mask bit moves to packed
-//     f16x2 (or bf16x2), and the products are taken on the tensor cores with
-//     mma.sync.m16n8k16 (16 weight rows x 8 activation rows, FP32 accumulate). At M = 8 the FP32
-//     FMA pipe could not keep up with the byte rate of HBM3e; the MMA makes M irrelevant.
-//   * x is consumed in its own type: f16 -> f16 MMA, bf16 -> bf16 MMA against bf16-decoded
-//     weights (every FP8 value is exact in both), f32 -> split into three bf16 terms (24
-//     mantissa bits) and three MMAs, so nothing is rounded before the FP32 accumulation.
-//   * per-K-group scales are applied in FP32 to the partial sum of each group (exact for any
-//     scale value), per-channel scales once at the end.
-//   * the eight partial sums are added in a fixed order through shared memory: results are
-//     deterministic and identical from call to call.
+// The weight stream is the whole cost (N*K bytes against M*(K+N) activation elements), so the
+// kernel is built around keeping HBM busy from its first to its last microsecond:
+//   * persistent CTAs, one per SM, each walking a list of 16-row weight tiles; K is cut into
+//     stages of 1024 codes that flow through one ring of shared-memory stages which does not
+//     drain between tiles;
+//   * a producer warp moves each stage with 1-D bulk async copies (cp.async.bulk: 16 row pieces of
+//     1 KB, evict-first in L2), completion counted in bytes on an mbarrier -- no registers are
+//     held for data in flight and about 90 KB per SM is always on its way;
+//   * the activations are copied into shared memory once per CTA when they fit (always for
+//     M = 1), otherwise piecewise with each stage;
+//   * eight consumer warps each take a 128-code slice of a stage: 128-bit shared loads, two
+//     codes per conversion instruction (see dec2_f16), products on the tensor cores with
+//     mma.sync.m16n8k16 (16 weight rows x 8 activation rows, FP32 accumulate): at M = 8 the
+//     FP32 FMA pipe could not keep up with HBM3e's byte rate, the MMA makes M irrelevant;
+//   * x is consumed in its own type: f16 -> f16 MMA; bf16 -> bf16 MMA against weights decoded
+//     to bf16 (every FP8 value is exact in both); f32 -> three bf16 terms (24 mantissa bits) and
+//     three MMAs. Nothing is rounded before the FP32 accumulation;
+//   * per-K-group scales multiply each group's partial sum in FP32 (exact for any scale value),
+//     per-channel scales once at the end; the eight partial sums of a tile are added in a fixed
+//     order, so results are deterministic;
+//   * programmatic dependent launch: the kernel releases its successor at once and only waits
+//     for its predecessor before it touches activations or outputs, so in a chain of layers the
+//     next layer's weights are already streaming while this one finishes. Weights are never
+//     written by a kernel that releases its successor early, so prefetching them is safe.
 // All mbarrier waits are bounded; a wait that runs out sets a status bit and ends the CTA.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace tfp8b {
 
-constexpr int GV_ROWS = 16;                      // weight rows per CTA (the MMA's M)
+constexpr int GV_ROWS = 16;                      // weight rows per tile (the MMA's M)
 constexpr int GV_WARPS = 8;                      // consumer warps
-constexpr int GV_THREADS = (GV_WARPS + 1) * 32;  // + one producer warp
-constexpr int GV_KS = 1024;                      // codes of K per stage
+constexpr int GV_CONSUMERS = GV_WARPS * 32;
+constexpr int GV_THREADS = GV_CONSUMERS + 32;    // + one producer warp
+#ifndef TFP8B_GV_KS
+#define TFP8B_GV_KS 1024
+#endif
+#ifndef TFP8B_GV_SMEM_KB
+#define TFP8B_GV_SMEM_KB 104
+#endif
+constexpr int GV_KS = TFP8B_GV_KS;               // codes of K per stage
 constexpr int GV_WK = GV_KS / GV_WARPS;          // codes of K per warp per stage
-constexpr int GV_MAX_STAGES = 8;
-constexpr int GV_HEADER = 128 + GV_WARPS * GV_ROWS * 8 * 4;   // barriers + reduction buffer
-constexpr int GV_SMEM_TARGET = 74 * 1024;        // per CTA, so that three CTAs share an SM
+constexpr int GV_MAX_STAGES = 14;
+constexpr int GV_RED = GV_WARPS * GV_ROWS * 8 * 4;            // one reduction buffer
+constexpr int GV_HEADER = 9 * 1024;                           // 256 B of barriers + two reduction buffers, padded to 1 KB
+constexpr int GV_SMEM_TARGET = TFP8B_GV_SMEM_KB * 1024;       // per CTA: two CTAs (this kernel + its successor) share an SM
+constexpr int GV_XRES_MAX = 40 * 1024;           // activations up to this size stay resident per CTA
 
 struct GemvParams {
     const void* x;
@@ -42,7 +58,8 @@ struct GemvParams {
     const float* bias;
     void* y;
     int M, N, K, G, scale_kind, y_dt;
-    int nstages, wpitch, xpitch, stage_bytes;
+    int nstages, wpitch, xpitch, wstage_bytes, stage_bytes, x_resident, xres_bytes, ntiles, pdl;
+    int xres_issues, xres_box_bytes, xres_box_kb;     // resident activations by tensor map: loads, bytes and k-blocks per load
 };
 
 __device__ __forceinline__ void mma16816_f16(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -67,7 +84,9 @@ __device__ __forceinline__ float bf16_lo(uint32_t p) { return __uint_as_float(p 
 __device__ __forceinline__ float bf16_hi(uint32_t p) { return __uint_as_float(p & 0xFFFF0000u); }
 
 // One MMA step: four codes of weight row g (word wa) and of row g+8 (word wb) against four
-// activations of row m. xq points at this lane's activations for the step.
+// activations of row m. The K positions inside an MMA are permuted the same way on both operands
+// (lane tig owns 16 consecutive k), which leaves the dot product unchanged and lets every lane
+// load whole 16-byte pieces.
 //   f16 / bf16 x: xq[0] = {x0,x1}, xq[1] = {x2,x3} as stored.
 //   f32 x       : xq[0..3] = x0..x3 as float bits, split into three bf16 terms.
 template <typename XT, int FMT>
@@ -92,192 +111,348 @@ __device__ __forceinline__ void mma_step(float c[4], uint32_t wa, uint32_t wb, c
     }
 }
 
-// A 64-code block of the stage: lane (g, tig) takes the 16 codes at k = kofs + 16*tig of rows g
-// and g+8 and the matching 16 activations of row m. MASK: the block is only half inside K (K is a
-// multiple of 32), lanes with tig >= 2 contribute zeros.
+// The MMA steps of a block go to separate accumulators c[0..3], so that no mma.sync waits for the
+// one before it.
+//
+// Where a lane finds its operands in shared memory: two weight pieces (rows R and R+8 of the
+// tile) and up to four 16-byte pieces of its activation slice.
+struct BlockAddr {
+    const uint8_t* wa;
+    const uint8_t* wb;
+    const uint8_t* xc[4];
+};
+
+// A 64-code block of the stage: lane (g, tig) takes the 16 codes at k = kofs + 16*tig of rows R
+// and R+8 and the matching 16 activations of row m. MASK (bulk-copy layout only): the block is only
+// half inside K (K is a multiple of 32), lanes with tig >= 2 contribute zeros.
 template <typename XT, int FMT, bool MASK>
-__device__ __forceinline__ void block64(float c[4], const uint8_t* wst, const uint8_t* xst, int wpitch, int xpitch,
-                                        int g, int tig, int mrow, int kofs, int klen) {
-    const int ko = kofs + tig * 16;
-    uint4 wa = *reinterpret_cast<const uint4*>(wst + g * wpitch + ko);
-    uint4 wb = *reinterpret_cast<const uint4*>(wst + (g + 8) * wpitch + ko);
+__device__ __forceinline__ void block64(float (*c)[4], const BlockAddr& a, bool live) {
+    uint4 wa = *reinterpret_cast<const uint4*>(a.wa);
+    uint4 wb = *reinterpret_cast<const uint4*>(a.wb);
     constexpr int XW = sizeof(XT) == 4 ? 16 : 8;           // 32-bit words of x per lane per block
     uint32_t xr[XW];
-    const uint4* xp = reinterpret_cast<const uint4*>(xst + mrow * xpitch + ko * static_cast<int>(sizeof(XT)));
 #pragma unroll
     for (int i = 0; i < XW / 4; ++i) {
-        uint4 v = xp[i];
+        uint4 v = *reinterpret_cast<const uint4*>(a.xc[i]);
         xr[4 * i] = v.x; xr[4 * i + 1] = v.y; xr[4 * i + 2] = v.z; xr[4 * i + 3] = v.w;
     }
-    if (MASK && ko >= klen) {
+    if (MASK && !live) {
         wa = make_uint4(0, 0, 0, 0); wb = make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int i = 0; i < XW; ++i) xr[i] = 0u;
     }
     const uint32_t was[4] = {wa.x, wa.y, wa.z, wa.w}, wbs[4] = {wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) mma_step<XT, FMT>(c, was[j], wbs[j], &xr[j * (XW / 4)]);
+    for (int j = 0; j < 4; ++j) mma_step<XT, FMT>(c[j], was[j], wbs[j], &xr[j * (XW / 4)]);
 }
 
 // A 32-code block (32-wide scale groups): lane (g, tig) takes 8 codes at k = kofs + 8*tig.
 template <typename XT, int FMT>
-__device__ __forceinline__ void block32(float c[4], const uint8_t* wst, const uint8_t* xst, int wpitch, int xpitch,
-                                        int g, int tig, int mrow, int kofs) {
-    const int ko = kofs + tig * 8;
-    uint2 wa = *reinterpret_cast<const uint2*>(wst + g * wpitch + ko);
-    uint2 wb = *reinterpret_cast<const uint2*>(wst + (g + 8) * wpitch + ko);
+__device__ __forceinline__ void block32(float (*c)[4], const BlockAddr& a) {
+    uint2 wa = *reinterpret_cast<const uint2*>(a.wa);
+    uint2 wb = *reinterpret_cast<const uint2*>(a.wb);
     constexpr int XW = sizeof(XT) == 4 ? 8 : 4;
     uint32_t xr[XW];
-    const uint4* xp = reinterpret_cast<const uint4*>(xst + mrow * xpitch + ko * static_cast<int>(sizeof(XT)));
 #pragma unroll
     for (int i = 0; i < XW / 4; ++i) {
-        uint4 v = xp[i];
+        uint4 v = *reinterpret_cast<const uint4*>(a.xc[i]);
         xr[4 * i] = v.x; xr[4 * i + 1] = v.y; xr[4 * i + 2] = v.z; xr[4 * i + 3] = v.w;
     }
-    mma_step<XT, FMT>(c, wa.x, wb.x, &xr[0]);
-    mma_step<XT, FMT>(c, wa.y, wb.y, &xr[XW / 2]);
+    mma_step<XT, FMT>(c[0], wa.x, wb.x, &xr[0]);
+    mma_step<XT, FMT>(c[1], wa.y, wb.y, &xr[XW / 2]);
 }
 
+// Which weight row of the 16-row tile sits in MMA row g (0..7; MMA row g+8 holds that row + 8).
+// With the tensor-map layout the rows of a tile are 128 bytes apart and the 16-byte pieces of a
+// row are XOR-swizzled with (row & 7): the permutation puts rows that differ in the right bit
+// into the lanes that load together, which makes the loads bank-conflict free (128-bit loads go
+// by quarter warps = MMA rows {2q, 2q+1}; 64-bit loads by half warps = MMA rows {4h..4h+3}).
+// Any permutation is legal: it only decides which output row a lane's accumulator belongs to.
+template <int SMODE, bool TMA>
+__device__ __forceinline__ int tile_row_of(int g) {
+    if (!TMA) return g;
+    return SMODE == 2 ? 2 * (g & 3) + (g >> 2) : (g >> 1) + 4 * (g & 1);
+}
+
+// Shared-memory map:  [0,256) mbarriers: full[0..13], empty[14..27], xfull[28]
+//                     [256, 256 + 2*GV_RED) two reduction buffers [warp][row][m]
+//                     (1024-byte aligned) resident activations, then the ring of stages.
+// Two data layouts:
+//   TMA   (K % 128 == 0) one 3-D tensor-map load per stage brings 16 rows x 1024 codes as
+//         [8 k-blocks][16 rows][128 B] with the 128-byte swizzle; activations likewise as
+//         [k-blocks][M rows][128 B]. One instruction per 16 KB: issuing one bulk copy per 1 KB row
+//         piece, as the other layout does, capped a CTA at about 20 GB/s.
+//   bulk  (any K % 32 == 0) 16 row pieces of up to 1 KB by cp.async.bulk, row pitch padded for
+//         conflict-free loads; used for the K that the tensor map cannot describe.
+//
 // SMODE 0: one scale per output channel (applied once, at the end)
 //       1: K-groups that are multiples of 64 (applied per 64-code block)
 //       2: K-groups that are multiples of 32 only (32-code blocks)
-template <typename XT, int FMT, int SMODE>
-__global__ void __launch_bounds__(GV_THREADS) gemv_kernel(const GemvParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);               // full[0..7], empty[8..15]
-    float* red = reinterpret_cast<float*>(smem + 128);                // [warp][row][m]
-    uint8_t* stages = smem + GV_HEADER;
+template <typename XT, int FMT, int SMODE, bool TMA>
+__global__ void __launch_bounds__(GV_THREADS)
+gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemvParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+    float* red = reinterpret_cast<float*>(smem + 256);
+    uint8_t* xres = smem + GV_HEADER;
+    uint8_t* stages = xres + p.xres_bytes;
+    const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[GV_MAX_STAGES]);
+    const uint32_t bar_x = smem_u32(&bars[2 * GV_MAX_STAGES]);
+    constexpr int SZ = static_cast<int>(sizeof(XT));
+    constexpr int EPB = 128 / SZ;                    // activations per 128-byte k-block (TMA layout)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * GV_ROWS;
     const int S = p.nstages;
     const int nchunks = (p.K + GV_KS - 1) / GV_KS;
+    const int my_tiles = (p.ntiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+    const int total = my_tiles * nchunks;            // stages this CTA moves in all
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
-            mbar_init(smem_u32(&bars[s]), 1);
-            mbar_init(smem_u32(&bars[GV_MAX_STAGES + s]), GV_WARPS);
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, GV_WARPS);
         }
+        mbar_init(bar_x, 1);
         mbar_fence_init();
         fence_proxy_async_smem();
+        if (TMA) { tma_prefetch_desc(&tm_w); tma_prefetch_desc(&tm_x); }
     }
     __syncthreads();
-
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (p.pdl) pdl_launch_dependents();
 
     if (warp == GV_WARPS) {
         // ---------------------------------------------------------------- producer warp
         const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
-        const int row = min(n0 + (lane & 15), p.N - 1);                // N tail: re-read the last row
-        const uint8_t* wsrc = p.w + static_cast<size_t>(row) * p.K;
         const int xm = lane - 16;
-        const uint8_t* xsrc = reinterpret_cast<const uint8_t*>(p.x) + static_cast<size_t>(max(xm, 0)) * p.K * sizeof(XT);
-        for (int c = 0; c < nchunks; ++c) {
-            const int slot = c % S;
-            if (c >= S && !mbar_wait(smem_u32(&bars[GV_MAX_STAGES + slot]), ((c / S) - 1) & 1, STATUS_GEMV_WAIT)) break;
+        const uint8_t* xrow = reinterpret_cast<const uint8_t*>(p.x) + static_cast<size_t>(max(xm, 0)) * p.K * SZ;
+        // bytes of activations that travel with a stage, per code of K (bulk) or per stage (TMA)
+        const uint32_t x_per_k = p.x_resident ? 0u : static_cast<uint32_t>(p.M * SZ);
+
+        auto issue_w = [&](int item) {
+            const int t = item / nchunks, c = item - t * nchunks;
+            const int n0 = (static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x)) * GV_ROWS;
             const int k0 = c * GV_KS, klen = min(GV_KS, p.K - k0);
-            const uint32_t full = smem_u32(&bars[slot]);
+            const int slot = item % S;
             uint8_t* wst = stages + static_cast<size_t>(slot) * p.stage_bytes;
-            uint8_t* xst = wst + GV_ROWS * p.wpitch;
-            if (lane == 0) mbar_expect_tx(full, static_cast<uint32_t>(GV_ROWS * klen + p.M * klen * static_cast<int>(sizeof(XT))));
-            __syncwarp();
-            if (lane < 16) bulk_g2s(smem_u32(wst + lane * p.wpitch), wsrc + k0, klen, full, pol_w);
-            else if (xm < p.M) bulk_g2s(smem_u32(xst + xm * p.xpitch), xsrc + static_cast<size_t>(k0) * sizeof(XT),
-                                        klen * static_cast<int>(sizeof(XT)), full, pol_x);
+            if (TMA) {
+                if (lane == 0) {
+                    mbar_expect_tx(bar_full + 8 * slot, static_cast<uint32_t>(GV_KS) * (GV_ROWS + x_per_k));
+                    tma_load_3d(smem_u32(wst), &tm_w, 0, n0, k0 >> 7, bar_full + 8 * slot, pol_w);
+                }
+            } else {
+                if (lane == 0) mbar_expect_tx(bar_full + 8 * slot, static_cast<uint32_t>(klen) * (GV_ROWS + x_per_k));
+                __syncwarp();
+                if (lane < GV_ROWS) {
+                    const int row = min(n0 + lane, p.N - 1);             // N tail: re-read the last row
+                    bulk_g2s(smem_u32(wst + lane * p.wpitch), p.w + static_cast<size_t>(row) * p.K + k0, klen,
+                             bar_full + 8 * slot, pol_w);
+                }
+            }
+        };
+        auto issue_x = [&](int item) {                                   // activations that travel with the stage
+            const int c = item % nchunks;
+            const int k0 = c * GV_KS, klen = min(GV_KS, p.K - k0);
+            const int slot = item % S;
+            uint8_t* xst = stages + static_cast<size_t>(slot) * p.stage_bytes + p.wstage_bytes;
+            if (TMA) {
+                if (lane == 0) tma_load_3d(smem_u32(xst), &tm_x, 0, 0, k0 / EPB, bar_full + 8 * slot, pol_x);
+            } else if (xm >= 0 && xm < p.M) {
+                bulk_g2s(smem_u32(xst + xm * p.xpitch), xrow + static_cast<size_t>(k0) * SZ, klen * SZ, bar_full + 8 * slot, pol_x);
+            }
+        };
+
+        const int pre = min(S, total);
+        for (int i = 0; i < pre; ++i) issue_w(i);        // weights first: they never depend on the predecessor
+        if (p.pdl) pdl_wait();                           // activations may be the predecessor's output
+        if (p.x_resident) {
+            if (TMA) {
+                if (lane == 0) {
+                    mbar_expect_tx(bar_x, static_cast<uint32_t>(p.xres_issues * p.xres_box_bytes));
+                    for (int j = 0; j < p.xres_issues; ++j)
+                        tma_load_3d(smem_u32(xres + static_cast<size_t>(j) * p.xres_box_bytes), &tm_x, 0, 0, j * p.xres_box_kb, bar_x, pol_x);
+                }
+            } else {
+                if (lane == 0) mbar_expect_tx(bar_x, static_cast<uint32_t>(p.M * p.K * SZ));
+                __syncwarp();
+                if (xm >= 0 && xm < p.M) {
+                    // one row can exceed what a single bulk copy should carry: cut it at 16 KB
+                    for (int off = 0; off < p.K * SZ; off += 16384)
+                        bulk_g2s(smem_u32(xres + xm * p.xpitch + off), xrow + off, min(16384, p.K * SZ - off), bar_x, pol_x);
+                }
+            }
+        } else {
+            for (int i = 0; i < pre; ++i) issue_x(i);
+        }
+        for (int i = pre; i < total; ++i) {
+            if (!mbar_wait(bar_empty + 8 * (i % S), ((i / S) - 1) & 1, STATUS_GEMV_WAIT)) break;
+            issue_w(i);
+            if (!p.x_resident) issue_x(i);
         }
     } else {
         // ---------------------------------------------------------------- consumer warps
         const int g = lane >> 2, tig = lane & 3;
+        const int R = tile_row_of<SMODE, TMA>(g);        // tile rows R and R + 8 live in this lane's MMA rows
         const int mrow = min(g, p.M - 1);
         const int ng = p.K / p.G;
-        const size_t srow_a = static_cast<size_t>(min(n0 + g, p.N - 1)) * ng;
-        const size_t srow_b = static_cast<size_t>(min(n0 + g + 8, p.N - 1)) * ng;
         constexpr int BLK = SMODE == 2 ? 32 : 64;
         constexpr int NB = GV_WK / BLK;
+        constexpr int XCH = BLK * SZ / 64;               // 16-byte pieces of x per lane per block
         const int kw = warp * GV_WK;
-        for (int c = 0; c < nchunks; ++c) {
-            const int slot = c % S;
-            const int k0 = c * GV_KS, klen = min(GV_KS, p.K - k0);
-            float sa[NB], sb[NB];
-            if (SMODE != 0) {
+        bool ok = true;
+        if (p.x_resident) ok = mbar_wait(bar_x, 0, STATUS_GEMV_WAIT);
+        if (p.pdl) pdl_wait();                           // before the first store to y
+        int item = 0;
+        // A wait that runs out clears `ok`; the warp then stops waiting and computing but keeps
+        // walking the loop, so it still meets the others at every barrier and the CTA ends.
+        for (int t = 0; t < my_tiles; ++t) {
+            const int n0 = (static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x)) * GV_ROWS;
+            const size_t srow_a = static_cast<size_t>(min(n0 + R, p.N - 1)) * ng;
+            const size_t srow_b = static_cast<size_t>(min(n0 + R + 8, p.N - 1)) * ng;
+            // SMODE 0 accumulates straight into eight independent MMA accumulators (block parity x
+            // step); the grouped modes sum each block's four partials and apply the group scale.
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            float cc[8][4];
+#pragma unroll
+            for (int a = 0; a < 8; ++a) cc[a][0] = cc[a][1] = cc[a][2] = cc[a][3] = 0.f;
+            for (int c = 0; c < nchunks; ++c, ++item) {
+                const int slot = item % S;
+                const int k0 = c * GV_KS, klen = min(GV_KS, p.K - k0);
+                float sa[NB], sb[NB];
+                if (SMODE != 0) {
+#pragma unroll
+                    for (int b = 0; b < NB; ++b) {
+                        sa[b] = sb[b] = 0.f;
+                        if (kw + b * BLK < klen) {
+                            const int gi = (k0 + kw + b * BLK) / p.G;
+                            sa[b] = load_scale(p.scale, srow_a + gi, p.scale_kind);
+                            sb[b] = load_scale(p.scale, srow_b + gi, p.scale_kind);
+                        }
+                    }
+                }
+                if (ok) ok = mbar_wait(bar_full + 8 * slot, (item / S) & 1, STATUS_GEMV_WAIT);
+                if (!ok) continue;
+                const uint8_t* wst = stages + static_cast<size_t>(slot) * p.stage_bytes;
+                // activations: resident tile indexed by global k, or this stage's piece by local k
+                const uint8_t* xbase = p.x_resident ? xres : wst + p.wstage_bytes;
+                const int xk0 = p.x_resident ? k0 : 0;
 #pragma unroll
                 for (int b = 0; b < NB; ++b) {
-                    sa[b] = sb[b] = 0.f;
-                    if (kw + b * BLK < klen) {
-                        const int gi = (k0 + kw + b * BLK) / p.G;
-                        sa[b] = load_scale(p.scale, srow_a + gi, p.scale_kind);
-                        sb[b] = load_scale(p.scale, srow_b + gi, p.scale_kind);
+                    const int kofs = kw + b * BLK;
+                    if (kofs < klen) {
+                        const int kk = kofs + tig * (BLK / 4);           // this lane's first code within the stage
+                        BlockAddr a;
+                        if (TMA) {
+                            const int wo = (kk >> 7) * 2048 + R * 128 + ((((kk >> 4) & 7) ^ R) << 4) + (kk & 8);
+                            a.wa = wst + wo;
+                            a.wb = a.wa + 1024;                          // row R + 8: same swizzle phase
+                            const int xk = xk0 + kk;
+                            const int xoff = ((xk / EPB) * p.M + mrow) * 128;
+                            const int c0 = ((xk % EPB) * SZ) >> 4, ph = (xoff >> 7) & 7;
+#pragma unroll
+                            for (int i = 0; i < XCH; ++i) a.xc[i] = xbase + xoff + (((c0 + i) ^ ph) << 4);
+                        } else {
+                            a.wa = wst + R * p.wpitch + kk;
+                            a.wb = a.wa + 8 * p.wpitch;
+                            const uint8_t* xp = xbase + mrow * p.xpitch + (xk0 + kk) * SZ;
+#pragma unroll
+                            for (int i = 0; i < XCH; ++i) a.xc[i] = xp + 16 * i;
+                        }
+                        const bool live = kk < klen;
+                        if (SMODE == 0) {
+                            float (*cb)[4] = &cc[(b & 1) * 4];
+                            if (TMA || kofs + 64 <= klen) block64<XT, FMT, false>(cb, a, true);
+                            else block64<XT, FMT, true>(cb, a, live);
+                        } else {
+                            float tt[4][4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) tt[q][0] = tt[q][1] = tt[q][2] = tt[q][3] = 0.f;
+                            if (SMODE == 2) block32<XT, FMT>(tt, a);
+                            else if (TMA || kofs + 64 <= klen) block64<XT, FMT, false>(tt, a, true);
+                            else block64<XT, FMT, true>(tt, a, live);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float t4 = (tt[0][e] + tt[1][e]) + (tt[2][e] + tt[3][e]);
+                                acc[e] = fmaf(t4, e < 2 ? sa[b] : sb[b], acc[e]);
+                            }
+                        }
                     }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
             }
-            if (!mbar_wait(smem_u32(&bars[slot]), (c / S) & 1, STATUS_GEMV_WAIT)) break;
-            const uint8_t* wst = stages + static_cast<size_t>(slot) * p.stage_bytes;
-            const uint8_t* xst = wst + GV_ROWS * p.wpitch;
+            if (SMODE == 0) {
 #pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                const int kofs = kw + b * BLK;
-                if (kofs < klen) {
-                    if (SMODE == 0) {
-                        if (kofs + 64 <= klen) block64<XT, FMT, false>(acc, wst, xst, p.wpitch, p.xpitch, g, tig, mrow, kofs, klen);
-                        else block64<XT, FMT, true>(acc, wst, xst, p.wpitch, p.xpitch, g, tig, mrow, kofs, klen);
-                    } else {
-                        float t[4] = {0.f, 0.f, 0.f, 0.f};
-                        if (SMODE == 2) block32<XT, FMT>(t, wst, xst, p.wpitch, p.xpitch, g, tig, mrow, kofs);
-                        else if (kofs + 64 <= klen) block64<XT, FMT, false>(t, wst, xst, p.wpitch, p.xpitch, g, tig, mrow, kofs, klen);
-                        else block64<XT, FMT, true>(t, wst, xst, p.wpitch, p.xpitch, g, tig, mrow, kofs, klen);
-                        acc[0] = fmaf(t[0], sa[b], acc[0]); acc[1] = fmaf(t[1], sa[b], acc[1]);
-                        acc[2] = fmaf(t[2], sb[b], acc[2]); acc[3] = fmaf(t[3], sb[b], acc[3]);
-                    }
+                for (int e = 0; e < 4; ++e)
+                    acc[e] = ((cc[0][e] + cc[1][e]) + (cc[2][e] + cc[3][e])) + ((cc[4][e] + cc[5][e]) + (cc[6][e] + cc[7][e]));
+            }
+            // fixed-order reduction of the eight K-slices, double-buffered so that one barrier per
+            // tile is enough (a buffer is rewritten two tiles later, after the next barrier)
+            float* r = red + (t & 1) * (GV_RED / 4) + warp * (GV_ROWS * 8);
+            r[R * 8 + 2 * tig] = acc[0];
+            r[R * 8 + 2 * tig + 1] = acc[1];
+            r[(R + 8) * 8 + 2 * tig] = acc[2];
+            r[(R + 8) * 8 + 2 * tig + 1] = acc[3];
+            named_barrier_sync(1, GV_CONSUMERS);
+            if (threadIdx.x < GV_ROWS * 8) {
+                const int row = threadIdx.x & 15, m = threadIdx.x >> 4;
+                const int n = n0 + row;
+                if (n < p.N && m < p.M) {
+                    const float* rr = red + (t & 1) * (GV_RED / 4) + row * 8 + m;
+                    float v = 0.f;
+#pragma unroll
+                    for (int w = 0; w < GV_WARPS; ++w) v += rr[w * (GV_ROWS * 8)];
+                    const float b = p.bias ? p.bias[n] : 0.f;
+                    if (SMODE == 0) v = fmaf(v, load_scale(p.scale, n, p.scale_kind), b);
+                    else v += b;
+                    store_dt(p.y, static_cast<size_t>(m) * p.N + n, v, p.y_dt);
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars[GV_MAX_STAGES + slot]));
-        }
-        float* r = red + warp * (GV_ROWS * 8);
-        r[g * 8 + 2 * tig] = acc[0];
-        r[g * 8 + 2 * tig + 1] = acc[1];
-        r[(g + 8) * 8 + 2 * tig] = acc[2];
-        r[(g + 8) * 8 + 2 * tig + 1] = acc[3];
-    }
-    __syncthreads();
-
-    // ---------------------------------------------------------------- fixed-order reduction + epilogue
-    if (threadIdx.x < GV_ROWS * 8) {
-        const int row = threadIdx.x & 15, m = threadIdx.x >> 4;
-        const int n = n0 + row;
-        if (n < p.N && m < p.M) {
-            float v = 0.f;
-#pragma unroll
-            for (int w = 0; w < GV_WARPS; ++w) v += red[w * (GV_ROWS * 8) + row * 8 + m];
-            const float b = p.bias ? p.bias[n] : 0.f;
-            if (SMODE == 0) v = fmaf(v, load_scale(p.scale, n, p.scale_kind), b);
-            else v += b;
-            store_dt(p.y, static_cast<size_t>(m) * p.N + n, v, p.y_dt);
         }
     }
 }
 
-template <typename XT, int FMT, int SMODE>
-static int launch_gemv(const GemvParams& p, size_t smem, cudaStream_t st) {
+static int sm_count_of_current_device() {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+        n = 148;
+    return n;
+}
+
+template <typename XT, int FMT, int SMODE, bool TMA>
+static int launch_gemv(const CUtensorMap& tw, const CUtensorMap& tx, const GemvParams& p, size_t smem, cudaStream_t st) {
     // The opt-in to more than 48 KB of dynamic shared memory is per device and per kernel.
     static unsigned long long configured = 0ull;        // bit d set: done on device d
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (dev >= 64 || !((configured >> dev) & 1ull)) {
-        e = cudaFuncSetAttribute(gemv_kernel<XT, FMT, SMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        e = cudaFuncSetAttribute(gemv_kernel<XT, FMT, SMODE, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemv)");
         if (dev < 64) __atomic_fetch_or(&configured, 1ull << dev, __ATOMIC_RELAXED);
     }
-    const int grid = (p.N + GV_ROWS - 1) / GV_ROWS;
-    gemv_kernel<XT, FMT, SMODE><<<grid, GV_THREADS, smem, st>>>(p);
-    TFP8B_LAUNCH_CHECK("tfp8b_gemv");
+    const int sms = sm_count_of_current_device();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(p.ntiles < sms ? p.ntiles : sms));
+    cfg.blockDim = dim3(GV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.pdl ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, gemv_kernel<XT, FMT, SMODE, TMA>, tw, tx, p);
+    if (e != cudaSuccess) return cuda_fail(e, "tfp8b_gemv launch");
     return TFP8B_OK;
 }
 
 template <typename XT>
-static int dispatch_gemv(const GemvParams& p, int fmt, int smode, size_t smem, cudaStream_t st) {
-#define GV_CASE(F, S) if (fmt == F && smode == S) return launch_gemv<XT, F, S>(p, smem, st)
+static int dispatch_gemv(const CUtensorMap& tw, const CUtensorMap& tx, const GemvParams& p, int fmt, int smode, bool tma,
+                         size_t smem, cudaStream_t st) {
+#define GV_CASE(F, S)                                                                   \
+    if (fmt == F && smode == S)                                                         \
+        return tma ? launch_gemv<XT, F, S, true>(tw, tx, p, smem, st) : launch_gemv<XT, F, S, false>(tw, tx, p, smem, st)
     GV_CASE(TFP8B_E4M3FN, 0); GV_CASE(TFP8B_E4M3FN, 1); GV_CASE(TFP8B_E4M3FN, 2);
     GV_CASE(TFP8B_E5M2, 0);   GV_CASE(TFP8B_E5M2, 1);   GV_CASE(TFP8B_E5M2, 2);
 #undef GV_CASE
@@ -313,22 +488,65 @@ extern "C" int tfp8b_gemv(const void* x, int x_dtype, const uint8_t* codes, cons
                   "tfp8b_gemv: x and codes must be 16-byte aligned");
     const int smode = G == K ? 0 : (G % 64 == 0 ? 1 : 2);
     const int xsz = dtype_size(x_dtype);
-    GemvParams p;
+    GemvParams p = {};
     p.x = x; p.w = codes; p.scale = scale; p.bias = bias; p.y = y;
     p.M = M; p.N = N; p.K = K; p.G = G; p.scale_kind = scale_kind; p.y_dt = y_dtype;
-    // Row pitches that keep the 128-bit (64-code blocks) or 64-bit (32-code blocks) shared loads
-    // of a quarter / half warp on distinct banks.
-    p.wpitch = GV_KS + (smode == 2 ? 32 : 64);
-    p.xpitch = GV_KS * xsz + (smode == 2 ? 64 : 16);
-    p.stage_bytes = (GV_ROWS * p.wpitch + M * p.xpitch + 127) & ~127;
+    p.ntiles = (N + GV_ROWS - 1) / GV_ROWS;
+    // TFP8B_NO_PDL=1 turns programmatic dependent launch off (profilers serialise kernels anyway);
+    // TFP8B_GEMV_BULK=1 forces the bulk-copy layout.
+    static const int no_pdl = [] { const char* v = getenv("TFP8B_NO_PDL"); return v && v[0] == '1'; }();
+    static const int force_bulk = [] { const char* v = getenv("TFP8B_GEMV_BULK"); return v && v[0] == '1'; }();
+    p.pdl = no_pdl ? 0 : 1;
+    // The tensor map describes K in whole 128-byte k-blocks: a K that is not a multiple of 128
+    // would make its last k-block read past the row (and, on the last row, past the buffer).
+    const bool tma = K % 128 == 0 && !force_bulk;
     const int nchunks = (K + GV_KS - 1) / GV_KS;
-    int S = (GV_SMEM_TARGET - GV_HEADER) / p.stage_bytes;
+    CUtensorMap tw = {}, tx = {};
+    if (tma) {
+        const int epb = 128 / xsz;                         // activations per 128-byte k-block
+        p.wstage_bytes = GV_ROWS * GV_KS;
+        p.x_resident = (M * K * xsz <= GV_XRES_MAX) ? 1 : 0;
+        const int nkb_x = K / epb;
+        p.xres_box_kb = nkb_x < 256 ? nkb_x : 256;
+        p.xres_box_bytes = p.xres_box_kb * M * 128;
+        p.xres_issues = (nkb_x + p.xres_box_kb - 1) / p.xres_box_kb;
+        p.xres_bytes = p.x_resident ? ((p.xres_issues * p.xres_box_bytes + 1023) & ~1023) : 0;
+        const int xstage = p.x_resident ? 0 : M * GV_KS * xsz;          // a multiple of 1024
+        p.stage_bytes = p.wstage_bytes + xstage;
+        // weights: [k-block][row][128 B]; dim 1 (rows) strides by K, dim 2 (k-blocks) by 128 bytes
+        const cuuint64_t wd[3] = {128, static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(K / 128)};
+        const cuuint64_t ws[2] = {static_cast<cuuint64_t>(K), 128};
+        const cuuint32_t wb[3] = {128, GV_ROWS, GV_KS / 128};
+        int rc = encode_tensor_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, codes, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != TFP8B_OK) return rc;
+        const cuuint64_t xd[3] = {static_cast<cuuint64_t>(epb), static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(nkb_x)};
+        const cuuint64_t xs[2] = {static_cast<cuuint64_t>(K) * xsz, 128};
+        const cuuint32_t xb[3] = {static_cast<cuuint32_t>(epb), static_cast<cuuint32_t>(M),
+                                  static_cast<cuuint32_t>(p.x_resident ? p.xres_box_kb : GV_KS / epb)};
+        const CUtensorMapDataType xt = x_dtype == TFP8B_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                     : x_dtype == TFP8B_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+        rc = encode_tensor_map(&tx, xt, 3, x, xd, xs, xb, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != TFP8B_OK) return rc;
+    } else {
+        // Row pitches that keep the 128-bit (64-code blocks) or 64-bit (32-code blocks) shared
+        // loads of a quarter / half warp on distinct banks.
+        const int xpad = smode == 2 ? 64 : 16;
+        p.wpitch = GV_KS + (smode == 2 ? 32 : 64);
+        p.wstage_bytes = GV_ROWS * p.wpitch;
+        p.x_resident = (M * (K * xsz + xpad) <= GV_XRES_MAX) ? 1 : 0;
+        p.xpitch = (p.x_resident ? K : GV_KS) * xsz + xpad;
+        p.xres_bytes = p.x_resident ? ((M * p.xpitch + 1023) & ~1023) : 0;
+        p.stage_bytes = (p.wstage_bytes + (p.x_resident ? 0 : M * p.xpitch) + 127) & ~127;
+    }
+    int S = (GV_SMEM_TARGET - 1024 - GV_HEADER - p.xres_bytes) / p.stage_bytes;
     S = S < 2 ? 2 : (S > GV_MAX_STAGES ? GV_MAX_STAGES : S);
-    if (S > nchunks) S = nchunks;
+    const int sms = sm_count_of_current_device();
+    const int max_items = ((p.ntiles + sms - 1) / sms) * nchunks;     // stages the busiest CTA moves
+    if (S > max_items) S = max_items;
     p.nstages = S;
-    const size_t smem = GV_HEADER + static_cast<size_t>(S) * p.stage_bytes;
+    const size_t smem = 1024 + GV_HEADER + p.xres_bytes + static_cast<size_t>(S) * p.stage_bytes;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (x_dtype == TFP8B_F16) return dispatch_gemv<__half>(p, fmt, smode, smem, st);
-    if (x_dtype == TFP8B_BF16) return dispatch_gemv<__nv_bfloat16>(p, fmt, smode, smem, st);
-    return dispatch_gemv<float>(p, fmt, smode, smem, st);
+    if (x_dtype == TFP8B_F16) return dispatch_gemv<__half>(tw, tx, p, fmt, smode, tma, smem, st);
+    if (x_dtype == TFP8B_BF16) return dispatch_gemv<__nv_bfloat16>(tw, tx, p, fmt, smode, tma, smem, st);
+    return dispatch_gemv<float>(tw, tx, p, fmt, smode, tma, smem, st);
 }
