@@ -235,6 +235,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
     atomicOr(&g_status, status_bit);
     return false;
 }
+// The same wait for a whole (converged) warp: one lane polls, the others sleep at the shuffle.
+// 256 threads polling one mbarrier keep the shared-memory pipe busy for nothing.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, unsigned status_bit) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, status_bit) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

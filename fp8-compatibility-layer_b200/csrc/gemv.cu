@@ -34,9 +34,12 @@
 namespace tfp8b {
 
 constexpr int GV_ROWS = 16;                      // weight rows per tile (the MMA's M)
-constexpr int GV_WARPS = 8;                      // consumer warps
+#ifndef TFP8B_GV_WARPS
+#define TFP8B_GV_WARPS 16
+#endif
+constexpr int GV_WARPS = TFP8B_GV_WARPS;         // consumer warps
 constexpr int GV_CONSUMERS = GV_WARPS * 32;
-constexpr int GV_THREADS = GV_CONSUMERS + 32;    // + one producer warp
+constexpr int GV_THREADS = GV_CONSUMERS + 64;    // + one producer warp + one epilogue warp
 #ifndef TFP8B_GV_KS
 #define TFP8B_GV_KS 1024
 #endif
@@ -47,9 +50,11 @@ constexpr int GV_KS = TFP8B_GV_KS;               // codes of K per stage
 constexpr int GV_WK = GV_KS / GV_WARPS;          // codes of K per warp per stage
 constexpr int GV_MAX_STAGES = 14;
 constexpr int GV_RED = GV_WARPS * GV_ROWS * 8 * 4;            // one reduction buffer
-constexpr int GV_HEADER = 9 * 1024;                           // 256 B of barriers + two reduction buffers, padded to 1 KB
+constexpr int GV_HEADER = (384 + 2 * GV_RED + 1023) / 1024 * 1024;   // barriers + two reduction buffers, padded to 1 KB
 constexpr int GV_SMEM_TARGET = TFP8B_GV_SMEM_KB * 1024;       // per CTA: two CTAs (this kernel + its successor) share an SM
-constexpr int GV_XRES_MAX = 40 * 1024;           // activations up to this size stay resident per CTA
+constexpr int GV_SMEM_LARGE = 200 * 1024;        // ... unless the activations need the room (M > 1 with a long K)
+constexpr int GV_XRES_SMALL = 40 * 1024;         // resident activations up to this size keep the small footprint
+constexpr int GV_XRES_MAX = 96 * 1024;           // activations up to this size stay resident per CTA
 
 struct GemvParams {
     const void* x;
@@ -59,7 +64,6 @@ struct GemvParams {
     void* y;
     int M, N, K, G, scale_kind, y_dt;
     int nstages, wpitch, xpitch, wstage_bytes, stage_bytes, x_resident, xres_bytes, ntiles, pdl;
-    int xres_issues, xres_box_bytes, xres_box_kb;     // resident activations by tensor map: loads, bytes and k-blocks per load
 };
 
 __device__ __forceinline__ void mma16816_f16(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -114,26 +118,32 @@ __device__ __forceinline__ void mma_step(float c[4], uint32_t wa, uint32_t wb, c
 // The MMA steps of a block go to separate accumulators c[0..3], so that no mma.sync waits for the
 // one before it.
 //
-// Where a lane finds its operands in shared memory: two weight pieces (rows R and R+8 of the
-// tile) and up to four 16-byte pieces of its activation slice.
-struct BlockAddr {
-    const uint8_t* wa;
-    const uint8_t* wb;
-    const uint8_t* xc[4];
-};
+// Shared-memory loads by 32-bit shared-window address: no generic-pointer arithmetic in the inner
+// loop (the first version spent 3.5 instructions per code, most of them on addresses).
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
+    return v;
+}
 
-// A 64-code block of the stage: lane (g, tig) takes the 16 codes at k = kofs + 16*tig of rows R
-// and R+8 and the matching 16 activations of row m. MASK (bulk-copy layout only): the block is only
-// half inside K (K is a multiple of 32), lanes with tig >= 2 contribute zeros.
+// A 64-code block of the stage: lane (g, tig) takes the 16 codes at k = kofs + 16*tig of tile rows
+// R (address wa) and R+8 (address wb) and the matching 16 activations of row m, found as XCH
+// 16-byte pieces at xb + xoff[i]. MASK (bulk-copy layout only): the block is only half inside K
+// (K is a multiple of 32), lanes with tig >= 2 contribute zeros.
 template <typename XT, int FMT, bool MASK>
-__device__ __forceinline__ void block64(float (*c)[4], const BlockAddr& a, bool live) {
-    uint4 wa = *reinterpret_cast<const uint4*>(a.wa);
-    uint4 wb = *reinterpret_cast<const uint4*>(a.wb);
+__device__ __forceinline__ void block64(float (*c)[4], uint32_t wa_addr, uint32_t wb_addr, uint32_t xb, const int* xoff, bool live) {
+    uint4 wa = lds128(wa_addr);
+    uint4 wb = lds128(wb_addr);
     constexpr int XW = sizeof(XT) == 4 ? 16 : 8;           // 32-bit words of x per lane per block
     uint32_t xr[XW];
 #pragma unroll
     for (int i = 0; i < XW / 4; ++i) {
-        uint4 v = *reinterpret_cast<const uint4*>(a.xc[i]);
+        uint4 v = lds128(xb + xoff[i]);
         xr[4 * i] = v.x; xr[4 * i + 1] = v.y; xr[4 * i + 2] = v.z; xr[4 * i + 3] = v.w;
     }
     if (MASK && !live) {
@@ -148,14 +158,14 @@ __device__ __forceinline__ void block64(float (*c)[4], const BlockAddr& a, bool 
 
 // A 32-code block (32-wide scale groups): lane (g, tig) takes 8 codes at k = kofs + 8*tig.
 template <typename XT, int FMT>
-__device__ __forceinline__ void block32(float (*c)[4], const BlockAddr& a) {
-    uint2 wa = *reinterpret_cast<const uint2*>(a.wa);
-    uint2 wb = *reinterpret_cast<const uint2*>(a.wb);
+__device__ __forceinline__ void block32(float (*c)[4], uint32_t wa_addr, uint32_t wb_addr, uint32_t xb, const int* xoff) {
+    uint2 wa = lds64(wa_addr);
+    uint2 wb = lds64(wb_addr);
     constexpr int XW = sizeof(XT) == 4 ? 8 : 4;
     uint32_t xr[XW];
 #pragma unroll
     for (int i = 0; i < XW / 4; ++i) {
-        uint4 v = *reinterpret_cast<const uint4*>(a.xc[i]);
+        uint4 v = lds128(xb + xoff[i]);
         xr[4 * i] = v.x; xr[4 * i + 1] = v.y; xr[4 * i + 2] = v.z; xr[4 * i + 3] = v.w;
     }
     mma_step<XT, FMT>(c[0], wa.x, wb.x, &xr[0]);
@@ -174,14 +184,14 @@ __device__ __forceinline__ int tile_row_of(int g) {
     return SMODE == 2 ? 2 * (g & 3) + (g >> 2) : (g >> 1) + 4 * (g & 1);
 }
 
-// Shared-memory map:  [0,256) mbarriers: full[0..13], empty[14..27], xfull[28]
-//                     [256, 256 + 2*GV_RED) two reduction buffers [warp][row][m]
+// Shared-memory map:  [0,256) mbarriers: full[0..13], empty[14..27], xfull[28], red_full[29..30], red_empty[31..32]
+//                     [384, 384 + 2*GV_RED) two reduction buffers [warp][row][m]
 //                     (1024-byte aligned) resident activations, then the ring of stages.
 // Two data layouts:
 //   TMA   (K % 128 == 0) one 3-D tensor-map load per stage brings 16 rows x 1024 codes as
-//         [8 k-blocks][16 rows][128 B] with the 128-byte swizzle; activations likewise as
-//         [k-blocks][M rows][128 B]. One instruction per 16 KB: issuing one bulk copy per 1 KB row
-//         piece, as the other layout does, capped a CTA at about 20 GB/s.
+//         [8 k-blocks][16 rows][128 B] with the 128-byte swizzle; activations that travel with
+//         the stage likewise as [k-blocks][M rows][128 B]. One instruction per 16 KB: issuing
+//         one bulk copy per 1 KB row piece, as the other layout does, capped a CTA at ~20 GB/s.
 //   bulk  (any K % 32 == 0) 16 row pieces of up to 1 KB by cp.async.bulk, row pitch padded for
 //         conflict-free loads; used for the K that the tensor map cannot describe.
 //
@@ -189,16 +199,18 @@ __device__ __forceinline__ int tile_row_of(int g) {
 //       1: K-groups that are multiples of 64 (applied per 64-code block)
 //       2: K-groups that are multiples of 32 only (32-code blocks)
 template <typename XT, int FMT, int SMODE, bool TMA>
-__global__ void __launch_bounds__(GV_THREADS)
+__global__ void __launch_bounds__(GV_THREADS, 2)
 gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemvParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-    float* red = reinterpret_cast<float*>(smem + 256);
+    float* red = reinterpret_cast<float*>(smem + 384);
     uint8_t* xres = smem + GV_HEADER;
     uint8_t* stages = xres + p.xres_bytes;
     const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[GV_MAX_STAGES]);
     const uint32_t bar_x = smem_u32(&bars[2 * GV_MAX_STAGES]);
+    const uint32_t bar_red_full = smem_u32(&bars[2 * GV_MAX_STAGES + 1]);     // [2]: partial sums of a tile written
+    const uint32_t bar_red_empty = smem_u32(&bars[2 * GV_MAX_STAGES + 3]);    // [2]: ... and read by the epilogue warp
     constexpr int SZ = static_cast<int>(sizeof(XT));
     constexpr int EPB = 128 / SZ;                    // activations per 128-byte k-block (TMA layout)
 
@@ -214,6 +226,10 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             mbar_init(bar_empty + 8 * s, GV_WARPS);
         }
         mbar_init(bar_x, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_red_full + 8 * b, GV_WARPS);
+            mbar_init(bar_red_empty + 8 * b, 1);
+        }
         mbar_fence_init();
         fence_proxy_async_smem();
         if (TMA) { tma_prefetch_desc(&tm_w); tma_prefetch_desc(&tm_x); }
@@ -229,11 +245,10 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         // bytes of activations that travel with a stage, per code of K (bulk) or per stage (TMA)
         const uint32_t x_per_k = p.x_resident ? 0u : static_cast<uint32_t>(p.M * SZ);
 
-        auto issue_w = [&](int item) {
-            const int t = item / nchunks, c = item - t * nchunks;
+        // (t, c, slot) name the stage being issued: tile of this CTA, chunk of K, ring slot
+        auto issue_w = [&](int t, int c, int slot) {
             const int n0 = (static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x)) * GV_ROWS;
             const int k0 = c * GV_KS, klen = min(GV_KS, p.K - k0);
-            const int slot = item % S;
             uint8_t* wst = stages + static_cast<size_t>(slot) * p.stage_bytes;
             if (TMA) {
                 if (lane == 0) {
@@ -250,10 +265,8 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 }
             }
         };
-        auto issue_x = [&](int item) {                                   // activations that travel with the stage
-            const int c = item % nchunks;
+        auto issue_x = [&](int c, int slot) {                            // activations that travel with the stage
             const int k0 = c * GV_KS, klen = min(GV_KS, p.K - k0);
-            const int slot = item % S;
             uint8_t* xst = stages + static_cast<size_t>(slot) * p.stage_bytes + p.wstage_bytes;
             if (TMA) {
                 if (lane == 0) tma_load_3d(smem_u32(xst), &tm_x, 0, 0, k0 / EPB, bar_full + 8 * slot, pol_x);
@@ -263,33 +276,38 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         };
 
         const int pre = min(S, total);
-        for (int i = 0; i < pre; ++i) issue_w(i);        // weights first: they never depend on the predecessor
-        if (p.pdl) pdl_wait();                           // activations may be the predecessor's output
+        int t = 0, c = 0;
+        for (int i = 0; i < pre; ++i) {                  // weights first: they never depend on the predecessor
+            issue_w(t, c, i);
+            if (++c == nchunks) { c = 0; ++t; }
+        }
+        if (p.pdl == 1) pdl_wait();                      // activations may be the predecessor's output
         if (p.x_resident) {
-            if (TMA) {
-                if (lane == 0) {
-                    mbar_expect_tx(bar_x, static_cast<uint32_t>(p.xres_issues * p.xres_box_bytes));
-                    for (int j = 0; j < p.xres_issues; ++j)
-                        tma_load_3d(smem_u32(xres + static_cast<size_t>(j) * p.xres_box_bytes), &tm_x, 0, 0, j * p.xres_box_kb, bar_x, pol_x);
-                }
-            } else {
-                if (lane == 0) mbar_expect_tx(bar_x, static_cast<uint32_t>(p.M * p.K * SZ));
-                __syncwarp();
-                if (xm >= 0 && xm < p.M) {
-                    // one row can exceed what a single bulk copy should carry: cut it at 16 KB
-                    for (int off = 0; off < p.K * SZ; off += 16384)
-                        bulk_g2s(smem_u32(xres + xm * p.xpitch + off), xrow + off, min(16384, p.K * SZ - off), bar_x, pol_x);
-                }
+            // resident activations: plain rows (pitch xpitch), loaded once per CTA by bulk copies
+            if (lane == 0) mbar_expect_tx(bar_x, static_cast<uint32_t>(p.M * p.K * SZ));
+            __syncwarp();
+            if (xm >= 0 && xm < p.M) {
+                // one row can exceed what a single bulk copy should carry: cut it at 16 KB
+                for (int off = 0; off < p.K * SZ; off += 16384)
+                    bulk_g2s(smem_u32(xres + xm * p.xpitch + off), xrow + off, min(16384, p.K * SZ - off), bar_x, pol_x);
             }
         } else {
-            for (int i = 0; i < pre; ++i) issue_x(i);
+            int cx = 0;
+            for (int i = 0; i < pre; ++i) {
+                issue_x(cx, i);
+                if (++cx == nchunks) cx = 0;
+            }
         }
+        int slot = 0;
+        uint32_t phase = 0;                              // parity of the slot's previous use
         for (int i = pre; i < total; ++i) {
-            if (!mbar_wait(bar_empty + 8 * (i % S), ((i / S) - 1) & 1, STATUS_GEMV_WAIT)) break;
-            issue_w(i);
-            if (!p.x_resident) issue_x(i);
+            if (!mbar_wait(bar_empty + 8 * slot, phase, STATUS_GEMV_WAIT)) break;
+            issue_w(t, c, slot);
+            if (!p.x_resident) issue_x(c, slot);
+            if (++c == nchunks) { c = 0; ++t; }
+            if (++slot == S) { slot = 0; phase ^= 1u; }
         }
-    } else {
+    } else if (warp < GV_WARPS) {
         // ---------------------------------------------------------------- consumer warps
         const int g = lane >> 2, tig = lane & 3;
         const int R = tile_row_of<SMODE, TMA>(g);        // tile rows R and R + 8 live in this lane's MMA rows
@@ -299,10 +317,28 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         constexpr int NB = GV_WK / BLK;
         constexpr int XCH = BLK * SZ / 64;               // 16-byte pieces of x per lane per block
         const int kw = warp * GV_WK;
+        // Lane-constant shared-memory offsets of this lane's operands inside a stage (weights) and
+        // relative to the activations of the stage's first code (x), one set per block.
+        int woff[NB], xoff[NB][XCH];
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            const int kk = kw + b * BLK + tig * (BLK / 4);           // this lane's first code within the stage
+            if (TMA) woff[b] = (kk >> 7) * 2048 + R * 128 + ((((kk >> 4) & 7) ^ R) << 4) + (kk & 8);
+            else woff[b] = R * p.wpitch + kk;
+            if (TMA && !p.x_resident) {
+                const int xo = ((kk / EPB) * p.M + mrow) * 128, ph = (xo >> 7) & 7, c0 = ((kk % EPB) * SZ) >> 4;
+#pragma unroll
+                for (int i = 0; i < XCH; ++i) xoff[b][i] = xo + (((c0 + i) ^ ph) << 4);
+            } else {
+#pragma unroll
+                for (int i = 0; i < XCH; ++i) xoff[b][i] = mrow * p.xpitch + kk * SZ + 16 * i;
+            }
+        }
+        const uint32_t stages_u32 = smem_u32(stages), xres_u32 = smem_u32(xres);
         bool ok = true;
         if (p.x_resident) ok = mbar_wait(bar_x, 0, STATUS_GEMV_WAIT);
-        if (p.pdl) pdl_wait();                           // before the first store to y
-        int item = 0;
+        int slot = 0;
+        uint32_t phase = 0;                              // ring position: no divisions in the loop
         // A wait that runs out clears `ok`; the warp then stops waiting and computing but keeps
         // walking the loop, so it still meets the others at every barrier and the CTA ends.
         for (int t = 0; t < my_tiles; ++t) {
@@ -315,8 +351,10 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             float cc[8][4];
 #pragma unroll
             for (int a = 0; a < 8; ++a) cc[a][0] = cc[a][1] = cc[a][2] = cc[a][3] = 0.f;
-            for (int c = 0; c < nchunks; ++c, ++item) {
-                const int slot = item % S;
+            for (int c = 0; c < nchunks; ++c) {
+                const int cur = slot;
+                const uint32_t par = phase;
+                if (++slot == S) { slot = 0; phase ^= 1u; }
                 const int k0 = c * GV_KS, klen = min(GV_KS, p.K - k0);
                 float sa[NB], sb[NB];
                 if (SMODE != 0) {
@@ -330,46 +368,29 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         }
                     }
                 }
-                if (ok) ok = mbar_wait(bar_full + 8 * slot, (item / S) & 1, STATUS_GEMV_WAIT);
+                if (ok) ok = mbar_wait(bar_full + 8 * cur, par, STATUS_GEMV_WAIT);
                 if (!ok) continue;
-                const uint8_t* wst = stages + static_cast<size_t>(slot) * p.stage_bytes;
-                // activations: resident tile indexed by global k, or this stage's piece by local k
-                const uint8_t* xbase = p.x_resident ? xres : wst + p.wstage_bytes;
-                const int xk0 = p.x_resident ? k0 : 0;
+                const uint32_t wst = stages_u32 + static_cast<uint32_t>(cur * p.stage_bytes);
+                // activations: the resident rows at this stage's first code, or the stage's own piece
+                const uint32_t xb = p.x_resident ? xres_u32 + static_cast<uint32_t>(k0 * SZ) : wst + static_cast<uint32_t>(p.wstage_bytes);
+                const uint32_t wrow8 = TMA ? 1024u : static_cast<uint32_t>(8 * p.wpitch);   // tile row R + 8
 #pragma unroll
                 for (int b = 0; b < NB; ++b) {
                     const int kofs = kw + b * BLK;
                     if (kofs < klen) {
-                        const int kk = kofs + tig * (BLK / 4);           // this lane's first code within the stage
-                        BlockAddr a;
-                        if (TMA) {
-                            const int wo = (kk >> 7) * 2048 + R * 128 + ((((kk >> 4) & 7) ^ R) << 4) + (kk & 8);
-                            a.wa = wst + wo;
-                            a.wb = a.wa + 1024;                          // row R + 8: same swizzle phase
-                            const int xk = xk0 + kk;
-                            const int xoff = ((xk / EPB) * p.M + mrow) * 128;
-                            const int c0 = ((xk % EPB) * SZ) >> 4, ph = (xoff >> 7) & 7;
-#pragma unroll
-                            for (int i = 0; i < XCH; ++i) a.xc[i] = xbase + xoff + (((c0 + i) ^ ph) << 4);
-                        } else {
-                            a.wa = wst + R * p.wpitch + kk;
-                            a.wb = a.wa + 8 * p.wpitch;
-                            const uint8_t* xp = xbase + mrow * p.xpitch + (xk0 + kk) * SZ;
-#pragma unroll
-                            for (int i = 0; i < XCH; ++i) a.xc[i] = xp + 16 * i;
-                        }
-                        const bool live = kk < klen;
+                        const uint32_t wa = wst + woff[b], wb = wa + wrow8;
+                        const bool live = kofs + tig * (BLK / 4) < klen;
                         if (SMODE == 0) {
                             float (*cb)[4] = &cc[(b & 1) * 4];
-                            if (TMA || kofs + 64 <= klen) block64<XT, FMT, false>(cb, a, true);
-                            else block64<XT, FMT, true>(cb, a, live);
+                            if (TMA || kofs + 64 <= klen) block64<XT, FMT, false>(cb, wa, wb, xb, xoff[b], true);
+                            else block64<XT, FMT, true>(cb, wa, wb, xb, xoff[b], live);
                         } else {
                             float tt[4][4];
 #pragma unroll
                             for (int q = 0; q < 4; ++q) tt[q][0] = tt[q][1] = tt[q][2] = tt[q][3] = 0.f;
-                            if (SMODE == 2) block32<XT, FMT>(tt, a);
-                            else if (TMA || kofs + 64 <= klen) block64<XT, FMT, false>(tt, a, true);
-                            else block64<XT, FMT, true>(tt, a, live);
+                            if (SMODE == 2) block32<XT, FMT>(tt, wa, wb, xb, xoff[b]);
+                            else if (TMA || kofs + 64 <= klen) block64<XT, FMT, false>(tt, wa, wb, xb, xoff[b], true);
+                            else block64<XT, FMT, true>(tt, wa, wb, xb, xoff[b], live);
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const float t4 = (tt[0][e] + tt[1][e]) + (tt[2][e] + tt[3][e]);
@@ -379,36 +400,54 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     }
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
+                if (lane == 0) mbar_arrive(bar_empty + 8 * cur);
             }
             if (SMODE == 0) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
                     acc[e] = ((cc[0][e] + cc[1][e]) + (cc[2][e] + cc[3][e])) + ((cc[4][e] + cc[5][e]) + (cc[6][e] + cc[7][e]));
             }
-            // fixed-order reduction of the eight K-slices, double-buffered so that one barrier per
-            // tile is enough (a buffer is rewritten two tiles later, after the next barrier)
+            // Hand the eight K-slices' partial sums to the epilogue warp through one of two
+            // buffers, so that the consumers go straight on with the next tile: the reduction, the
+            // scale / bias loads and the stores are off their critical path.
+            if (ok && t >= 2) ok = mbar_wait(bar_red_empty + 8 * (t & 1), ((t >> 1) - 1) & 1, STATUS_GEMV_WAIT);
             float* r = red + (t & 1) * (GV_RED / 4) + warp * (GV_ROWS * 8);
             r[R * 8 + 2 * tig] = acc[0];
             r[R * 8 + 2 * tig + 1] = acc[1];
             r[(R + 8) * 8 + 2 * tig] = acc[2];
             r[(R + 8) * 8 + 2 * tig + 1] = acc[3];
-            named_barrier_sync(1, GV_CONSUMERS);
-            if (threadIdx.x < GV_ROWS * 8) {
-                const int row = threadIdx.x & 15, m = threadIdx.x >> 4;
-                const int n = n0 + row;
-                if (n < p.N && m < p.M) {
-                    const float* rr = red + (t & 1) * (GV_RED / 4) + row * 8 + m;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_red_full + 8 * (t & 1));
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue warp
+        // lane -> four outputs (row, m) of the 16 x 8 tile; the eight partial sums are added in a
+        // fixed order, so the result does not depend on timing.
+        bool ok = true;
+        if (p.pdl == 1) pdl_wait();                      // before the first store to y
+        for (int t = 0; t < my_tiles; ++t) {
+            const int n0 = (static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x)) * GV_ROWS;
+            const int row = lane & 15, n = n0 + row;
+            const bool live = n < p.N;
+            const float bv = (live && p.bias) ? p.bias[n] : 0.f;
+            const float sv = (live && SMODE == 0) ? load_scale(p.scale, n, p.scale_kind) : 1.f;
+            if (ok) ok = mbar_wait(bar_red_full + 8 * (t & 1), (t >> 1) & 1, STATUS_GEMV_WAIT);
+            if (ok) {
+                const float* rb = red + (t & 1) * (GV_RED / 4);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int m = (lane >> 4) + 2 * j;
                     float v = 0.f;
 #pragma unroll
-                    for (int w = 0; w < GV_WARPS; ++w) v += rr[w * (GV_ROWS * 8)];
-                    const float b = p.bias ? p.bias[n] : 0.f;
-                    if (SMODE == 0) v = fmaf(v, load_scale(p.scale, n, p.scale_kind), b);
-                    else v += b;
-                    store_dt(p.y, static_cast<size_t>(m) * p.N + n, v, p.y_dt);
+                    for (int w = 0; w < GV_WARPS; ++w) v += rb[w * (GV_ROWS * 8) + row * 8 + m];
+                    v = SMODE == 0 ? fmaf(v, sv, bv) : v + bv;
+                    if (live && m < p.M) store_dt(p.y, static_cast<size_t>(m) * p.N + n, v, p.y_dt);
                 }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_red_empty + 8 * (t & 1));
         }
+        if (p.pdl == 2) pdl_wait();                      // independent I/O: only completion is ordered
     }
 }
 
@@ -474,6 +513,12 @@ using namespace tfp8b;
 extern "C" int tfp8b_gemv(const void* x, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind,
                           const float* bias, void* y, int y_dtype, int M, int N, int K, int G, int fmt,
                           tfp8b_stream_t stream) {
+    return tfp8b_gemv_ex(x, x_dtype, codes, scale, scale_kind, bias, y, y_dtype, M, N, K, G, fmt, 0u, stream);
+}
+
+extern "C" int tfp8b_gemv_ex(const void* x, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind,
+                             const float* bias, void* y, int y_dtype, int M, int N, int K, int G, int fmt,
+                             unsigned int flags, tfp8b_stream_t stream) {
     TFP8B_REQUIRE(M >= 0 && N >= 0 && K > 0 && G > 0, TFP8B_ERR_INVALID, "tfp8b_gemv: bad size M=%d N=%d K=%d G=%d", M, N, K, G);
     TFP8B_REQUIRE(x_dtype >= 0 && x_dtype <= 2 && y_dtype >= 0 && y_dtype <= 2, TFP8B_ERR_INVALID, "tfp8b_gemv: bad dtype");
     TFP8B_REQUIRE(fmt == TFP8B_E4M3FN || fmt == TFP8B_E5M2, TFP8B_ERR_INVALID, "tfp8b_gemv: bad fmt %d", fmt);
@@ -496,7 +541,11 @@ extern "C" int tfp8b_gemv(const void* x, int x_dtype, const uint8_t* codes, cons
     // TFP8B_GEMV_BULK=1 forces the bulk-copy layout.
     static const int no_pdl = [] { const char* v = getenv("TFP8B_NO_PDL"); return v && v[0] == '1'; }();
     static const int force_bulk = [] { const char* v = getenv("TFP8B_GEMV_BULK"); return v && v[0] == '1'; }();
-    p.pdl = no_pdl ? 0 : 1;
+    // pdl: 0 = plain launch; 1 = early launch, wait for the predecessor before touching x / y;
+    //      2 = early launch, caller vouches that x / y are independent of the predecessor: the wait
+    //          moves to the very end (so that this grid never completes before its predecessor and
+    //          later work in the stream still sees both finished).
+    p.pdl = no_pdl ? 0 : ((flags & TFP8B_GEMV_INDEPENDENT_IO) ? 2 : 1);
     // The tensor map describes K in whole 128-byte k-blocks: a K that is not a multiple of 128
     // would make its last k-block read past the row (and, on the last row, past the buffer).
     const bool tma = K % 128 == 0 && !force_bulk;
@@ -505,12 +554,11 @@ extern "C" int tfp8b_gemv(const void* x, int x_dtype, const uint8_t* codes, cons
     if (tma) {
         const int epb = 128 / xsz;                         // activations per 128-byte k-block
         p.wstage_bytes = GV_ROWS * GV_KS;
-        p.x_resident = (M * K * xsz <= GV_XRES_MAX) ? 1 : 0;
+        const int xpad = smode == 2 ? 64 : 16;
+        p.x_resident = (M * (K * xsz + xpad) <= GV_XRES_MAX) ? 1 : 0;
+        p.xpitch = K * xsz + xpad;                                      // resident rows only
+        p.xres_bytes = p.x_resident ? ((M * p.xpitch + 1023) & ~1023) : 0;
         const int nkb_x = K / epb;
-        p.xres_box_kb = nkb_x < 256 ? nkb_x : 256;
-        p.xres_box_bytes = p.xres_box_kb * M * 128;
-        p.xres_issues = (nkb_x + p.xres_box_kb - 1) / p.xres_box_kb;
-        p.xres_bytes = p.x_resident ? ((p.xres_issues * p.xres_box_bytes + 1023) & ~1023) : 0;
         const int xstage = p.x_resident ? 0 : M * GV_KS * xsz;          // a multiple of 1024
         p.stage_bytes = p.wstage_bytes + xstage;
         // weights: [k-block][row][128 B]; dim 1 (rows) strides by K, dim 2 (k-blocks) by 128 bytes
@@ -522,7 +570,7 @@ extern "C" int tfp8b_gemv(const void* x, int x_dtype, const uint8_t* codes, cons
         const cuuint64_t xd[3] = {static_cast<cuuint64_t>(epb), static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(nkb_x)};
         const cuuint64_t xs[2] = {static_cast<cuuint64_t>(K) * xsz, 128};
         const cuuint32_t xb[3] = {static_cast<cuuint32_t>(epb), static_cast<cuuint32_t>(M),
-                                  static_cast<cuuint32_t>(p.x_resident ? p.xres_box_kb : GV_KS / epb)};
+                                  static_cast<cuuint32_t>(GV_KS / epb)};
         const CUtensorMapDataType xt = x_dtype == TFP8B_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                      : x_dtype == TFP8B_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
         rc = encode_tensor_map(&tx, xt, 3, x, xd, xs, xb, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -538,7 +586,8 @@ extern "C" int tfp8b_gemv(const void* x, int x_dtype, const uint8_t* codes, cons
         p.xres_bytes = p.x_resident ? ((M * p.xpitch + 1023) & ~1023) : 0;
         p.stage_bytes = (p.wstage_bytes + (p.x_resident ? 0 : M * p.xpitch) + 127) & ~127;
     }
-    int S = (GV_SMEM_TARGET - 1024 - GV_HEADER - p.xres_bytes) / p.stage_bytes;
+    const int target = (p.x_resident && p.xres_bytes <= GV_XRES_SMALL) ? GV_SMEM_TARGET : GV_SMEM_LARGE;
+    int S = (target - 1024 - GV_HEADER - p.xres_bytes) / p.stage_bytes;
     S = S < 2 ? 2 : (S > GV_MAX_STAGES ? GV_MAX_STAGES : S);
     const int sms = sm_count_of_current_device();
     const int max_items = ((p.ntiles + sms - 1) / sms) * nchunks;     // stages the busiest CTA moves

@@ -38,6 +38,7 @@ _SIGNATURES = {
     "tfp8b_dequant": ([_P, _P, _I, _P, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_prep": ([_P, _I, _P, _P, _I, _I, _P], _I),
     "tfp8b_gemv": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
+    "tfp8b_gemv_ex": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.c_uint, _P], _I),
     "tfp8b_gemm": ([_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_epilogue": ([_P, _P, _P, _P, _I, _I, _I, _I, _P], _I),
 }
@@ -226,22 +227,25 @@ class GemvLaunch:
         self.device = qweight.device
         N, K = qweight.shape
         self.N = N
-        self.fn = lib.tfp8b_gemv
+        self.fn = lib.tfp8b_gemv_ex
         self._stream = torch._C._cuda_getCurrentRawStream
         self.args = [_P(0), _I(_DT[x_dtype]), _P(qweight.data_ptr()), _P(wscale.data_ptr()), _I(_scale_kind(wscale)),
                      _P(bias.data_ptr() if bias is not None else 0), _P(0), _I(_DT[out_dtype]), _I(0), _I(N), _I(K),
-                     _I(group_size), _I(FMT_ID[fmt]), _P(0)]
+                     _I(group_size), _I(FMT_ID[fmt]), ctypes.c_uint(0), _P(0)]
         self.q, self.ws, self.bias, self.lut, self.out_dtype = qweight, wscale, bias, lut16, out_dtype
 
-    def __call__(self, x, M, out_shape=None):
+    def __call__(self, x, M, out_shape=None, independent=False):
         """x: contiguous CUDA tensor of the bound dtype on this layer's device holding M rows of K
-        (any rank: only its data pointer is used). out_shape: shape of y, default (M, N)."""
+        (any rank: only its data pointer is used). out_shape: shape of y, default (M, N).
+        independent: the caller vouches that x is not produced (and y not used) by the kernel that
+        precedes this call in the stream, so the two may run concurrently."""
         y = torch.empty(out_shape or (M, self.N), dtype=self.out_dtype, device=self.device)
         a = self.args
         a[0].value = x.data_ptr()
         a[6].value = y.data_ptr()
         a[8].value = M
-        a[13].value = self._stream(self.dev)
+        a[13].value = 1 if independent else 0
+        a[14].value = self._stream(self.dev)
         rc = self.fn(*a)
         if rc != 0:
             _check(rc, "tfp8b_gemv")

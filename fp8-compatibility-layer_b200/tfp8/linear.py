@@ -52,6 +52,10 @@ class FP8Linear(nn.Module):
         self._shape_ok = in_features % 32 == 0 and self.group_size % 32 == 0
         self._kernels_ok = self._shape_ok and _ext.available()
         self._lut = lut(self.fmt, device) if device is not None else None
+        # Set by a model runner for layers whose input is not produced by the kernel launched just
+        # before them (K / V after Q, up after gate, the layers of a sweep): the decode GEMV may then
+        # overlap that kernel completely instead of only prefetching its weights.
+        self.independent_input = False
         self._gemv = {}            # (x dtype, out dtype) -> _ext.GemvLaunch
         self._e8 = None            # (weight_scale object, its version, uint8 tensor) for scale_format="ue8m0"
 
@@ -146,7 +150,7 @@ class FP8Linear(nn.Module):
                 p = self._gemv_launch(x.dtype)
                 if p is not None and x.get_device() == p.dev and torch.cuda.current_device() == p.dev:
                     self.stats["gemv"] += 1
-                    return p(x, M, x.shape[:-1] + (self.out_features,))
+                    return p(x, M, x.shape[:-1] + (self.out_features,), self.independent_input)
         if self.fallback is not None:
             self.stats["fallback"] += 1
             return self.fallback(x)

@@ -111,6 +111,18 @@ TFP8B_API int tfp8b_gemv(const void* x, int x_dtype, const uint8_t* codes, const
                const float* bias, void* y, int y_dtype, int M, int N, int K, int G, int fmt,
                tfp8b_stream_t stream);
 
+/* tfp8b_gemv with flags. TFP8B_GEMV_INDEPENDENT_IO: the caller vouches that x and y (and scale,
+ * bias) are neither written nor read by the kernel that precedes this call in the stream -- as
+ * for the K and V projections that follow the Q projection of the same activations, or the layers
+ * of a sweep. The call then runs concurrently with that kernel (programmatic dependent launch
+ * without the wait in front of the activations); it still never completes before its
+ * predecessor, so later work in the stream sees both finished. Without the flag the kernel
+ * prefetches only its weights while the predecessor runs. No reference counterpart. */
+#define TFP8B_GEMV_INDEPENDENT_IO 1u
+TFP8B_API int tfp8b_gemv_ex(const void* x, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind,
+                  const float* bias, void* y, int y_dtype, int M, int N, int K, int G, int fmt,
+                  unsigned int flags, tfp8b_stream_t stream);
+
 /* Tile GEMM for any M >= 1 on prepared activations (tfp8b_prep):
  *   y[m,n] = xs[m] * sum_k x16[m,k] * dec(codes[n,k]) * scale[n,k/G] + bias[n]
  * FP8 tiles are decoded to fp16 in shared memory (group scales folded in as scale/rowmax),
