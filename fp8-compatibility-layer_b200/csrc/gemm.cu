@@ -352,6 +352,34 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmP
     return TFP8B_OK;
 }
 
+// ------------------------------------------------------------------ scratch for tfp8b_linear_static
+// The tile GEMM consumes PREPARED activations (fp16 rows + one power-of-two scale per row), which
+// the ordinary path keeps in a buffer the caller allocates. This array is that buffer for callers
+// that have no way to allocate device memory; every GPU that loads the library carries it until
+// the process exits. In host code its name is only a handle, not a device address: the address
+// is fetched once per device with cudaGetSymbolAddress and handed to the kernels.
+constexpr size_t STATIC_X16_ELEMS = 4u << 20;          // 4 Mi fp16 values = 8 MiB: M * K may not exceed this
+constexpr int STATIC_MAX_ROWS = 8192;                  // row scales
+constexpr size_t STATIC_SCRATCH_BYTES = STATIC_X16_ELEMS * 2 + static_cast<size_t>(STATIC_MAX_ROWS) * 4;
+static __device__ __align__(256) unsigned char g_linear_scratch[STATIC_SCRATCH_BYTES];
+
+// Device address of the scratch array on the current device (looked up on first use per device).
+static int static_scratch(unsigned char** out) {
+    static unsigned char* ptrs[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) { set_error("tfp8b_linear_static: device index %d not supported", dev); return TFP8B_ERR_UNSUPPORTED; }
+    unsigned char* p = __atomic_load_n(&ptrs[dev], __ATOMIC_ACQUIRE);
+    if (!p) {
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_linear_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(linear scratch)");
+        __atomic_store_n(&ptrs[dev], p, __ATOMIC_RELEASE);
+    }
+    *out = p;
+    return TFP8B_OK;
+}
+
 int gemm_status(unsigned int* out, cudaStream_t st) {
     unsigned int* word = nullptr;
     cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&word), g_status);
@@ -402,4 +430,26 @@ extern "C" int tfp8b_gemm(const void* x16, const float* xs, const uint8_t* codes
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (fmt == TFP8B_E4M3FN) return launch_gemm<TFP8B_E4M3FN>(tw, tx, p, smem, st);
     return launch_gemm<TFP8B_E5M2>(tw, tx, p, smem, st);
+}
+
+extern "C" int tfp8b_linear_static(const void* x, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind,
+                                   const float* bias, void* y, int y_dtype, int M, int N, int K, int G, int fmt,
+                                   tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(M >= 0 && N >= 0 && K > 0, TFP8B_ERR_INVALID, "tfp8b_linear_static: bad size M=%d N=%d K=%d", M, N, K);
+    TFP8B_REQUIRE(M <= STATIC_MAX_ROWS && static_cast<size_t>(M) * static_cast<size_t>(K) <= STATIC_X16_ELEMS,
+                  TFP8B_ERR_UNSUPPORTED,
+                  "tfp8b_linear_static: M=%d x K=%d exceeds the built-in scratch (at most %d rows and %zu activation "
+                  "values per call); use tfp8b_prep + tfp8b_gemm with a buffer of your own", M, K, STATIC_MAX_ROWS,
+                  STATIC_X16_ELEMS);
+    if (M == 0 || N == 0) return TFP8B_OK;
+    unsigned char* scratch = nullptr;
+    int rc = static_scratch(&scratch);
+    if (rc != TFP8B_OK) return rc;
+    void* x16 = scratch;
+    float* xs = reinterpret_cast<float*>(scratch + STATIC_X16_ELEMS * 2);
+    // prep overwrites every value the GEMM will read (M * K activations, M scales): nothing in the
+    // array has to start out as zero, whatever an earlier call left there.
+    rc = tfp8b_prep(x, x_dtype, x16, xs, M, K, stream);
+    if (rc != TFP8B_OK) return rc;
+    return tfp8b_gemm(x16, xs, codes, scale, scale_kind, bias, y, y_dtype, M, N, K, G, fmt, stream);
 }

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "tfp8b_gemv": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_gemv_ex": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.c_uint, _P], _I),
     "tfp8b_gemm": ([_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
+    "tfp8b_linear_static": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_epilogue": ([_P, _P, _P, _P, _I, _I, _I, _I, _P], _I),
 }
 

@@ -134,6 +134,27 @@ TFP8B_API int tfp8b_gemm(const void* x16, const float* xs, const uint8_t* codes,
                int scale_kind, const float* bias, void* y, int y_dtype, int M, int N, int K, int G,
                int fmt, tfp8b_stream_t stream);
 
+/* The whole linear layer for any M >= 1 in one call that allocates nothing:
+ *   y = x @ dequant(codes).T + bias   (activation prep, then the tile GEMM)
+ * This entry point has no counterpart in the reference. It exists for callers that cannot obtain
+ * device memory at the moment they need the layer: code that runs while a stream is being
+ * captured, serving loops in which an allocation would stall every other stream of the device,
+ * and hosts that bind this library through a foreign-function interface without a CUDA allocator
+ * of their own. The prepared activations, which tfp8b_prep / tfp8b_gemm keep in caller memory,
+ * live here in an 8 MiB array inside the library (present on every GPU that loads it, until the
+ * process ends).
+ *   Limits: M <= 8192 and M * K <= 4 Mi values per call; larger calls are refused with
+ *           TFP8B_ERR_UNSUPPORTED and a message that names the limit.
+ *   First call on a device: looks up the array's device address (a host-side query, no
+ *           allocation); make that call before any stream capture begins.
+ *   The array is shared by every call and keeps what the last call wrote; each call rewrites all
+ *           of what it reads. Two calls that overlap on the GPU (different streams) race on it:
+ *           issue them on one stream, or order them with events.
+ * x: f16 | bf16 | f32 [M, K]; the other arguments as for tfp8b_gemm. */
+TFP8B_API int tfp8b_linear_static(const void* x, int x_dtype, const uint8_t* codes, const void* scale,
+                  int scale_kind, const float* bias, void* y, int y_dtype, int M, int N, int K, int G,
+                  int fmt, tfp8b_stream_t stream);
+
 /* y[m, 0:n] = y_dtype(acc[m, 0:n] * xs[m] + bias[0:n]) into a column window of a wider output
  * (row pitch ldy elements). Replaces tfp8_epilogue_* / epilogue_into
  * (tfp8/csrc/tfp8_kernels.cu:478-503, tfp8/_ext.py:282-302). */
