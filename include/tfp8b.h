@@ -5,8 +5,8 @@
  * stream of the CURRENT device and returns immediately: 0 on success, a negative TFP8B_ERR_*
  * code otherwise (tfp8b_last_error_string() holds the detail for the calling thread). Unless
  * its comment says otherwise an entry point never allocates or frees device memory, never
- * synchronises and keeps no mutable global state, so calls may be captured in a CUDA graph and
- * issued from several threads or streams at once. All buffers are owned by the caller and must
+ * synchronises and keeps no mutable global state, so the codec, prep, GEMV and GEMM calls may be
+ * captured in a CUDA graph and issued from several threads or streams at once. All buffers are owned by the caller and must
  * stay alive until the stream has passed the call.
  *
  * Each declaration names the interface of the reference project (tfp8, Turing NVRTC kernels
@@ -137,10 +137,10 @@ TFP8B_API int tfp8b_gemm(const void* x16, const float* xs, const uint8_t* codes,
 /* The whole linear layer for any M >= 1 in one call that allocates nothing:
  *   y = x @ dequant(codes).T + bias   (activation prep, then the tile GEMM)
  * This entry point has no counterpart in the reference. It exists for callers that cannot obtain
- * device memory at the moment they need the layer: code that runs while a stream is being
- * captured, serving loops in which an allocation would stall every other stream of the device,
- * and hosts that bind this library through a foreign-function interface without a CUDA allocator
- * of their own. The prepared activations, which tfp8b_prep / tfp8b_gemm keep in caller memory,
+ * device memory at the moment they need the layer: serving loops in which an allocation would
+ * stall every other stream of the device, processes whose device-memory budget was fixed at
+ * start-up, and hosts that bind this library through a foreign-function interface without a
+ * CUDA allocator of their own. The prepared activations, which tfp8b_prep / tfp8b_gemm keep in caller memory,
  * live here in an 8 MiB array inside the library (present on every GPU that loads it, until the
  * process ends).
  *   Limits: M <= 8192 and M * K <= 4 Mi values per call; larger calls are refused with

@@ -1,9 +1,9 @@
 """The allocation-free entry point, tfp8b_linear_static, against the ordinary pair
 tfp8b_prep + tfp8b_gemm.
 
-Some users of the library cannot allocate device memory where they call it (inside a stream
-capture, in a serving loop that must not stall the device, from a host runtime without a CUDA
-allocator). For them the library keeps the GEMM's prepared activations in a fixed array of its
+Some users of the library cannot allocate device memory where they call it (a serving loop that
+must not stall the device, a process with a fixed device-memory budget, a host runtime without a
+CUDA allocator). For them the library keeps the GEMM's prepared activations in a fixed array of its
 own. This file checks, through the C ABI and on two calls in a row that leave different contents
 in that array, that the result is bit-identical to the path that uses caller-allocated buffers,
 and that oversized calls are refused. It is collected last on purpose: a run that stops at the
