@@ -357,6 +357,42 @@ def extra_measurements(args, device, peaks, world):
     return out
 
 
+def run_probe(args):
+    """`--probe gemm:M,N,K,G` / `--probe gemv:M,N,K,G`: a few launches of one kernel on one shape
+    (a small, self-ending case for profiler captures). Prints one JSON line with the timing."""
+    from tfp8 import _ext, synth
+    kind, dims = args.probe.split(":")
+    M, N, K, G = (int(v) for v in dims.split(","))
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    lib = _ext.load()
+    copies = max(1, min(8, int(2.2 * 126e6 / (N * K)) + 1))
+    qs = [synth.random_codes(N, K, torch.float8_e4m3fn, seed=c).to(device) for c in range(copies)]
+    ng = K // G
+    sc = torch.randint(110, 118, (N, ng), dtype=torch.uint8, device=device) if ng > 1 else torch.full((N, 1), 2.0 ** -13, device=device)
+    skind = 1 if ng > 1 else 0
+    x = synth.activations(M, K).to(device)
+    y = torch.empty(M, N, dtype=torch.float16, device=device)
+    x16 = torch.empty(M, K, dtype=torch.float16, device=device)
+    xs = torch.empty(M, dtype=torch.float32, device=device)
+    st = lambda: torch.cuda.current_stream().cuda_stream
+    lib.tfp8b_prep(x.data_ptr(), 0, x16.data_ptr(), xs.data_ptr(), M, K, st())
+
+    def step():
+        for q in qs:
+            if kind == "gemm":
+                rc = lib.tfp8b_gemm(x16.data_ptr(), xs.data_ptr(), q.data_ptr(), sc.data_ptr(), skind, None, y.data_ptr(), 0,
+                                    M, N, K, G, 0, st())
+            else:
+                rc = lib.tfp8b_gemv_ex(x.data_ptr(), 0, q.data_ptr(), sc.data_ptr(), skind, None, y.data_ptr(), 0, M, N, K, G, 0,
+                                       0, st())
+            assert rc == 0, lib.tfp8b_last_error_string()
+    sec = time_eager(step, args.steps, args.warmup) / copies
+    fl = 2.0 * M * N * K
+    print(json.dumps({"probe": args.probe, "copies": copies, "us_per_launch": sec * 1e6, "tflops": fl / sec / 1e12,
+                      "gbs": gemv_bytes(M, N, K, G) / sec / 1e9}))
+
+
 def run_reference(args, rank, world):
     """The reference's own CPU implementation of the path on the host cores, same metric."""
     if rank != 0:
@@ -379,11 +415,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--quick", action="store_true", help="headline only: skip the per-shape / GEMM / codec tables")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--probe", default=None, help="gemm:M,N,K,G or gemv:M,N,K,G -- a few launches of one kernel (profiling)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.probe:
+        run_probe(args)
+        return
     if args.impl == "reference":
         line = run_reference(args, rank, world)
         if line is not None:

@@ -14,12 +14,12 @@
 //                and one of the activation tile (BN x 64 fp16, 128-byte swizzle); no multicast;
 //   warp 1       tensor-memory allocation; one thread issues tcgen05.mma (kind::f16, M = 128,
 //                N = BN, K = 16) four times per stage and tcgen05.commit's the stage free;
-//   warps 2..9   decode: 16 codes per thread per step to fp16 (two codes per conversion
+//   warps 2..17  decode: 16 codes per thread per step to fp16 (two codes per conversion
 //                instruction), the K-group scale folded in as scale / rowmax (a packed fp16
 //                multiply when the ratio is a power of two, else an FP32 multiply with one fp16
 //                rounding), written in the 128-byte-swizzled K-major layout the MMA reads;
 //                fence.proxy.async, then an mbarrier arrive;
-//   warps 10..13 epilogue: tcgen05.ld the FP32 accumulators, apply smax[n], xs[m], bias[n], round
+//   warps 18..21 epilogue: tcgen05.ld the FP32 accumulators, apply smax[n], xs[m], bias[n], round
 //                once to the output type and store (32 lanes = 32 consecutive n per m).
 // No fp16 copy of the weights ever exists outside shared memory. Every mbarrier wait is bounded;
 // a wait that runs out sets a status bit, and the thread keeps walking its loops without waiting
@@ -30,8 +30,12 @@ namespace tfp8b {
 
 constexpr int GM_BM = 128;          // weight rows per tile = UMMA M = TMEM lanes
 constexpr int GM_BK = 64;           // K per stage: one 128-byte swizzle atom of fp16
-constexpr int GM_DEC_WARPS = 8;
+#ifndef TFP8B_GM_DEC_WARPS
+#define TFP8B_GM_DEC_WARPS 16
+#endif
+constexpr int GM_DEC_WARPS = TFP8B_GM_DEC_WARPS;   // 8: two rows per thread and stage; 16: one
 constexpr int GM_DEC_THREADS = GM_DEC_WARPS * 32;
+constexpr int GM_ROWS_PER_THREAD = 512 / GM_DEC_THREADS;   // 128 rows x 4 chunks per stage
 constexpr int GM_EPI_WARP0 = 2 + GM_DEC_WARPS;
 constexpr int GM_THREADS = (GM_EPI_WARP0 + 4) * 32;
 constexpr int GM_MAX_STAGES = 8;
@@ -101,10 +105,45 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-// max over one row's K-group scales, entries [g0, g1)
+// max over one row's K-group scales, entries [g0, g1). The loads are independent and issued in
+// batches (16-byte vectors where the row allows it): a one-load-at-a-time loop costs an L2 round
+// trip per scale, which for 256 groups is longer than the tile's whole main loop.
 __device__ __forceinline__ float row_scale_max(const void* scale, size_t row_off, int g0, int g1, int kind) {
+    const int esz = kind == TFP8B_SCALE_UE8M0 ? 1 : 4;
+    const uint8_t* base = reinterpret_cast<const uint8_t*>(scale) + (row_off + g0) * esz;
+    const int n = g1 - g0;
+    const int per = 16 / esz;                                   // scales per 16-byte vector
     float mx = 0.f;
-    for (int gi = g0; gi < g1; ++gi) mx = fmaxf(mx, load_scale(scale, row_off + gi, kind));
+    uint32_t bmax = 0u;                                         // UE8M0: max of the exponent bytes (255 = NaN wins)
+    int i = 0;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) {
+        const uint4* v = reinterpret_cast<const uint4*>(base);
+        const int nv = n / per;
+        for (int j = 0; j < nv; j += 8) {
+            uint4 t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) t[u] = j + u < nv ? __ldg(v + j + u) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t w[4] = {t[u].x, t[u].y, t[u].z, t[u].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (kind == TFP8B_SCALE_UE8M0) {
+                        const uint32_t m4 = __vmaxu4(w[e], __byte_perm(w[e], 0u, 0x4321));   // pairwise byte maxima
+                        bmax = max(bmax, max(m4 & 0xFFu, (m4 >> 16) & 0xFFu));
+                    } else {
+                        mx = fmaxf(mx, __uint_as_float(w[e]));
+                    }
+                }
+            }
+        }
+        i = nv * per;
+    }
+    for (; i < n; ++i) {
+        if (kind == TFP8B_SCALE_UE8M0) bmax = max(bmax, static_cast<uint32_t>(base[i]));
+        else mx = fmaxf(mx, reinterpret_cast<const float*>(base)[i]);
+    }
+    if (kind == TFP8B_SCALE_UE8M0) mx = n > 0 ? ue8m0_to_f32(bmax) : 0.f;
     return mx;
 }
 
@@ -160,18 +199,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             // Several tiles: the CTAs of the other tiles read the same stripe from L2 next.
             const uint64_t pol_w = p.m_tiles == 1 ? l2_policy_evict_first() : l2_policy_evict_normal();
             const uint64_t pol_x = l2_policy_evict_last();
-            int it = 0;
-            bool ok = true;
+            int slot = 0;
+            uint32_t phase = 1;               // ring position (no divisions): the first pass over the ring does not wait
+            bool ok = true, first_pass = true;
             for (int i = 0; i < my_tiles && ok; ++i) {
                 const int m0 = tile_m0(i), n0 = tile_n0(i);
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int slot = it % S;
-                    if (it >= S && !mbar_wait(smem_u32(&hd->empty[slot]), ((it / S) - 1) & 1, STATUS_GEMM_WAIT)) { ok = false; break; }
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!first_pass && !mbar_wait(smem_u32(&hd->empty[slot]), phase, STATUS_GEMM_WAIT)) { ok = false; break; }
                     uint8_t* st = stages + static_cast<size_t>(slot) * p.stage_bytes;
                     const uint32_t bar = smem_u32(&hd->full_raw[slot]);
                     mbar_expect_tx(bar, static_cast<uint32_t>(GM_RAW_BYTES + x_bytes));
                     tma_load_2d(smem_u32(st + GM_A_BYTES), &tm_x, kb * GM_BK, m0, bar, pol_x);
                     tma_load_2d(smem_u32(st + GM_A_BYTES + x_bytes), &tm_w, kb * GM_BK, n0, bar, pol_w);
+                    if (++slot == S) { slot = 0; phase ^= 1u; first_pass = false; }
                 }
             }
         }
@@ -181,7 +221,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         if (lane == 0) {
             // D fp32, A/B fp16, both K-major, N = BN, M = 128
             const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(p.BN >> 3) << 17) | (static_cast<uint32_t>(GM_BM >> 4) << 24);
-            int it = 0;
+            int slot = 0;
+            uint32_t phase = 0;
             bool ok = true;
             for (int i = 0; i < my_tiles && ok; ++i) {
                 const int buf = i & 1;
@@ -190,9 +231,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(buf * p.BN);
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int slot = it % S;
-                    const uint32_t par = (it / S) & 1;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    const uint32_t par = phase;
                     ok = mbar_wait(smem_u32(&hd->full_raw[slot]), par, STATUS_GEMM_WAIT) &&
                          mbar_wait(smem_u32(&hd->full_a[slot]), par, STATUS_GEMM_WAIT);
                     if (!ok) break;
@@ -204,6 +244,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     for (int kk = 0; kk < GM_BK / 16; ++kk)
                         tc_mma_f16(tmem_acc, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
                     tc_commit(smem_u32(&hd->empty[slot]));
+                    if (++slot == S) { slot = 0; phase ^= 1u; }
                 }
                 if (ok) tc_commit(smem_u32(&hd->acc_full[buf]));
             }
@@ -211,76 +252,107 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         __syncwarp();
     } else if (warp < GM_EPI_WARP0) {
         // ---------------------------------------------------------------- decode warps
-        const int td = threadIdx.x - 64;             // 0..255
+        constexpr int RPT = GM_ROWS_PER_THREAD;
+        constexpr int RSTEP = GM_BM / RPT;           // distance between a thread's rows
+        const int td = threadIdx.x - 64;             // 0 .. GM_DEC_THREADS-1
         const int c = td & 3;                        // 16-code chunk of the 64-wide K block
-        const int r0 = td >> 2;                      // rows r0 and r0 + 64
-        int it = 0;
+        const int r0 = td >> 2;                      // rows r0 (+ RSTEP)
+        int slot = 0;
+        uint32_t phase = 0;
         bool ok = true;
+        constexpr int PF = 8;                        // k-blocks whose scale ratios are fetched ahead
         for (int i = 0; i < my_tiles; ++i) {
             const int n0 = tile_n0(i);
-            float binv[2] = {1.f, 1.f};
-            size_t srow[2];
-            srow[0] = static_cast<size_t>(min(n0 + r0, p.N - 1)) * ng;
-            srow[1] = static_cast<size_t>(min(n0 + r0 + 64, p.N - 1)) * ng;
-            if (ng > 1) {
-                // row maxima of the K-group scales: thread pair (2r, 2r+1) scans row r in halves
-                const int row = td >> 1, half = td & 1;
-                const size_t off = static_cast<size_t>(min(n0 + row, p.N - 1)) * ng;
-                const int mid = ng >> 1;
-                float mx = row_scale_max(p.scale, off, half ? mid : 0, half ? ng : mid, p.scale_kind);
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                if (!half) hd->binv[i & 1][row] = mx > 0.f ? 1.f / mx : 0.f;
-                named_barrier_sync(1, GM_DEC_THREADS);
-                binv[0] = hd->binv[i & 1][r0];
-                binv[1] = hd->binv[i & 1][r0 + 64];
+            float binv[RPT];
+            size_t srow[RPT];
+#pragma unroll
+            for (int h2 = 0; h2 < RPT; ++h2) {
+                binv[h2] = 1.f;
+                srow[h2] = static_cast<size_t>(min(n0 + r0 + RSTEP * h2, p.N - 1)) * ng;
             }
-            for (int kb = 0; kb < nkb; ++kb, ++it) {
-                const int slot = it % S;
-                float ratio[2] = {1.f, 1.f};
-                if (ng > 1) {
-                    const int gi = min((kb * GM_BK + c * 16) / p.G, ng - 1);
-                    ratio[0] = load_scale(p.scale, srow[0] + gi, p.scale_kind) * binv[0];
-                    ratio[1] = load_scale(p.scale, srow[1] + gi, p.scale_kind) * binv[1];
+            if (ng > 1) {
+                // row maxima of the K-group scales: GM_DEC_THREADS / 128 threads share a row
+                constexpr int TPR = GM_DEC_THREADS / GM_BM;
+                const int row = td / TPR, part = td % TPR;
+                const size_t off = static_cast<size_t>(min(n0 + row, p.N - 1)) * ng;
+                const int g0 = (ng * part) / TPR, g1 = (ng * (part + 1)) / TPR;
+                float mx = row_scale_max(p.scale, off, g0, g1, p.scale_kind);
+#pragma unroll
+                for (int o = 1; o < TPR; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                if (part == 0) hd->binv[i & 1][row] = mx > 0.f ? 1.f / mx : 0.f;
+                named_barrier_sync(1, GM_DEC_THREADS);
+#pragma unroll
+                for (int h2 = 0; h2 < RPT; ++h2) binv[h2] = hd->binv[i & 1][r0 + RSTEP * h2];
+            }
+            // scale / rowmax of this thread's two rows for PF k-blocks, loaded one batch ahead of
+            // their use: a global load in the k-block loop itself would stall every decode warp
+            // for an L2 round trip per stage.
+            auto load_ratios = [&](int kb0, float (*dst)[RPT]) {
+#pragma unroll
+                for (int j = 0; j < PF; ++j) {
+#pragma unroll
+                    for (int h2 = 0; h2 < RPT; ++h2) dst[j][h2] = 1.f;
+                    if (ng > 1 && kb0 + j < nkb) {
+                        const int gi = min(((kb0 + j) * GM_BK + c * 16) / p.G, ng - 1);
+#pragma unroll
+                        for (int h2 = 0; h2 < RPT; ++h2) dst[j][h2] = load_scale(p.scale, srow[h2] + gi, p.scale_kind) * binv[h2];
+                    }
                 }
-                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->full_raw[slot]), (it / S) & 1, STATUS_GEMM_WAIT));
-                if (!ok) continue;
-                uint8_t* st = stages + static_cast<size_t>(slot) * p.stage_bytes;
-                const uint8_t* raw = st + GM_A_BYTES + x_bytes;
+            };
+            float rcur[PF][RPT], rnext[PF][RPT];
+            load_ratios(0, rcur);
+            for (int kb0 = 0; kb0 < nkb; kb0 += PF) {
+                load_ratios(kb0 + PF, rnext);
 #pragma unroll
-                for (int h2 = 0; h2 < 2; ++h2) {
-                    const int r = r0 + 64 * h2;
-                    const uint4 q = *reinterpret_cast<const uint4*>(raw + r * GM_BK + c * 16);
-                    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-                    uint32_t h[8];
+                for (int j = 0; j < PF; ++j) {
+                    if (kb0 + j >= nkb) break;
+                    const int cur = slot;
+                    const uint32_t par = phase;
+                    if (++slot == S) { slot = 0; phase ^= 1u; }
+                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->full_raw[cur]), par, STATUS_GEMM_WAIT));
+                    if (!ok) continue;
+                    uint8_t* st = stages + static_cast<size_t>(cur) * p.stage_bytes;
+                    const uint8_t* raw = st + GM_A_BYTES + x_bytes;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) dec4<FMT, false>(w[j], h[2 * j], h[2 * j + 1]);
-                    const float rt = ratio[h2];
-                    if (rt != 1.f) {
-                        const uint32_t rb = __float_as_uint(rt);
-                        if ((rb & 0x007FFFFFu) == 0u && rb >= 0x38800000u && rb <= 0x47000000u) {
-                            // power of two inside fp16's normal range: one packed multiply, same rounding
-                            const __half2 r2 = __float2half2_rn(rt);
+                    for (int h2 = 0; h2 < RPT; ++h2) {
+                        const int r = r0 + RSTEP * h2;
+                        const uint4 q = *reinterpret_cast<const uint4*>(raw + r * GM_BK + c * 16);
+                        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                        uint32_t h[8];
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                __half2 o = __hmul2(*reinterpret_cast<__half2*>(&h[j]), r2);
-                                h[j] = *reinterpret_cast<uint32_t*>(&o);
-                            }
-                        } else {
+                        for (int e = 0; e < 4; ++e) dec4<FMT, false>(w[e], h[2 * e], h[2 * e + 1]);
+                        const float rt = rcur[j][h2];
+                        if (rt != 1.f) {
+                            const uint32_t rb = __float_as_uint(rt);
+                            if ((rb & 0x007FFFFFu) == 0u && rb >= 0x38800000u && rb <= 0x47000000u) {
+                                // power of two inside fp16's normal range: one packed multiply, same rounding
+                                const __half2 r2 = __float2half2_rn(rt);
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                float2 f = __half22float2(*reinterpret_cast<__half2*>(&h[j]));
-                                __half2 o = __floats2half2_rn(f.x * rt, f.y * rt);
-                                h[j] = *reinterpret_cast<uint32_t*>(&o);
+                                for (int e = 0; e < 8; ++e) {
+                                    __half2 o = __hmul2(*reinterpret_cast<__half2*>(&h[e]), r2);
+                                    h[e] = *reinterpret_cast<uint32_t*>(&o);
+                                }
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    float2 f = __half22float2(*reinterpret_cast<__half2*>(&h[e]));
+                                    __half2 o = __floats2half2_rn(f.x * rt, f.y * rt);
+                                    h[e] = *reinterpret_cast<uint32_t*>(&o);
+                                }
                             }
                         }
+                        uint8_t* arow = st + r * 128;
+                        *reinterpret_cast<uint4*>(arow + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                        *reinterpret_cast<uint4*>(arow + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
                     }
-                    uint8_t* arow = st + r * 128;
-                    *reinterpret_cast<uint4*>(arow + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-                    *reinterpret_cast<uint4*>(arow + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+                    fence_proxy_async_smem();        // generic-proxy stores -> visible to the tensor core
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&hd->full_a[cur]));
                 }
-                fence_proxy_async_smem();        // generic-proxy stores -> visible to the tensor core
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&hd->full_a[slot]));
+#pragma unroll
+                for (int j = 0; j < PF; ++j)
+#pragma unroll
+                    for (int h2 = 0; h2 < RPT; ++h2) rcur[j][h2] = rnext[j][h2];
             }
         }
     } else {
