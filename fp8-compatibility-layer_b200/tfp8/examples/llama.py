@@ -1,0 +1,236 @@
+"""Llama-architecture decoder used as the serving harness of the benchmark (random weights).
+
+Same role as the reference's examples/demo_llm.py: a plain decoder (RMSNorm, RoPE, grouped-query
+attention through torch SDPA, SwiGLU) whose projections `prepare_model` turns into FP8Linear.
+Differences that matter on B200: a static KV cache and a device-side position, so that one decode
+step can be captured in a CUDA graph and replayed (at batch 1 a token is about a millisecond of
+kernels: launch overhead would dominate an eager loop); Megatron-style tensor parallelism (heads
+and FFN columns split across ranks, one all-reduce after o_proj and one after down_proj); and the
+`independent_input` hint on K, V and up projections, whose activations are not produced by the
+kernel launched just before them.
+"""
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..config import FP8Config
+from ..linear import FP8Linear
+from ..parallel import ColumnParallelFP8Linear, RowParallelFP8Linear
+
+
+@dataclass
+class LlamaConfig:
+    n_layers: int = 32
+    d_model: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    ffn: int = 14336
+    vocab: int = 128256
+    rope_theta: float = 500000.0
+    eps: float = 1e-5
+    max_seq: int = 2304
+
+    @property
+    def head_dim(self):
+        return self.d_model // self.n_heads
+
+
+LLAMA3_8B = LlamaConfig()
+TINY = LlamaConfig(n_layers=2, d_model=256, n_heads=8, n_kv_heads=2, ffn=512, vocab=1000, max_seq=64)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, d, eps, device=None, dtype=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(d, device=device, dtype=dtype))
+        self.eps = eps
+
+    def forward(self, x):
+        v = x.float()
+        return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype) * self.weight
+
+
+def _rope(x, cos, sin):
+    """x [B, H, T, hd]; cos / sin [T, hd/2] (rotate-half convention)."""
+    x1, x2 = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2:]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
+
+
+class Block(nn.Module):
+    def __init__(self, cfg: LlamaConfig, tp: int, device, dtype):
+        super().__init__()
+        d, hd = cfg.d_model, cfg.head_dim
+        self.cfg, self.tp = cfg, tp
+        self.h_local, self.kv_local = cfg.n_heads // tp, max(1, cfg.n_kv_heads // tp)
+        mk = lambda i, o: nn.Linear(i, o, bias=False, device=device, dtype=dtype)
+        self.q_proj, self.k_proj, self.v_proj = mk(d, cfg.n_heads * hd), mk(d, cfg.n_kv_heads * hd), mk(d, cfg.n_kv_heads * hd)
+        self.o_proj = mk(cfg.n_heads * hd, d)
+        self.gate_proj, self.up_proj, self.down_proj = mk(d, cfg.ffn), mk(d, cfg.ffn), mk(cfg.ffn, d)
+        self.input_layernorm = RMSNorm(d, cfg.eps, device, dtype)
+        self.post_attention_layernorm = RMSNorm(d, cfg.eps, device, dtype)
+        self.k_cache = self.v_cache = None
+
+    def alloc_cache(self, batch, device, dtype):
+        shape = (batch, self.kv_local, self.cfg.max_seq, self.cfg.head_dim)
+        self.k_cache = torch.zeros(shape, device=device, dtype=dtype)
+        self.v_cache = torch.zeros(shape, device=device, dtype=dtype)
+
+    def forward(self, x, pos, cos, sin, mask):
+        """x [B, T, d]; pos int64 [T] (device) = cache positions of these tokens; mask additive
+        [T, max_seq] or None (prefill from position 0 uses the causal flag)."""
+        B, T, _ = x.shape
+        hd = self.cfg.head_dim
+        h = self.input_layernorm(x)
+        q = self.q_proj(h).to(x.dtype).view(B, T, self.h_local, hd).transpose(1, 2)
+        k = self.k_proj(h).to(x.dtype).view(B, T, self.kv_local, hd).transpose(1, 2)
+        v = self.v_proj(h).to(x.dtype).view(B, T, self.kv_local, hd).transpose(1, 2)
+        q, k = _rope(q, cos, sin), _rope(k, cos, sin)
+        self.k_cache.index_copy_(2, pos, k)
+        self.v_cache.index_copy_(2, pos, v)
+        if mask is None:
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        else:
+            a = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask, enable_gqa=True)
+        x = x + self.o_proj(a.transpose(1, 2).reshape(B, T, self.h_local * hd)).to(x.dtype)
+        h = self.post_attention_layernorm(x)
+        return x + self.down_proj(F.silu(self.gate_proj(h)) * self.up_proj(h)).to(x.dtype)
+
+
+class Llama(nn.Module):
+    def __init__(self, cfg: LlamaConfig = LLAMA3_8B, device="cpu", dtype=torch.float16, tp=1):
+        super().__init__()
+        self.cfg, self.tp = cfg, tp
+        self.embed = nn.Embedding(cfg.vocab, cfg.d_model, device=device, dtype=dtype)
+        self.layers = nn.ModuleList([Block(cfg, tp, device, dtype) for _ in range(cfg.n_layers)])
+        self.norm = RMSNorm(cfg.d_model, cfg.eps, device, dtype)
+        self.lm_head = nn.Linear(cfg.d_model, cfg.vocab, bias=False, device=device, dtype=dtype)
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=device).float() / cfg.head_dim))
+        ang = torch.arange(cfg.max_seq, device=device).float()[:, None] * inv[None, :]
+        self.register_buffer("cos", ang.cos(), persistent=False)
+        self.register_buffer("sin", ang.sin(), persistent=False)
+
+    def alloc_cache(self, batch):
+        p = self.embed.weight
+        for l in self.layers:
+            l.alloc_cache(batch, p.device, p.dtype)
+
+    def forward(self, tokens, pos, prefill=False):
+        """tokens int64 [B, T]; pos int64 [T] on the same device. Returns logits [B, T, vocab]."""
+        x = self.embed(tokens)
+        cos, sin = self.cos[pos], self.sin[pos]
+        mask = None
+        if not prefill:
+            seq = torch.arange(self.cfg.max_seq, device=pos.device)
+            mask = torch.where(seq[None, :] <= pos[:, None], 0.0, float("-inf")).to(x.dtype)
+        for l in self.layers:
+            x = l(x, pos, cos, sin, mask)
+        return self.lm_head(self.norm(x))
+
+
+def build_fp8_llama(cfg: LlamaConfig, device, dtype=torch.float16, fp8: FP8Config | None = None, group=None, seed=0,
+                    sigma=0.02):
+    """Random-init (N(0, sigma^2)) decoder with every projection quantized to FP8Linear, built one
+    layer at a time so the full-precision model never exists. With a process group the layers are
+    quantized first and then sharded Megatron-style (every rank draws the same full weights)."""
+    fp8 = fp8 or FP8Config(profile="llm_safe", nan_check=False)
+    world = dist.get_world_size(group) if (group is not None or (dist.is_available() and dist.is_initialized())) else 1
+    if cfg.n_heads % world or (cfg.n_kv_heads % world and world % cfg.n_kv_heads) or cfg.ffn % world:
+        raise ValueError(f"tensor-parallel size {world} does not divide the model")
+    with torch.device("meta"):
+        model = Llama(cfg, dtype=dtype, tp=world)
+    g = torch.Generator(device=device).manual_seed(seed)
+    rnd = lambda *s: (torch.randn(*s, generator=g, device=device) * sigma).to(dtype)
+
+    def quantized(out_f, in_f, kind, independent=False):
+        lin = nn.Linear(in_f, out_f, bias=False, device=device, dtype=dtype)
+        lin.weight.data = rnd(out_f, in_f)
+        q = FP8Linear.from_linear(lin, fp8.fmt, fp8.weight_group, fp8.pow2_scale, nan_check=fp8.nan_check,
+                                  scale_format=fp8.scale_format)
+        del lin
+        if world > 1:
+            q = (ColumnParallelFP8Linear.from_full(q, group, gather_output=False) if kind == "col"
+                 else RowParallelFP8Linear.from_full(q, group, input_is_parallel=True))
+            q.local.independent_input = independent
+        else:
+            q.independent_input = independent
+        return q
+
+    d, hd = cfg.d_model, cfg.head_dim
+    for blk in model.layers:
+        blk.q_proj = quantized(cfg.n_heads * hd, d, "col")
+        blk.k_proj = quantized(cfg.n_kv_heads * hd, d, "col", independent=True)     # same input as q_proj
+        blk.v_proj = quantized(cfg.n_kv_heads * hd, d, "col", independent=True)
+        blk.o_proj = quantized(d, cfg.n_heads * hd, "row")
+        blk.gate_proj = quantized(cfg.ffn, d, "col")
+        blk.up_proj = quantized(cfg.ffn, d, "col", independent=True)                # same input as gate_proj
+        blk.down_proj = quantized(d, cfg.ffn, "row")
+        blk.input_layernorm = RMSNorm(d, cfg.eps, device, dtype)
+        blk.post_attention_layernorm = RMSNorm(d, cfg.eps, device, dtype)
+    model.embed = nn.Embedding(cfg.vocab, d, device=device, dtype=dtype)
+    model.embed.weight.data = rnd(cfg.vocab, d)
+    model.norm = RMSNorm(d, cfg.eps, device, dtype)
+    model.lm_head = nn.Linear(d, cfg.vocab, bias=False, device=device, dtype=dtype)    # stays fp16 (planner rule)
+    model.lm_head.weight.data = rnd(cfg.vocab, d)
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, device=device).float() / hd))
+    ang = torch.arange(cfg.max_seq, device=device).float()[:, None] * inv[None, :]
+    model.register_buffer("cos", ang.cos(), persistent=False)
+    model.register_buffer("sin", ang.sin(), persistent=False)
+    return model
+
+
+class DecodeRunner:
+    """Prefill, then greedy decode with the whole step (all layers, lm_head, argmax, position bump)
+    captured in one CUDA graph."""
+
+    def __init__(self, model: Llama, batch: int):
+        self.model, self.batch = model, batch
+        model.alloc_cache(batch)
+        dev = model.embed.weight.device
+        self.tok = torch.zeros(batch, 1, dtype=torch.int64, device=dev)
+        self.pos = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.graph = None
+
+    @torch.no_grad()
+    def prefill(self, tokens):
+        T = tokens.shape[1]
+        pos = torch.arange(T, device=tokens.device)
+        logits = self.model(tokens, pos, prefill=True)
+        self.tok.copy_(logits[:, -1:].argmax(-1))
+        self.pos.fill_(T)
+        return logits
+
+    @torch.no_grad()
+    def _step(self):
+        logits = self.model(self.tok, self.pos, prefill=False)
+        self.tok.copy_(logits[:, -1:].argmax(-1))
+        self.pos.add_(1)
+
+    @torch.no_grad()
+    def capture(self, warmup=3):
+        keep_tok, keep_pos = self.tok.clone(), self.pos.clone()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(warmup):                  # un-captured calls first (kernel opt-ins, NaN-check calls)
+                self._step()
+        torch.cuda.current_stream().wait_stream(s)
+        self.tok.copy_(keep_tok); self.pos.copy_(keep_pos)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._step()
+        self.tok.copy_(keep_tok); self.pos.copy_(keep_pos)
+
+    @torch.no_grad()
+    def decode(self, steps):
+        out = []
+        for _ in range(steps):
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self._step()
+            out.append(self.tok.clone())
+        return torch.cat(out, dim=1)

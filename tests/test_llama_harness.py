@@ -1,0 +1,25 @@
+"""The serving harness on CPU with a tiny configuration: a decode step through the static KV cache
+must reproduce what a longer prefill computes for the same position (cache write, RoPE at the
+device-side position and the additive mask are what a CUDA-graph decode loop relies on)."""
+import torch
+
+from tfp8 import FP8Config
+from tfp8.examples.llama import TINY, DecodeRunner, build_fp8_llama
+from tfp8.linear import FP8Linear
+
+
+def test_decode_step_matches_prefill():
+    torch.manual_seed(0)
+    model = build_fp8_llama(TINY, "cpu", dtype=torch.float32, fp8=FP8Config(min_features=64, nan_check=False))
+    assert sum(isinstance(m, FP8Linear) for m in model.modules()) == 7 * TINY.n_layers
+    assert isinstance(model.lm_head, torch.nn.Linear)
+    toks = torch.randint(0, TINY.vocab, (2, 9))
+    full = DecodeRunner(model, 2).prefill(toks)                      # logits for positions 0..8
+    run = DecodeRunner(model, 2)
+    run.prefill(toks[:, :8])
+    run.tok.copy_(toks[:, 8:9])                                      # feed the true 9th token
+    logits = model(run.tok, run.pos, prefill=False)
+    assert torch.allclose(logits[:, 0], full[:, 8], rtol=1e-3, atol=1e-3)          # fp16 projection outputs
+    out = run.decode(3)
+    assert out.shape == (2, 3) and int(run.pos) == 8 + 3
+    assert model.layers[0].k_proj.independent_input and not model.layers[0].q_proj.independent_input
