@@ -274,8 +274,14 @@ def run_ours(args, rank, world, local_rank):
                                          "note": "same pass without TFP8B_GEMV_INDEPENDENT_IO: every call waits for "
                                                  "its predecessor before it reads activations"}},
     }
-    if not args.quick and world == 1:
-        line["extra"] = extra_measurements(args, device, peaks, world)
+    if not args.quick:
+        line["extra"] = extra_measurements(args, device, peaks, world) if world == 1 else {}
+        del layers, launches, xs, outs, hx, hy, dx
+        torch.cuda.empty_cache()
+        if world > 1:
+            line["extra"]["tp_gemm"] = tp_gemm_measurements(device, peaks, world, rank)
+        if not args.no_llama:
+            line["extra"]["llama_decode"] = llama_decode_measurements(device, peaks, world)
     if rank == 0 and world == 1:
         line["cpu_baseline"] = cpu_baseline(args.cpu_seconds)
     return line
@@ -357,6 +363,87 @@ def extra_measurements(args, device, peaks, world):
     return out
 
 
+def llama_decode_measurements(device, peaks, world, batches=(1, 4, 8), prompt=2048, new_tokens=256):
+    """Config 5: Llama-3-8B architecture, random weights, every projection FP8Linear (E4M3FN,
+    per-channel); a `prompt`-token prefill, then `new_tokens` greedy decode steps replayed from a
+    CUDA graph, per batch size. With world > 1 the model is tensor-parallel over all ranks
+    (Megatron layout, NCCL all-reduce after o_proj and down_proj)."""
+    from tfp8.examples.llama import LLAMA3_8B, DecodeRunner, build_fp8_llama
+    from tfp8.linear import FP8Linear
+    t0 = time.perf_counter()
+    model = build_fp8_llama(LLAMA3_8B, device, torch.float16)
+    torch.cuda.synchronize()
+    build_s = time.perf_counter() - t0
+    code_bytes = sum(m.qweight.numel() for m in model.modules() if isinstance(m, FP8Linear))
+    stream_bytes = code_bytes + model.lm_head.weight.numel() * 2 // 1          # per rank, per decoded token
+    rows = []
+    warm = DecodeRunner(model, 1)                                   # one-time costs (library handles, kernel opt-ins)
+    warm.prefill(torch.randint(0, LLAMA3_8B.vocab, (1, 128), device=device))
+    del warm
+    for B in batches:
+        g = torch.Generator(device=device).manual_seed(100 + B)
+        toks = torch.randint(0, LLAMA3_8B.vocab, (B, prompt), generator=g, device=device)
+        run = DecodeRunner(model, B)
+        barrier(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); run.prefill(toks); e1.record(); torch.cuda.synchronize()
+        prefill_s = max_over_ranks(e0.elapsed_time(e1) / 1e3, world, device)
+        run.capture()
+        barrier(world)
+        e0.record(); out = run.decode(new_tokens); e1.record(); torch.cuda.synchronize()
+        dec_s = max_over_ranks(e0.elapsed_time(e1) / 1e3, world, device)
+        ms_tok = dec_s / new_tokens * 1e3
+        rows.append({"batch": B, "tp": world, "prefill_tokens": prompt, "prefill_ms": prefill_s * 1e3,
+                     "prefill_tok_s": B * prompt / prefill_s, "decode_tokens": new_tokens, "ms_per_step": ms_tok,
+                     "decode_tok_s": B * new_tokens / dec_s,
+                     "hbm_bound_ms_per_step": stream_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3,
+                     "frac_of_hbm_bound": stream_bytes / (peaks["hbm_gbs"] * 1e9) / (dec_s / new_tokens),
+                     "finite": bool(torch.isfinite(out.float()).all())})
+        del run
+        torch.cuda.empty_cache()
+    return {"model": "Llama-3-8B architecture, random N(0,0.02^2) fp16 weights, FP8 E4M3FN per-channel projections",
+            "fp8_code_bytes_per_rank": code_bytes, "bytes_streamed_per_token_per_rank": stream_bytes,
+            "build_seconds": build_s, "runs": rows}
+
+
+def tp_gemm_measurements(device, peaks, world, rank):
+    """Config 4: 28672 x 8192 E4M3FN weight with 32-wide UE8M0 K-groups, column-sharded across the
+    ranks, bf16 activations replicated, outputs all-gathered (NCCL). TFLOP/s of the whole job,
+    with and without the gather."""
+    from tfp8 import _ext, synth
+    lib = _ext.load()
+    N, K = synth.GROUP_GEMM_SHAPE
+    Nl = N // world
+    q = synth.random_codes(N, K, torch.float8_e4m3fn, seed=3)[rank * Nl:(rank + 1) * Nl].contiguous().to(device)
+    e8 = torch.randint(110, 118, (Nl, K // 32), dtype=torch.uint8, device=device)
+    st = lambda: torch.cuda.current_stream().cuda_stream
+    rows = []
+    for M in synth.PREFILL_M:
+        x = synth.activations(M, K, dtype=torch.bfloat16).to(device)
+        x16 = torch.empty(M, K, dtype=torch.float16, device=device)
+        xs = torch.empty(M, dtype=torch.float32, device=device)
+        y = torch.empty(M, Nl, dtype=torch.float16, device=device)
+        full = torch.empty(world * M, Nl, dtype=torch.float16, device=device)
+
+        def step(gather):
+            lib.tfp8b_prep(x.data_ptr(), 1, x16.data_ptr(), xs.data_ptr(), M, K, st())
+            rc = lib.tfp8b_gemm(x16.data_ptr(), xs.data_ptr(), q.data_ptr(), e8.data_ptr(), 1, None, y.data_ptr(), 0,
+                                M, Nl, K, 32, 0, st())
+            assert rc == 0, lib.tfp8b_last_error_string()
+            if gather and world > 1:
+                torch.distributed.all_gather_into_tensor(full, y)
+        barrier(world)
+        t_g = max_over_ranks(time_eager(lambda: step(True), 4, 3), world, device)
+        barrier(world)
+        t_n = max_over_ranks(time_eager(lambda: step(False), 4, 3), world, device)
+        fl = 2.0 * M * N * K
+        rows.append({"M": M, "N": N, "K": K, "G": 32, "tp": world, "ms_with_gather": t_g * 1e3, "ms_without_gather": t_n * 1e3,
+                     "tflops_with_gather": fl / t_g / 1e12, "tflops_without_gather": fl / t_n / 1e12,
+                     "frac_tensor_peak_all_gpus": fl / t_g / 1e12 / (world * peaks["bf16_tflops"])})
+        del x, x16, y, full
+    return rows
+
+
 def run_probe(args):
     """`--probe gemm:M,N,K,G` / `--probe gemv:M,N,K,G`: a few launches of one kernel on one shape
     (a small, self-ending case for profiler captures). Prints one JSON line with the timing."""
@@ -415,6 +502,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--quick", action="store_true", help="headline only: skip the per-shape / GEMM / codec tables")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--no-llama", action="store_true", help="skip the Llama-3-8B decode measurement")
     ap.add_argument("--probe", default=None, help="gemm:M,N,K,G or gemv:M,N,K,G -- a few launches of one kernel (profiling)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)

@@ -42,6 +42,8 @@ _SIGNATURES = {
     "tfp8b_gemm": ([_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_linear_static": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_epilogue": ([_P, _P, _P, _P, _I, _I, _I, _I, _P], _I),
+    "tfp8b_rope_kv_store": ([_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
+    "tfp8b_silu_mul": ([_P, _P, _I, ctypes.c_longlong, _I, _P], _I),
 }
 
 
@@ -316,3 +318,32 @@ def epilogue_into(y, acc, xs, bias, n0=0):
                                    yv.data_ptr(), _DT[y.dtype], M, n, y.shape[1], _stream(dev))
     _check(rc, "tfp8b_epilogue")
     return y
+
+
+# ------------------------------------------------------------------ decode-step helpers
+def rope_kv_store(qkv, pos, cos, sin, k_cache, v_cache, n_heads, n_kv_heads):
+    """Rotary embedding + KV-cache write for a fused QKV projection output [B, T, (H + 2 KV) * hd]
+    (f16 / bf16, contiguous). Returns Q as [B, H, T, hd]; K and V land in the caches
+    [B, KV, max_seq, hd] at positions `pos` (int64 [T], on the device)."""
+    dev = _need_cuda(qkv, pos, cos, sin, k_cache, v_cache)
+    B, T = qkv.shape[0], qkv.shape[1]
+    hd = k_cache.shape[-1]
+    q = torch.empty(B, n_heads, T, hd, dtype=qkv.dtype, device=qkv.device)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_rope_kv_store(qkv.data_ptr(), _DT[qkv.dtype], pos.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), B, T, n_heads, n_kv_heads,
+                                        hd, k_cache.shape[2], _stream(dev))
+    _check(rc, "tfp8b_rope_kv_store")
+    return q
+
+
+def silu_mul(gate_up):
+    """silu(gate) * up for a fused gate/up projection output [..., 2F] (f16 / bf16, contiguous)."""
+    dev = _need_cuda(gate_up)
+    F = gate_up.shape[-1] // 2
+    out = torch.empty(*gate_up.shape[:-1], F, dtype=gate_up.dtype, device=gate_up.device)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_silu_mul(gate_up.data_ptr(), out.data_ptr(), _DT[gate_up.dtype], gate_up.numel() // (2 * F), F,
+                                   _stream(dev))
+    _check(rc, "tfp8b_silu_mul")
+    return out

@@ -4,10 +4,9 @@ Same role as the reference's examples/demo_llm.py: a plain decoder (RMSNorm, RoP
 attention through torch SDPA, SwiGLU) whose projections `prepare_model` turns into FP8Linear.
 Differences that matter on B200: a static KV cache and a device-side position, so that one decode
 step can be captured in a CUDA graph and replayed (at batch 1 a token is about a millisecond of
-kernels: launch overhead would dominate an eager loop); Megatron-style tensor parallelism (heads
-and FFN columns split across ranks, one all-reduce after o_proj and one after down_proj); and the
-`independent_input` hint on K, V and up projections, whose activations are not produced by the
-kernel launched just before them.
+kernels: launch overhead would dominate an eager loop); fused QKV and gate/up projections (one
+weight stream and one launch each); and Megatron-style tensor parallelism (heads and FFN columns
+split across ranks, one all-reduce after o_proj and one after down_proj).
 """
 import math
 from dataclasses import dataclass
@@ -17,6 +16,7 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .. import _ext
 from ..config import FP8Config
 from ..linear import FP8Linear
 from ..parallel import ColumnParallelFP8Linear, RowParallelFP8Linear
@@ -50,8 +50,7 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x):
-        v = x.float()
-        return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype) * self.weight
+        return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)       # one fused kernel
 
 
 def _rope(x, cos, sin):
@@ -67,12 +66,16 @@ class Block(nn.Module):
         self.cfg, self.tp = cfg, tp
         self.h_local, self.kv_local = cfg.n_heads // tp, max(1, cfg.n_kv_heads // tp)
         mk = lambda i, o: nn.Linear(i, o, bias=False, device=device, dtype=dtype)
-        self.q_proj, self.k_proj, self.v_proj = mk(d, cfg.n_heads * hd), mk(d, cfg.n_kv_heads * hd), mk(d, cfg.n_kv_heads * hd)
+        # Fused projections, as most serving stacks store them: one weight stream and one launch for
+        # Q, K, V and one for gate, up. Rows are ordered rank by rank ([q_r | k_r | v_r], [gate_r | up_r])
+        # so that a column-parallel shard is a contiguous row block.
+        self.qkv_proj = mk(d, (cfg.n_heads + 2 * cfg.n_kv_heads) * hd)
         self.o_proj = mk(cfg.n_heads * hd, d)
-        self.gate_proj, self.up_proj, self.down_proj = mk(d, cfg.ffn), mk(d, cfg.ffn), mk(cfg.ffn, d)
+        self.gate_up_proj, self.down_proj = mk(d, 2 * cfg.ffn), mk(cfg.ffn, d)
         self.input_layernorm = RMSNorm(d, cfg.eps, device, dtype)
         self.post_attention_layernorm = RMSNorm(d, cfg.eps, device, dtype)
         self.k_cache = self.v_cache = None
+        self.cos_table = self.sin_table = None      # the model's [max_seq, hd/2] tables, shared by all blocks
 
     def alloc_cache(self, batch, device, dtype):
         shape = (batch, self.kv_local, self.cfg.max_seq, self.cfg.head_dim)
@@ -85,19 +88,31 @@ class Block(nn.Module):
         B, T, _ = x.shape
         hd = self.cfg.head_dim
         h = self.input_layernorm(x)
-        q = self.q_proj(h).to(x.dtype).view(B, T, self.h_local, hd).transpose(1, 2)
-        k = self.k_proj(h).to(x.dtype).view(B, T, self.kv_local, hd).transpose(1, 2)
-        v = self.v_proj(h).to(x.dtype).view(B, T, self.kv_local, hd).transpose(1, 2)
-        q, k = _rope(q, cos, sin), _rope(k, cos, sin)
-        self.k_cache.index_copy_(2, pos, k)
-        self.v_cache.index_copy_(2, pos, v)
+        qkv = self.qkv_proj(h).to(x.dtype)
+        fused = x.is_cuda and x.dtype in (torch.float16, torch.bfloat16)
+        if fused:      # one kernel: rotate Q and K, write K and V into the cache, lay Q out head-major
+            q = _ext.rope_kv_store(qkv.contiguous(), pos, self.cos_table, self.sin_table, self.k_cache, self.v_cache,
+                                   self.h_local, self.kv_local)
+            k, v = self.k_cache[:, :, :T], self.v_cache[:, :, :T]           # prefill starts at position 0
+        else:
+            qkv = qkv.view(B, T, self.h_local + 2 * self.kv_local, hd).transpose(1, 2)
+            q, k, v = qkv.split((self.h_local, self.kv_local, self.kv_local), dim=1)
+            q, k = _rope(q, cos, sin), _rope(k, cos, sin)
+            self.k_cache.index_copy_(2, pos, k)
+            self.v_cache.index_copy_(2, pos, v)
         if mask is None:
             a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         else:
             a = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask, enable_gqa=True)
         x = x + self.o_proj(a.transpose(1, 2).reshape(B, T, self.h_local * hd)).to(x.dtype)
         h = self.post_attention_layernorm(x)
-        return x + self.down_proj(F.silu(self.gate_proj(h)) * self.up_proj(h)).to(x.dtype)
+        gu = self.gate_up_proj(h)
+        if fused and gu.dtype == x.dtype:
+            act = _ext.silu_mul(gu.contiguous())
+        else:
+            f = gu.shape[-1] // 2
+            act = F.silu(gu[..., :f]) * gu[..., f:]
+        return x + self.down_proj(act).to(x.dtype)
 
 
 class Llama(nn.Module):
@@ -117,6 +132,7 @@ class Llama(nn.Module):
         p = self.embed.weight
         for l in self.layers:
             l.alloc_cache(batch, p.device, p.dtype)
+            l.cos_table, l.sin_table = self.cos, self.sin
 
     def forward(self, tokens, pos, prefill=False):
         """tokens int64 [B, T]; pos int64 [T] on the same device. Returns logits [B, T, vocab]."""
@@ -161,12 +177,9 @@ def build_fp8_llama(cfg: LlamaConfig, device, dtype=torch.float16, fp8: FP8Confi
 
     d, hd = cfg.d_model, cfg.head_dim
     for blk in model.layers:
-        blk.q_proj = quantized(cfg.n_heads * hd, d, "col")
-        blk.k_proj = quantized(cfg.n_kv_heads * hd, d, "col", independent=True)     # same input as q_proj
-        blk.v_proj = quantized(cfg.n_kv_heads * hd, d, "col", independent=True)
+        blk.qkv_proj = quantized((cfg.n_heads + 2 * cfg.n_kv_heads) * hd, d, "col")
         blk.o_proj = quantized(d, cfg.n_heads * hd, "row")
-        blk.gate_proj = quantized(cfg.ffn, d, "col")
-        blk.up_proj = quantized(cfg.ffn, d, "col", independent=True)                # same input as gate_proj
+        blk.gate_up_proj = quantized(2 * cfg.ffn, d, "col")
         blk.down_proj = quantized(d, cfg.ffn, "row")
         blk.input_layernorm = RMSNorm(d, cfg.eps, device, dtype)
         blk.post_attention_layernorm = RMSNorm(d, cfg.eps, device, dtype)

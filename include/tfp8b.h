@@ -161,6 +161,21 @@ TFP8B_API int tfp8b_linear_static(const void* x, int x_dtype, const uint8_t* cod
 TFP8B_API int tfp8b_epilogue(const float* acc, const float* xs, const float* bias, void* y, int y_dtype,
                    int M, int n, int ldy, tfp8b_stream_t stream);
 
+/* Decode-step helpers around the FP8Linear layers of a Llama-style block (the reference's demo,
+ * tfp8/examples/demo_llm.py:64-87, does this work with eager torch kernels).
+ * tfp8b_rope_kv_store: rotary embedding (rotate-half pairs i, i + hd/2) of the Q and K heads of a
+ * fused projection output qkv [B, T, H + 2*KV, hd]; Q goes to q_out [B, H, T, hd], K and V into the
+ * static caches [B, KV, max_seq, hd] at positions pos[t] (int64, on the device). cos / sin are
+ * f32 [max_seq, hd/2]. dtype f16 or bf16. */
+TFP8B_API int tfp8b_rope_kv_store(const void* qkv, int dtype, const long long* pos, const float* cosv,
+                  const float* sinv, void* q_out, void* k_cache, void* v_cache, int B, int T, int H,
+                  int KV, int hd, int max_seq, tfp8b_stream_t stream);
+
+/* out[r, 0:F] = silu(gate_up[r, 0:F]) * gate_up[r, F:2F]; f16 or bf16, F % 8 == 0 (reference:
+ * tfp8/examples/demo_llm.py:86-87). */
+TFP8B_API int tfp8b_silu_mul(const void* gate_up, void* out, int dtype, long long rows, int F,
+                  tfp8b_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,65 @@
+"""The two fused decode-step helpers (rotary embedding + KV-cache store, silu*mul) against plain
+PyTorch float32 references of the same operations, and the serving harness end to end on the GPU
+(a decode step through the static cache and the FP8 kernels reproduces a longer prefill)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16))
+def test_rope_kv_store_matches_torch(dtype):
+    from tfp8 import _ext
+    torch.manual_seed(0)
+    B, T, H, KV, hd, S = 2, 5, 8, 2, 128, 40
+    qkv = torch.randn(B, T, (H + 2 * KV) * hd, device="cuda").to(dtype)
+    pos = torch.tensor([7, 8, 9, 20, 3], device="cuda")
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, device="cuda").float() / hd))
+    ang = torch.arange(S, device="cuda").float()[:, None] * inv[None]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    kc = torch.zeros(B, KV, S, hd, device="cuda", dtype=dtype)
+    vc = torch.zeros_like(kc)
+    q = _ext.rope_kv_store(qkv, pos, cos, sin, kc, vc, H, KV)
+    x = qkv.float().view(B, T, H + 2 * KV, hd).transpose(1, 2)
+    qr, kr, vr = x.split((H, KV, KV), dim=1)
+    c, s = cos[pos], sin[pos]
+    rot = lambda t: torch.cat([t[..., :hd // 2] * c - t[..., hd // 2:] * s, t[..., hd // 2:] * c + t[..., :hd // 2] * s], -1)
+    # float32 math, one rounding to the 16-bit type (the kernel may contract a*b - c*d into an FMA)
+    tol = dict(rtol=2.0 ** -9 if dtype == torch.float16 else 2.0 ** -7, atol=2e-3 if dtype == torch.float16 else 2e-2)
+    assert torch.allclose(q.float(), rot(qr), **tol)
+    assert torch.allclose(kc[:, :, pos].float(), rot(kr), **tol) and torch.equal(vc[:, :, pos], vr.to(dtype))
+    untouched = torch.ones(S, dtype=torch.bool, device="cuda")
+    untouched[pos] = False
+    assert not kc[:, :, untouched].any() and not vc[:, :, untouched].any()
+
+
+@pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16))
+def test_silu_mul_matches_torch(dtype):
+    from tfp8 import _ext
+    torch.manual_seed(1)
+    gu = (torch.randn(3, 7, 2 * 1024, device="cuda") * 3).to(dtype)
+    got = _ext.silu_mul(gu).float()
+    g, u = gu.float()[..., :1024], gu.float()[..., 1024:]
+    want = F.silu(g) * u
+    tol = 2.0 ** -9 if dtype == torch.float16 else 2.0 ** -7          # one rounding of the output type (+ __expf)
+    assert ((got - want).abs() <= tol * want.abs() + 1e-4).all()
+
+
+def test_harness_decode_matches_prefill_on_gpu():
+    from tfp8 import FP8Config, _ext
+    from tfp8.examples.llama import TINY, DecodeRunner, build_fp8_llama
+    torch.manual_seed(0)
+    model = build_fp8_llama(TINY, torch.device("cuda"), torch.float16, fp8=FP8Config(min_features=64, nan_check=False))
+    toks = torch.randint(0, TINY.vocab, (2, 9), device="cuda")
+    full = DecodeRunner(model, 2).prefill(toks).float()
+    run = DecodeRunner(model, 2)
+    run.prefill(toks[:, :8])
+    run.tok.copy_(toks[:, 8:9])
+    logits = model(run.tok, run.pos, prefill=False).float()
+    assert (logits[:, 0] - full[:, 8]).abs().max() <= 2e-2 * full.abs().max()
+    run.capture()
+    out = run.decode(4)
+    assert out.shape == (2, 4) and int(run.pos) == 8 + 4
+    assert model.layers[0].qkv_proj.stats["gemv"] > 0 and model.layers[0].qkv_proj.stats["gemm"] > 0
+    assert _ext.device_status() == 0
