@@ -512,16 +512,27 @@ def main():
     if args.probe:
         run_probe(args)
         return
+    # The result is ONE line on stdout. Libraries write there too (NCCL prints a version banner
+    # when NCCL_DEBUG asks for it), so during the run file descriptor 1 points at stderr and the
+    # line goes to the saved descriptor at the end.
+    sys.stdout.flush()
+    result_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(line):
+        sys.stdout.flush()
+        os.write(result_fd, (json.dumps(line) + "\n").encode())
+
     if args.impl == "reference":
         line = run_reference(args, rank, world)
         if line is not None:
-            print(json.dumps(line))
+            emit(line)
         return
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     line = run_ours(args, rank, world, local_rank)
     if rank == 0:
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         torch.distributed.destroy_process_group()
 

@@ -87,13 +87,31 @@ __device__ __forceinline__ float scalar_f32(__half v) { return half_bits_to_f32(
 __device__ __forceinline__ float scalar_f32(__nv_bfloat16 v) { return __uint_as_float(static_cast<uint32_t>(__bfloat16_as_ushort(v)) << 16); }
 __device__ __forceinline__ float scalar_f32(float v) { return v; }
 
+// Two floats -> two codes (lo in bits 0-7) by the conversion instruction: round to nearest even,
+// saturate to the largest finite code (+-inf included). A NaN comes back as some NaN code of the
+// format, never as a finite one, which is all `encode16` relies on.
+template <int FMT>
+__device__ __forceinline__ uint32_t enc2_hw(float lo, float hi) {
+    unsigned short r;
+    if (FMT == TFP8B_E4M3FN) asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// 16 floats -> 16 codes. The conversion instruction does the rounding; a word that holds a NaN
+// code (E4M3FN: 0x7F; E5M2: anything above the largest finite 0x7B, as saturation leaves no
+// infinity) is redone by the integer encoder, which knows the NaN convention asked for.
 template <int FMT>
 __device__ __forceinline__ uint4 encode16(const float v[16], int nan_mode) {
+    constexpr uint32_t NAN_PROBE = FMT == TFP8B_E4M3FN ? 0x01010101u : 0x04040404u;
     uint32_t w[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-        w[i] = encode1<FMT>(v[4 * i], nan_mode) | (encode1<FMT>(v[4 * i + 1], nan_mode) << 8) |
-               (encode1<FMT>(v[4 * i + 2], nan_mode) << 16) | (encode1<FMT>(v[4 * i + 3], nan_mode) << 24);
+    for (int i = 0; i < 4; ++i) {
+        w[i] = enc2_hw<FMT>(v[4 * i], v[4 * i + 1]) | (enc2_hw<FMT>(v[4 * i + 2], v[4 * i + 3]) << 16);
+        if (((w[i] & 0x7F7F7F7Fu) + NAN_PROBE) & 0x80808080u)
+            w[i] = encode1<FMT>(v[4 * i], nan_mode) | (encode1<FMT>(v[4 * i + 1], nan_mode) << 8) |
+                   (encode1<FMT>(v[4 * i + 2], nan_mode) << 16) | (encode1<FMT>(v[4 * i + 3], nan_mode) << 24);
+    }
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
@@ -222,10 +240,16 @@ __global__ void __launch_bounds__(EW_THREADS) quantize_kernel(const T* __restric
         const float s = __uint_as_float(s_amax[k / G]);
         float v[16];
         load16<T>(row + k, v);
+        // w / s, then clamp to +-fmax: the encoder's saturation is that clamp. Dividing by a power
+        // of two is multiplying by its reciprocal, exactly (the quotient's subnormal range included).
+        const uint32_t sb = __float_as_uint(s);
+        if ((sb & 0x007FFFFFu) == 0u && sb >= 0x00800000u && sb <= 0x7E800000u) {
+            const float inv = __uint_as_float(0x7F000000u - sb);
 #pragma unroll
-        for (int t = 0; t < 16; ++t) {
-            float r = __fdiv_rn(v[t], s);
-            v[t] = r > fmax ? fmax : (r < -fmax ? -fmax : r);     // keeps NaN, like torch.clamp
+            for (int t = 0; t < 16; ++t) v[t] *= inv;
+        } else {
+#pragma unroll
+            for (int t = 0; t < 16; ++t) v[t] = __fdiv_rn(v[t], s);
         }
         *reinterpret_cast<uint4*>(q + static_cast<size_t>(n) * K + k) = encode16<FMT>(v, TFP8B_NAN_CAST);
     }

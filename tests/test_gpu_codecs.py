@@ -69,6 +69,26 @@ def test_encode_random_float32_bit_patterns(ext, fmt):
     assert np.array_equal(ext.encode(x[3:1000].clone(), fmt).cpu().numpy(), got[3:1000])
 
 
+@pytest.mark.parametrize("fmt", FMTS)
+def test_encode_float32_rounding_boundaries(ext, fmt):
+    """Every midpoint between neighbouring codes (a tie: exact in float32), the float32 values one
+    and two ulps either side of it, and the neighbourhoods of every code value, zero, the largest
+    finite value and the smallest subnormal, in both signs: where a double rounding or a wrong
+    tie rule would show. Checked against the oracle for both NaN conventions."""
+    table = O.decode_table(fmt).astype(np.float64)
+    pos = np.sort(table[:128][np.isfinite(table[:128])])
+    pts = np.concatenate([pos, (pos[:-1] + pos[1:]) / 2, [pos[1] / 2, pos[1] / 4, pos[-1] * 1.03125, pos[-1] * 2]])
+    centre = pts.astype(np.float32).view(np.int32).astype(np.int64)
+    near = (centre[:, None] + np.arange(-3, 4)[None, :]).clip(0, 0x7F7FFFFF).reshape(-1)
+    bits = np.concatenate([near, near | 0x80000000, [0x7F800000, 0xFF800000, 0x7FC00000, 0xFFC00000, 0x7F800001]])
+    x = bits.astype(np.uint32).view(np.float32)
+    x = np.concatenate([x, x[:7]])                    # a ragged tail after the 16-wide body
+    xt = torch.from_numpy(x.copy()).cuda()
+    for canonical, conv in ((False, "cast"), (True, "canonical")):
+        got = ext.encode(xt, fmt, canonical_nan=canonical).cpu().numpy()
+        assert np.array_equal(got, O.encode(x, fmt, conv))
+
+
 def test_round_trip_all_codes(ext, golden_c1):
     for fmt in FMTS:
         codes = torch.arange(256, dtype=torch.uint8, device="cuda")
