@@ -6,43 +6,53 @@
 // decodes each FP8 tile once and multiplies it against up to 256 activation rows, and small M
 // (16..128) simply uses a narrower MMA instead of padding the 128-row dimension.
 //
-// Persistent CTAs (one per SM) walk the list of 128 x BN output tiles; K flows in 64-wide blocks
-// through one ring of shared-memory stages that does not drain between tiles, and the FP32
-// accumulators are double-buffered in tensor memory so the epilogue of a tile overlaps the main
-// loop of the next one. Warp roles:
-//   warp 0       TMA producer: per stage one 2-D tiled load of the raw FP8 tile (128 x 64 bytes)
-//                and one of the activation tile (BN x 64 fp16, 128-byte swizzle); no multicast;
+// Persistent CTAs (one per SM) walk the list of 128 x BN output tiles. K flows in 64-wide k-blocks
+// through three shared-memory rings that never drain between tiles -- raw FP8 codes (deep: it
+// hides HBM latency), activation tiles, decoded fp16 weight tiles -- and the FP32 accumulators are
+// double-buffered in tensor memory so the epilogue of a tile overlaps the main loop of the next.
+// Warp roles:
+//   warp 0       raw-code producer: one tiled TMA load per raw slot, 128 weight rows x 128
+//                contiguous bytes (two k-blocks; 64 bytes when K is not a multiple of 128);
+//   warp 2       activation producer: per k-block one load of the BN x 64 fp16 tile in the
+//                128-byte swizzle; no multicast anywhere;
 //   warp 1       tensor-memory allocation; one thread issues tcgen05.mma (kind::f16, M = 128,
-//                N = BN, K = 16) four times per stage and tcgen05.commit's the stage free;
-//   warps 2..17  decode: 16 codes per thread per step to fp16 (two codes per conversion
-//                instruction), the K-group scale folded in as scale / rowmax (a packed fp16
-//                multiply when the ratio is a power of two, else an FP32 multiply with one fp16
-//                rounding), written in the 128-byte-swizzled K-major layout the MMA reads;
-//                fence.proxy.async, then an mbarrier arrive;
-//   warps 18..21 epilogue: tcgen05.ld the FP32 accumulators, apply smax[n], xs[m], bias[n], round
+//                N = BN, K = 16) four times per k-block and tcgen05.commit's the two tiles free;
+//   warps 3..18  decode, in groups that take alternate k-blocks: 16 codes per thread per step to
+//                fp16 (two codes per conversion instruction), the K-group scale folded in as
+//                scale / rowmax (a packed fp16 multiply when the ratio is a power of two, else an
+//                FP32 multiply with one fp16 rounding), written in the 128-byte-swizzled K-major
+//                layout the MMA reads; fence.proxy.async, then mbarrier arrives;
+//   warps 19..22 epilogue: tcgen05.ld the FP32 accumulators, apply smax[n], xs[m], bias[n], round
 //                once to the output type and store (32 lanes = 32 consecutive n per m).
 // No fp16 copy of the weights ever exists outside shared memory. Every mbarrier wait is bounded;
 // a wait that runs out sets a status bit, and the thread keeps walking its loops without waiting
 // so that every barrier is still met and the CTA ends.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace tfp8b {
 
 constexpr int GM_BM = 128;          // weight rows per tile = UMMA M = TMEM lanes
-constexpr int GM_BK = 64;           // K per stage: one 128-byte swizzle atom of fp16
-#ifndef TFP8B_GM_DEC_WARPS
-#define TFP8B_GM_DEC_WARPS 16
-#endif
-constexpr int GM_DEC_WARPS = TFP8B_GM_DEC_WARPS;   // 8: two rows per thread and stage; 16: one
+constexpr int GM_BK = 64;           // K per k-block: one 128-byte swizzle atom of fp16
+constexpr int GM_DEC_WARPS = 16;
 constexpr int GM_DEC_THREADS = GM_DEC_WARPS * 32;
-constexpr int GM_ROWS_PER_THREAD = 512 / GM_DEC_THREADS;   // 128 rows x 4 chunks per stage
-constexpr int GM_EPI_WARP0 = 2 + GM_DEC_WARPS;
+#ifndef TFP8B_GM_GROUPS
+#define TFP8B_GM_GROUPS 2
+#endif
+constexpr int GM_NG = TFP8B_GM_GROUPS;                 // decode groups; group g decodes k-blocks g, g + NG, ...
+constexpr int GM_GROUP_THREADS = GM_DEC_THREADS / GM_NG;
+constexpr int GM_GROUP_WARPS = GM_DEC_WARPS / GM_NG;
+constexpr int GM_RPT = GM_NG;                          // rows per decode thread and k-block (128 rows x 4 chunks)
+constexpr int GM_DEC_WARP0 = 4;                        // warps 0..3: raw producer, MMA, activation producer, second MMA
+constexpr int GM_EPI_WARP0 = GM_DEC_WARP0 + GM_DEC_WARPS;
 constexpr int GM_THREADS = (GM_EPI_WARP0 + 4) * 32;
-constexpr int GM_MAX_STAGES = 8;
+constexpr int GM_MAX_SLOTS = 8;     // per ring
 constexpr int GM_HEADER = 2048;     // barriers, TMEM base, per-row scale reciprocals
 constexpr int GM_A_BYTES = GM_BM * GM_BK * 2;    // decoded fp16 tile
-constexpr int GM_RAW_BYTES = GM_BM * GM_BK;      // raw FP8 tile
+constexpr int GM_RAW_BYTES = GM_BM * GM_BK;      // raw FP8 tile of one k-block
 constexpr int GM_SMEM_MAX = 232448;              // 227 KB opt-in limit per CTA
+static_assert(GM_NG == 2 || GM_NG == 4, "two or four decode groups");
 
 struct GemmParams {
     const float* xs;
@@ -50,13 +60,17 @@ struct GemmParams {
     const float* bias;
     void* y;
     int M, N, K, G, scale_kind, y_dt;
-    int BN, nstages, stage_bytes, tmem_cols, m_tiles, ntiles;
+    int BN, tmem_cols, m_tiles, ntiles;
+    int ns, sr;          // stages (decoded weight tile + activation tile), slots of the raw-code ring
+    int rb;              // k-blocks per raw slot: 2 (128 bytes per weight row and copy) or 1
+    int x_bytes;         // one activation tile: BN x 64 fp16
+    int stage_bytes;
+    int nmma;            // MMA-issuing threads; thread t takes k-blocks t, t + nmma, ... into its own accumulator
 };
 
 struct GemmHeader {
-    uint64_t full_raw[GM_MAX_STAGES];
-    uint64_t full_a[GM_MAX_STAGES];
-    uint64_t empty[GM_MAX_STAGES];
+    uint64_t full[GM_MAX_SLOTS], empty[GM_MAX_SLOTS];
+    uint64_t raw_full[GM_MAX_SLOTS], raw_empty[GM_MAX_SLOTS];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint32_t tmem_base;
@@ -64,6 +78,15 @@ struct GemmHeader {
     float binv[2][GM_BM];   // per weight row: 1 / max_g scale[n,g], double-buffered by tile parity
 };
 static_assert(sizeof(GemmHeader) <= GM_HEADER, "header too large");
+
+// Build with -DTFP8B_GM_TRACE to record, for CTA 0, the SM clock at which each role passes each
+// k-block (a diagnostic for pipeline tuning; the array is read with cudaMemcpyFromSymbol).
+#ifdef TFP8B_GM_TRACE
+__device__ long long g_trace[8][256];
+#define GM_TRACE(ev, idx) do { if (blockIdx.x == 0 && (idx) < 256) g_trace[ev][idx] = clock64(); } while (0)
+#else
+#define GM_TRACE(ev, idx) do { } while (0)
+#endif
 
 // ------------------------------------------------------------------ tcgen05 wrappers
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
@@ -152,15 +175,15 @@ template <int FMT>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
-    // 1024-byte alignment of the stage buffers is required by the swizzled layouts.
+    // 1024-byte alignment of the tile buffers is required by the swizzled layouts.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     GemmHeader* hd = reinterpret_cast<GemmHeader*>(smem);
-    uint8_t* stages = smem + GM_HEADER;
+    uint8_t* stages = smem + GM_HEADER;                                   // [decoded tile 16 KB][activation tile]
+    uint8_t* raw_ring = stages + static_cast<size_t>(p.ns) * p.stage_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int S = p.nstages;
     const int nkb = (p.K + GM_BK - 1) / GM_BK;
-    const int x_bytes = p.BN * GM_BK * 2;
+    const int raw_slot_bytes = p.rb * GM_RAW_BYTES;
     const int ng = p.K / p.G;
     const int my_tiles = (p.ntiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
     // Tile i of this CTA is global tile blockIdx.x + i * gridDim.x; the activation-row tile is the
@@ -169,13 +192,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     auto tile_n0 = [&](int i) { return ((static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x)) / p.m_tiles) * GM_BM; };
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < S; ++s) {
-            mbar_init(smem_u32(&hd->full_raw[s]), 1);
-            mbar_init(smem_u32(&hd->full_a[s]), GM_DEC_WARPS);
+        for (int s = 0; s < p.ns; ++s) {
+            mbar_init(smem_u32(&hd->full[s]), GM_GROUP_WARPS + 1);      // a group's warps + the activation copy
             mbar_init(smem_u32(&hd->empty[s]), 1);
         }
+        for (int s = 0; s < p.sr; ++s) {
+            mbar_init(smem_u32(&hd->raw_full[s]), 1);
+            mbar_init(smem_u32(&hd->raw_empty[s]), GM_GROUP_WARPS * p.rb);
+        }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&hd->acc_full[b]), 1);
+            mbar_init(smem_u32(&hd->acc_full[b]), p.nmma);
             mbar_init(smem_u32(&hd->acc_empty[b]), 4);
         }
         mbar_fence_init();
@@ -193,74 +219,125 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     const uint32_t tmem_base = hd->tmem_base;
 
     if (warp == 0) {
-        // ---------------------------------------------------------------- TMA producer
+        // ---------------------------------------------------------------- raw-code producer
         if (lane == 0) {
             // One activation tile only: the weight stripe is read once, keep it out of L2's way.
             // Several tiles: the CTAs of the other tiles read the same stripe from L2 next.
             const uint64_t pol_w = p.m_tiles == 1 ? l2_policy_evict_first() : l2_policy_evict_normal();
-            const uint64_t pol_x = l2_policy_evict_last();
             int slot = 0;
             uint32_t phase = 1;               // ring position (no divisions): the first pass over the ring does not wait
             bool ok = true, first_pass = true;
             for (int i = 0; i < my_tiles && ok; ++i) {
-                const int m0 = tile_m0(i), n0 = tile_n0(i);
-                for (int kb = 0; kb < nkb; ++kb) {
-                    if (!first_pass && !mbar_wait(smem_u32(&hd->empty[slot]), phase, STATUS_GEMM_WAIT)) { ok = false; break; }
-                    uint8_t* st = stages + static_cast<size_t>(slot) * p.stage_bytes;
-                    const uint32_t bar = smem_u32(&hd->full_raw[slot]);
-                    mbar_expect_tx(bar, static_cast<uint32_t>(GM_RAW_BYTES + x_bytes));
-                    tma_load_2d(smem_u32(st + GM_A_BYTES), &tm_x, kb * GM_BK, m0, bar, pol_x);
-                    tma_load_2d(smem_u32(st + GM_A_BYTES + x_bytes), &tm_w, kb * GM_BK, n0, bar, pol_w);
-                    if (++slot == S) { slot = 0; phase ^= 1u; first_pass = false; }
+                const int n0 = tile_n0(i);
+                for (int kb = 0; kb < nkb; kb += p.rb) {
+                    if (!first_pass && !mbar_wait(smem_u32(&hd->raw_empty[slot]), phase, STATUS_GEMM_WAIT)) { ok = false; break; }
+                    GM_TRACE(0, i * nkb + kb);
+                    const uint32_t bar = smem_u32(&hd->raw_full[slot]);
+                    const uint32_t dst = smem_u32(raw_ring + static_cast<size_t>(slot) * raw_slot_bytes);
+                    mbar_expect_tx(bar, static_cast<uint32_t>(raw_slot_bytes));
+                    if (p.rb == 2) tma_load_3d(dst, &tm_w, 0, n0, kb >> 1, bar, pol_w);     // [row][128 bytes]
+                    else tma_load_2d(dst, &tm_w, kb * GM_BK, n0, bar, pol_w);               // [row][64 bytes]
+                    if (++slot == p.sr) { slot = 0; phase ^= 1u; first_pass = false; }
                 }
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
+    } else if (warp == 2) {
+        // ---------------------------------------------------------------- activation producer
+        if (lane == 0) {
+            const uint64_t pol_x = l2_policy_evict_last();
+            int slot = 0;
+            uint32_t phase = 1;
+            bool ok = true, first_pass = true;
+            for (int i = 0; i < my_tiles && ok; ++i) {
+                const int m0 = tile_m0(i);
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!first_pass && !mbar_wait(smem_u32(&hd->empty[slot]), phase, STATUS_GEMM_WAIT)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&hd->full[slot]);
+                    mbar_expect_tx(bar, static_cast<uint32_t>(p.x_bytes));
+                    tma_load_2d(smem_u32(stages + static_cast<size_t>(slot) * p.stage_bytes + GM_A_BYTES), &tm_x, kb * GM_BK, m0, bar, pol_x);
+                    if (++slot == p.ns) { slot = 0; phase ^= 1u; first_pass = false; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1 || (warp == 3 && p.nmma == 2)) {
+        // ---------------------------------------------------------------- MMA issuer(s)
+        // tcgen05.mma issue is paced by the tensor pipe, and everything else the issuing thread does
+        // per k-block (the barrier wait, the fence, the commit, its bookkeeping) is a gap in which
+        // the pipe can run dry. Two measures: the barrier of the thread's NEXT k-block is polled in
+        // the middle of the current k-block's four MMAs, while two of them are still queued; and
+        // for narrow tiles, where an MMA is short, two threads take alternate k-blocks of the
+        // CTA's stream, each into an accumulator of its own (the epilogue adds the two). At
+        // BN = 256 one double-buffered accumulator fills tensor memory and one thread issues.
         if (lane == 0) {
             // D fp32, A/B fp16, both K-major, N = BN, M = 128
             const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(p.BN >> 3) << 17) | (static_cast<uint32_t>(GM_BM >> 4) << 24);
-            int slot = 0;
-            uint32_t phase = 0;
-            bool ok = true;
+            const int t = warp == 1 ? 0 : 1;
+            const uint32_t stage_step = static_cast<uint32_t>(p.nmma * p.stage_bytes);
+            const uint32_t ring_bytes = static_cast<uint32_t>(p.ns * p.stage_bytes);
+            const uint32_t stages_u32 = smem_u32(stages);
+            uint32_t st = stages_u32 + static_cast<uint32_t>(t * p.stage_bytes);     // this thread's next stage
+            uint32_t bar_off = static_cast<uint32_t>(t * 8);                          // its barriers' offset in full[] / empty[]
+            const uint32_t full0 = smem_u32(&hd->full[0]), empty0 = smem_u32(&hd->empty[0]);
+            int next = t;                     // CTA-wide number of this thread's next k-block
+            uint32_t par = 0;
+            bool ok = true, ready = false;    // ready: the next k-block's barrier was already seen complete
+            uint64_t da = umma_desc_sw128(st), db = umma_desc_sw128(st + GM_A_BYTES);
             for (int i = 0; i < my_tiles && ok; ++i) {
                 const int buf = i & 1;
                 // the accumulator buffer must have been drained by the epilogue of tile i - 2
                 if (i >= 2) ok = mbar_wait(smem_u32(&hd->acc_empty[buf]), ((i >> 1) - 1) & 1, STATUS_GEMM_WAIT);
                 if (!ok) break;
-                tc_fence_after();
-                const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(buf * p.BN);
-                for (int kb = 0; kb < nkb; ++kb) {
-                    const uint32_t par = phase;
-                    ok = mbar_wait(smem_u32(&hd->full_raw[slot]), par, STATUS_GEMM_WAIT) &&
-                         mbar_wait(smem_u32(&hd->full_a[slot]), par, STATUS_GEMM_WAIT);
+                const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>((buf * p.nmma + t) * p.BN);
+                uint32_t accumulate = 0u;
+                int kb = next - i * nkb;
+                for (; kb < nkb; kb += p.nmma) {
+                    GM_TRACE(5, i * nkb + kb);
+                    if (!ready) ok = mbar_wait(full0 + bar_off, par, STATUS_GEMM_WAIT);
                     if (!ok) break;
+                    GM_TRACE(3, i * nkb + kb);
                     tc_fence_after();
-                    uint8_t* st = stages + static_cast<size_t>(slot) * p.stage_bytes;
-                    const uint64_t da = umma_desc_sw128(smem_u32(st));
-                    const uint64_t db = umma_desc_sw128(smem_u32(st + GM_A_BYTES));
-#pragma unroll
-                    for (int kk = 0; kk < GM_BK / 16; ++kk)
-                        tc_mma_f16(tmem_acc, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
-                    tc_commit(smem_u32(&hd->empty[slot]));
-                    if (++slot == S) { slot = 0; phase ^= 1u; }
+                    tc_mma_f16(tmem_acc, da, db, idesc, accumulate);
+                    tc_mma_f16(tmem_acc, da + 2, db + 2, idesc, 1u);
+                    // while those two are queued: move on to this thread's next k-block, look at its
+                    // barrier once and build its descriptors
+                    const uint32_t cur_empty = empty0 + bar_off;
+                    const uint64_t da_cur = da, db_cur = db;
+                    st += stage_step; bar_off += static_cast<uint32_t>(p.nmma * 8);
+                    if (st >= stages_u32 + ring_bytes) { st -= ring_bytes; bar_off -= static_cast<uint32_t>(p.ns * 8); par ^= 1u; }
+                    ready = mbar_try_wait(full0 + bar_off, par);
+                    da = umma_desc_sw128(st); db = umma_desc_sw128(st + GM_A_BYTES);
+                    tc_mma_f16(tmem_acc, da_cur + 4, db_cur + 4, idesc, 1u);
+                    tc_mma_f16(tmem_acc, da_cur + 6, db_cur + 6, idesc, 1u);
+                    GM_TRACE(6, i * nkb + kb);
+                    tc_commit(cur_empty);
+                    GM_TRACE(4, i * nkb + kb);
+                    accumulate = 1u;
                 }
+                next = i * nkb + kb;
                 if (ok) tc_commit(smem_u32(&hd->acc_full[buf]));
             }
         }
         __syncwarp();
-    } else if (warp < GM_EPI_WARP0) {
+    } else if (warp >= GM_DEC_WARP0 && warp < GM_EPI_WARP0) {
         // ---------------------------------------------------------------- decode warps
-        constexpr int RPT = GM_ROWS_PER_THREAD;
+        // The CTA's k-blocks are numbered through all its tiles; group g owns numbers g, g + NG, ...
+        // so NG k-blocks are in decode at once and a group's fixed costs per k-block (barrier
+        // round trips, the proxy fence) overlap another group's work.
+        constexpr int RPT = GM_RPT;
         constexpr int RSTEP = GM_BM / RPT;           // distance between a thread's rows
-        const int td = threadIdx.x - 64;             // 0 .. GM_DEC_THREADS-1
-        const int c = td & 3;                        // 16-code chunk of the 64-wide K block
-        const int r0 = td >> 2;                      // rows r0 (+ RSTEP)
-        int slot = 0;
-        uint32_t phase = 0;
+        const int td = threadIdx.x - GM_DEC_WARP0 * 32;   // 0 .. GM_DEC_THREADS-1
+        const int group = td / GM_GROUP_THREADS;
+        const int tg = td % GM_GROUP_THREADS;
+        const int c = tg & 3;                        // 16-code chunk of the 64-wide K block
+        const int r0 = tg >> 2;                      // rows r0 + RSTEP * h
+        const int r_step = GM_NG / p.rb;             // raw slots between this group's consecutive k-blocks
+        int a_slot = group, r_slot = group / p.rb;   // positions of the group's first k-block (NG <= ns, sr)
+        uint32_t a_par = 0, r_par = 0;
+        int done = group;                            // CTA-wide number of the group's next k-block
         bool ok = true;
-        constexpr int PF = 8;                        // k-blocks whose scale ratios are fetched ahead
+        constexpr int PF = 4;                        // the group's k-blocks whose scale ratios are fetched ahead
         for (int i = 0; i < my_tiles; ++i) {
             const int n0 = tile_n0(i);
             float binv[RPT];
@@ -284,16 +361,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 #pragma unroll
                 for (int h2 = 0; h2 < RPT; ++h2) binv[h2] = hd->binv[i & 1][r0 + RSTEP * h2];
             }
-            // scale / rowmax of this thread's two rows for PF k-blocks, loaded one batch ahead of
-            // their use: a global load in the k-block loop itself would stall every decode warp
-            // for an L2 round trip per stage.
-            auto load_ratios = [&](int kb0, float (*dst)[RPT]) {
+            // this group's k-blocks inside the tile: first, first + NG, ... (nloc of them)
+            const int first = done - i * nkb;
+            const int nloc = first < nkb ? (nkb - first + GM_NG - 1) / GM_NG : 0;
+            // scale / rowmax of this thread's rows for PF of the group's k-blocks, loaded one batch
+            // ahead of their use: a global load in the k-block loop itself would stall every
+            // decode warp for an L2 round trip per k-block.
+            auto load_ratios = [&](int l0, float (*dst)[RPT]) {
 #pragma unroll
                 for (int j = 0; j < PF; ++j) {
 #pragma unroll
                     for (int h2 = 0; h2 < RPT; ++h2) dst[j][h2] = 1.f;
-                    if (ng > 1 && kb0 + j < nkb) {
-                        const int gi = min(((kb0 + j) * GM_BK + c * 16) / p.G, ng - 1);
+                    if (ng > 1 && l0 + j < nloc) {
+                        const int gi = min(((first + (l0 + j) * GM_NG) * GM_BK + c * 16) / p.G, ng - 1);
 #pragma unroll
                         for (int h2 = 0; h2 < RPT; ++h2) dst[j][h2] = load_scale(p.scale, srow[h2] + gi, p.scale_kind) * binv[h2];
                     }
@@ -301,53 +381,88 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             };
             float rcur[PF][RPT], rnext[PF][RPT];
             load_ratios(0, rcur);
-            for (int kb0 = 0; kb0 < nkb; kb0 += PF) {
-                load_ratios(kb0 + PF, rnext);
+            for (int l0 = 0; l0 < nloc; l0 += PF) {
+                load_ratios(l0 + PF, rnext);
 #pragma unroll
                 for (int j = 0; j < PF; ++j) {
-                    if (kb0 + j >= nkb) break;
-                    const int cur = slot;
-                    const uint32_t par = phase;
-                    if (++slot == S) { slot = 0; phase ^= 1u; }
-                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->full_raw[cur]), par, STATUS_GEMM_WAIT));
+                    if (l0 + j >= nloc) break;
+                    const int kb = first + (l0 + j) * GM_NG;
+                    const int acur = a_slot, rcur_slot = r_slot;
+                    const uint32_t apar = a_par, rpar = r_par;
+                    const bool fresh = done < p.ns;          // the stage's first use: nothing to wait for
+                    done += GM_NG;
+                    a_slot += GM_NG; if (a_slot >= p.ns) { a_slot -= p.ns; a_par ^= 1u; }
+                    r_slot += r_step; if (r_slot >= p.sr) { r_slot -= p.sr; r_par ^= 1u; }
+                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->raw_full[rcur_slot]), rpar, STATUS_GEMM_WAIT));
+                    if (ok && !fresh) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->empty[acur]), apar ^ 1u, STATUS_GEMM_WAIT));
                     if (!ok) continue;
-                    uint8_t* st = stages + static_cast<size_t>(cur) * p.stage_bytes;
-                    const uint8_t* raw = st + GM_A_BYTES + x_bytes;
+                    if (tg == 0) GM_TRACE(1, i * nkb + kb);
+                    uint8_t* st = stages + static_cast<size_t>(acur) * p.stage_bytes;
+                    const uint8_t* raw = raw_ring + static_cast<size_t>(rcur_slot) * raw_slot_bytes + (p.rb == 2 ? (kb & 1) * 64 : 0);
+                    const int rpitch = p.rb == 2 ? 128 : 64;
+                    // all loads, then all conversions, then all stores: the rows of a thread are
+                    // independent, and kept apart like this their latencies overlap
+                    uint32_t h[RPT][8];
+                    {
+                        uint4 q[RPT];
 #pragma unroll
-                    for (int h2 = 0; h2 < RPT; ++h2) {
-                        const int r = r0 + RSTEP * h2;
-                        const uint4 q = *reinterpret_cast<const uint4*>(raw + r * GM_BK + c * 16);
-                        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-                        uint32_t h[8];
+                        for (int h2 = 0; h2 < RPT; ++h2)
+                            q[h2] = *reinterpret_cast<const uint4*>(raw + (r0 + RSTEP * h2) * rpitch + c * 16);
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) dec4<FMT, false>(w[e], h[2 * e], h[2 * e + 1]);
-                        const float rt = rcur[j][h2];
-                        if (rt != 1.f) {
-                            const uint32_t rb = __float_as_uint(rt);
-                            if ((rb & 0x007FFFFFu) == 0u && rb >= 0x38800000u && rb <= 0x47000000u) {
-                                // power of two inside fp16's normal range: one packed multiply, same rounding
-                                const __half2 r2 = __float2half2_rn(rt);
+                        for (int h2 = 0; h2 < RPT; ++h2) {
+                            const uint32_t w[4] = {q[h2].x, q[h2].y, q[h2].z, q[h2].w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) dec4<FMT, false>(w[e], h[h2][2 * e], h[h2][2 * e + 1]);
+                        }
+                    }
+                    if (ng > 1) {
+                        // fold scale / rowmax in. A power of two inside fp16's normal range (1 included)
+                        // is one packed multiply with the same rounding as the general path: an FP32
+                        // multiply and one fp16 rounding. The choice is made for the whole warp.
+                        bool pow2 = true;
+#pragma unroll
+                        for (int h2 = 0; h2 < RPT; ++h2) {
+                            const uint32_t rb = __float_as_uint(rcur[j][h2]);
+                            pow2 = pow2 && (rb & 0x007FFFFFu) == 0u && rb >= 0x38800000u && rb <= 0x47000000u;
+                        }
+                        if (__all_sync(0xffffffffu, pow2)) {
+#pragma unroll
+                            for (int h2 = 0; h2 < RPT; ++h2) {
+                                const __half2 r2 = __float2half2_rn(rcur[j][h2]);
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) {
-                                    __half2 o = __hmul2(*reinterpret_cast<__half2*>(&h[e]), r2);
-                                    h[e] = *reinterpret_cast<uint32_t*>(&o);
+                                    __half2 o = __hmul2(*reinterpret_cast<__half2*>(&h[h2][e]), r2);
+                                    h[h2][e] = *reinterpret_cast<uint32_t*>(&o);
                                 }
-                            } else {
+                            }
+                        } else {
+#pragma unroll
+                            for (int h2 = 0; h2 < RPT; ++h2) {
+                                const float rt = rcur[j][h2];
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) {
-                                    float2 f = __half22float2(*reinterpret_cast<__half2*>(&h[e]));
+                                    float2 f = __half22float2(*reinterpret_cast<__half2*>(&h[h2][e]));
                                     __half2 o = __floats2half2_rn(f.x * rt, f.y * rt);
-                                    h[e] = *reinterpret_cast<uint32_t*>(&o);
+                                    h[h2][e] = *reinterpret_cast<uint32_t*>(&o);
                                 }
                             }
                         }
-                        uint8_t* arow = st + r * 128;
-                        *reinterpret_cast<uint4*>(arow + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-                        *reinterpret_cast<uint4*>(arow + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
                     }
+#pragma unroll
+                    for (int h2 = 0; h2 < RPT; ++h2) {
+                        const int r = r0 + RSTEP * h2;
+                        uint8_t* arow = st + r * 128;
+                        *reinterpret_cast<uint4*>(arow + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(h[h2][0], h[h2][1], h[h2][2], h[h2][3]);
+                        *reinterpret_cast<uint4*>(arow + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(h[h2][4], h[h2][5], h[h2][6], h[h2][7]);
+                    }
+                    if (tg == 0) GM_TRACE(7, i * nkb + kb);
                     fence_proxy_async_smem();        // generic-proxy stores -> visible to the tensor core
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&hd->full_a[cur]));
+                    if (tg == 0) GM_TRACE(2, i * nkb + kb);
+                    if (lane == 0) {
+                        mbar_arrive(smem_u32(&hd->full[acur]));
+                        mbar_arrive(smem_u32(&hd->raw_empty[rcur_slot]));   // this warp has read its part of the raw slot
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < PF; ++j)
@@ -355,7 +470,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     for (int h2 = 0; h2 < RPT; ++h2) rcur[j][h2] = rnext[j][h2];
             }
         }
-    } else {
+    } else if (warp >= GM_EPI_WARP0) {
         // ---------------------------------------------------------------- epilogue warps
         const int quarter = warp & 3;                           // TMEM lanes this warp may read
         const int row = quarter * 32 + lane;
@@ -370,11 +485,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->acc_full[buf]), (i >> 1) & 1, STATUS_GEMM_WAIT));
             if (!ok) continue;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * p.BN);
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * p.nmma * p.BN);
             for (int col = 0; col < p.BN; col += 16) {
                 uint32_t v[16];
                 tmem_ld16(taddr + col, v);
                 tmem_ld_wait();
+                for (int a = 1; a < p.nmma; ++a) {               // the second issuer's accumulator
+                    uint32_t u[16];
+                    tmem_ld16(taddr + a * p.BN + col, u);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
+                }
                 if (n < p.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -404,6 +526,11 @@ static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes,
     const cuuint64_t strides[1] = {inner * static_cast<uint64_t>(elem_bytes)};
     const cuuint32_t box[2] = {box_inner, box_outer};
     return encode_tensor_map(map, dt, 2, base, dims, strides, box, swz);
+}
+
+static int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return (v && *v) ? atoi(v) : dflt;
 }
 
 template <int FMT>
@@ -483,18 +610,44 @@ extern "C" int tfp8b_gemm(const void* x16, const float* xs, const uint8_t* codes
     int bn = 16;
     while (bn < M && bn < 256) bn <<= 1;
     p.BN = bn;
-    p.tmem_cols = 2 * bn < 32 ? 32 : 2 * bn;                 // two accumulator buffers
+    const int nkb = (K + GM_BK - 1) / GM_BK;
+    static const int env_nmma = env_int("TFP8B_GM_NMMA", 0), env_ns = env_int("TFP8B_GM_NS", 0), env_sr = env_int("TFP8B_GM_SR", 0);
+    // Two issuing threads, each with a double-buffered accumulator, while tensor memory has the
+    // room: 2 x 2 x BN <= 512 columns. (Two threads accumulating into ONE accumulator is not an
+    // option: that variant ended every BN = 256 launch with a launch failure.)
+    p.nmma = (bn <= 128 && nkb >= 4) ? 2 : 1;
+    if (env_nmma == 1) p.nmma = 1;
+    p.tmem_cols = 2 * p.nmma * bn < 32 ? 32 : 2 * p.nmma * bn;
     p.m_tiles = (M + bn - 1) / bn;
     p.ntiles = p.m_tiles * ((N + GM_BM - 1) / GM_BM);
-    p.stage_bytes = GM_A_BYTES + bn * GM_BK * 2 + GM_RAW_BYTES;
-    int S = (GM_SMEM_MAX - 1024 - GM_HEADER) / p.stage_bytes;
-    S = S > GM_MAX_STAGES ? GM_MAX_STAGES : S;
-    p.nstages = S;
-    const size_t smem = 1024 + GM_HEADER + static_cast<size_t>(S) * p.stage_bytes;
+    // Shared memory: four stages (the groups' tiles in decode, the one in the MMA, one spare), the
+    // rest raw codes -- the ring whose depth hides HBM latency. (At BN = 256 that rest is two slots,
+    // four k-blocks: there the CTAs of the other activation tiles pull the same stripe through L2.)
+    p.rb = K % 128 == 0 ? 2 : 1;
+    p.x_bytes = bn * GM_BK * 2;
+    p.stage_bytes = GM_A_BYTES + p.x_bytes;
+    const int budget = GM_SMEM_MAX - 1024 - GM_HEADER;
+    p.ns = env_ns > 0 ? env_ns : 4;
+    const int raw_slot = p.rb * GM_RAW_BYTES;
+    p.sr = (budget - p.ns * p.stage_bytes) / raw_slot;
+    if (p.sr > GM_MAX_SLOTS) p.sr = GM_MAX_SLOTS;
+    if (env_sr > 0 && env_sr < p.sr) p.sr = env_sr;
+    TFP8B_REQUIRE(p.ns >= GM_NG && p.ns <= GM_MAX_SLOTS && p.sr >= GM_NG, TFP8B_ERR_INVALID,
+                  "tfp8b_gemm: ring sizes ns=%d sr=%d do not fit", p.ns, p.sr);
+    const size_t smem = 1024 + GM_HEADER + static_cast<size_t>(p.ns) * p.stage_bytes + static_cast<size_t>(p.sr) * raw_slot;
 
     CUtensorMap tw, tx;
-    int rc = make_map_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, static_cast<uint64_t>(K), static_cast<uint64_t>(N),
+    int rc;
+    if (p.rb == 2) {
+        // codes seen as [K/128][N][128 bytes]: one copy brings 128 rows x 128 contiguous bytes
+        const cuuint64_t wd[3] = {128, static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(K / 128)};
+        const cuuint64_t ws[2] = {static_cast<cuuint64_t>(K), 128};
+        const cuuint32_t wb[3] = {128, GM_BM, 1};
+        rc = encode_tensor_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, codes, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_NONE);
+    } else {
+        rc = make_map_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, static_cast<uint64_t>(K), static_cast<uint64_t>(N),
                          GM_BK, GM_BM, CU_TENSOR_MAP_SWIZZLE_NONE);
+    }
     if (rc != TFP8B_OK) return rc;
     rc = make_map_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x16, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
                      GM_BK, static_cast<uint32_t>(bn), CU_TENSOR_MAP_SWIZZLE_128B);
