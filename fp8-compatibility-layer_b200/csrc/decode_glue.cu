@@ -1,11 +1,18 @@
-// Two small fused kernels for the decode step AROUND the FP8Linear layers of a Llama-style block
-// (the reference's demo does these with a dozen eager torch kernels per layer, which on B200 cost
+// Small fused kernels for the decode step AROUND the FP8Linear layers of a Llama-style block (the
+// reference's demo does these with a dozen eager torch kernels per layer, which on B200 cost
 // more time than the FP8 GEMVs themselves):
 //   rope_kv_store  rotary embedding of Q and K from the fused QKV projection, Q written
 //                  head-major for the attention call, K and V written into the static KV cache
 //                  at the tokens' positions -- one launch instead of ~16;
-//   silu_mul       silu(gate) * up on the fused gate/up projection -- one launch instead of 2-3.
-// Both are plain bandwidth-bound elementwise kernels on 16-bit activations.
+//   silu_mul       silu(gate) * up on the fused gate/up projection -- one launch instead of 2-3;
+//   add_rmsnorm    residual += delta, then RMSNorm of the residual -- one launch instead of 2;
+//   argmax         greedy token choice over the vocabulary, one CTA per row.
+// All are plain bandwidth- or latency-bound kernels on 16-bit activations. They are launched
+// with programmatic stream serialization and release their dependents at once: the FP8 GEMV
+// that follows starts streaming its weights while the helper is still running, and waits for
+// it (griddepcontrol.wait) only before it reads the activations.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace tfp8b {
@@ -28,6 +35,8 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const T* __restrict__ qkv,
                                                       T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                                       int B, int Tn, int H, int KV, int hd, int max_seq) {
     using P = typename pair_of<T>::type;
+    pdl_launch_dependents();
+    pdl_wait();
     const int half = hd / 2, pairs = half / 2, heads = H + 2 * KV;
     const long long total = static_cast<long long>(B) * Tn * heads * pairs;
     for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
@@ -60,6 +69,8 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const T* __restrict__ qkv,
 template <typename T>
 __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int F) {
     using P = typename pair_of<T>::type;
+    pdl_launch_dependents();
+    pdl_wait();
     const int vec = F / 8;
     const long long total = rows * vec;
     for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
@@ -79,6 +90,163 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu,
         }
         *reinterpret_cast<uint4*>(out + r * F + c) = o;
     }
+}
+
+// x[r, :] += delta[r, :] (rounded to T, stored), out[r, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps) * w.
+// One CTA per row, eight elements per thread and step, the row kept in registers between the two
+// passes when it fits (dim <= 8 * 256 * ADD_NORM_KEEP).
+constexpr int ADD_NORM_THREADS = 256;
+constexpr int ADD_NORM_KEEP = 4;
+template <typename T>
+__global__ void __launch_bounds__(ADD_NORM_THREADS) add_rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta,
+                                                                       const T* __restrict__ w, T* __restrict__ out,
+                                                                       int dim, float eps) {
+    using P = typename pair_of<T>::type;
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t row = static_cast<size_t>(blockIdx.x) * dim;
+    const int nvec = dim / 8;
+    uint4 keep[ADD_NORM_KEEP];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < ADD_NORM_KEEP; ++it) {
+        const int v = threadIdx.x + it * ADD_NORM_THREADS;
+        if (v < nvec) {
+            uint4 a = *reinterpret_cast<const uint4*>(x + row + v * 8);
+            if (delta) {
+                const uint4 d = *reinterpret_cast<const uint4*>(delta + row + v * 8);
+                P* ap = reinterpret_cast<P*>(&a);
+                const P* dp = reinterpret_cast<const P*>(&d);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = unpack2(ap[i]), g = unpack2(dp[i]);
+                    ap[i] = pack2(f.x + g.x, f.y + g.y, P());
+                }
+                *reinterpret_cast<uint4*>(x + row + v * 8) = a;
+            }
+            keep[it] = a;
+            const P* ap = reinterpret_cast<const P*>(&a);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = unpack2(ap[i]); ss += f.x * f.x + f.y * f.y; }
+        }
+    }
+    for (int v = threadIdx.x + ADD_NORM_KEEP * ADD_NORM_THREADS; v < nvec; v += ADD_NORM_THREADS) {   // long rows: the tail
+        uint4 a = *reinterpret_cast<const uint4*>(x + row + v * 8);
+        P* ap = reinterpret_cast<P*>(&a);
+        if (delta) {
+            const uint4 d = *reinterpret_cast<const uint4*>(delta + row + v * 8);
+            const P* dp = reinterpret_cast<const P*>(&d);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = unpack2(ap[i]), g = unpack2(dp[i]); ap[i] = pack2(f.x + g.x, f.y + g.y, P()); }
+            *reinterpret_cast<uint4*>(x + row + v * 8) = a;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = unpack2(ap[i]); ss += f.x * f.x + f.y * f.y; }
+    }
+    __shared__ float s_part[ADD_NORM_THREADS / 32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < ADD_NORM_THREADS / 32; ++i) ss += s_part[i];
+    const float rstd = rsqrtf(ss / static_cast<float>(dim) + eps);
+    auto emit = [&](int v, const uint4& a) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(w + v * 8);
+        const P* ap = reinterpret_cast<const P*>(&a);
+        const P* wp = reinterpret_cast<const P*>(&wv);
+        uint4 o;
+        P* op = reinterpret_cast<P*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = unpack2(ap[i]), g = unpack2(wp[i]);
+            op[i] = pack2(f.x * rstd * g.x, f.y * rstd * g.y, P());
+        }
+        *reinterpret_cast<uint4*>(out + row + v * 8) = o;
+    };
+#pragma unroll
+    for (int it = 0; it < ADD_NORM_KEEP; ++it) {
+        const int v = threadIdx.x + it * ADD_NORM_THREADS;
+        if (v < nvec) emit(v, keep[it]);
+    }
+    for (int v = threadIdx.x + ADD_NORM_KEEP * ADD_NORM_THREADS; v < nvec; v += ADD_NORM_THREADS)
+        emit(v, *reinterpret_cast<const uint4*>(x + row + v * 8));       // re-read what this thread stored
+}
+
+// out[r] = index of the largest logits[r, :]; the lowest index among equals; a NaN counts as the
+// largest value (the first NaN wins), as torch.argmax does. One CTA per row.
+constexpr int ARGMAX_THREADS = 1024;
+__device__ __forceinline__ bool argmax_better(float v, long long i, float bv, long long bi) {
+    const bool vn = v != v, bn = bv != bv;
+    if (vn || bn) return vn && (!bn || i < bi);
+    return v > bv || (v == bv && i < bi);
+}
+template <typename T>
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const T* __restrict__ logits, long long* __restrict__ out,
+                                                                long long n, long long row_pitch) {
+    using P = typename pair_of<T>::type;
+    pdl_launch_dependents();
+    pdl_wait();
+    const T* row = logits + static_cast<size_t>(blockIdx.x) * row_pitch;
+    float best = -INFINITY;
+    long long bi = 0x7fffffffffffffffll;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
+    const long long nvec = vec_ok ? n / 8 : 0;
+    for (long long v = threadIdx.x; v < nvec; v += ARGMAX_THREADS) {
+        const uint4 a = *reinterpret_cast<const uint4*>(row + v * 8);
+        const P* ap = reinterpret_cast<const P*>(&a);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = unpack2(ap[i]);
+            if (argmax_better(f.x, v * 8 + 2 * i, best, bi)) { best = f.x; bi = v * 8 + 2 * i; }
+            if (argmax_better(f.y, v * 8 + 2 * i + 1, best, bi)) { best = f.y; bi = v * 8 + 2 * i + 1; }
+        }
+    }
+    for (long long i = nvec * 8 + threadIdx.x; i < n; i += ARGMAX_THREADS) {
+        const float f = to_f32(row[i]);
+        if (argmax_better(f, i, best, bi)) { best = f; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (argmax_better(ov, oi, best, bi)) { best = ov; bi = oi; }
+    }
+    __shared__ float s_v[ARGMAX_THREADS / 32];
+    __shared__ long long s_i[ARGMAX_THREADS / 32];
+    if ((threadIdx.x & 31) == 0) { s_v[threadIdx.x >> 5] = best; s_i[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = s_v[threadIdx.x]; bi = s_i[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (argmax_better(ov, oi, best, bi)) { best = ov; bi = oi; }
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = bi;
+    }
+}
+
+// Launch with programmatic stream serialization (the kernel may start while its predecessor is
+// finishing and waits for it itself); TFP8B_NO_PDL=1 in the environment makes it a plain launch.
+template <typename... KArgs, typename... Args>
+static int launch_pdl(const char* what, void (*kernel)(KArgs...), int grid, int block, cudaStream_t st, Args... args) {
+    static const int no_pdl = [] { const char* v = getenv("TFP8B_NO_PDL"); return v && v[0] == '1'; }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(static_cast<unsigned>(block));
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = no_pdl ? 0 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) return cuda_fail(e, what);
+    return TFP8B_OK;
 }
 
 static int grid_of(long long work) {
@@ -101,14 +269,12 @@ extern "C" int tfp8b_rope_kv_store(const void* qkv, int dtype, const long long* 
     const long long work = static_cast<long long>(B) * T * (H + 2 * KV) * (hd / 4);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == TFP8B_F16)
-        rope_kv_kernel<__half><<<grid_of(work), 256, 0, st>>>(static_cast<const __half*>(qkv), pos, cosv, sinv, static_cast<__half*>(q_out),
-                                                             static_cast<__half*>(k_cache), static_cast<__half*>(v_cache), B, T, H, KV, hd, max_seq);
-    else
-        rope_kv_kernel<__nv_bfloat16><<<grid_of(work), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(qkv), pos, cosv, sinv,
-                                                                    static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
-                                                                    static_cast<__nv_bfloat16*>(v_cache), B, T, H, KV, hd, max_seq);
-    TFP8B_LAUNCH_CHECK("tfp8b_rope_kv_store");
-    return TFP8B_OK;
+        return launch_pdl("tfp8b_rope_kv_store", rope_kv_kernel<__half>, grid_of(work), 256, st, static_cast<const __half*>(qkv), pos, cosv,
+                          sinv, static_cast<__half*>(q_out), static_cast<__half*>(k_cache), static_cast<__half*>(v_cache), B, T, H, KV,
+                          hd, max_seq);
+    return launch_pdl("tfp8b_rope_kv_store", rope_kv_kernel<__nv_bfloat16>, grid_of(work), 256, st, static_cast<const __nv_bfloat16*>(qkv),
+                      pos, cosv, sinv, static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
+                      static_cast<__nv_bfloat16*>(v_cache), B, T, H, KV, hd, max_seq);
 }
 
 extern "C" int tfp8b_silu_mul(const void* gate_up, void* out, int dtype, long long rows, int F, tfp8b_stream_t stream) {
@@ -118,8 +284,42 @@ extern "C" int tfp8b_silu_mul(const void* gate_up, void* out, int dtype, long lo
     TFP8B_REQUIRE(gate_up && out, TFP8B_ERR_INVALID, "tfp8b_silu_mul: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const long long work = rows * (F / 8);
-    if (dtype == TFP8B_F16) silu_mul_kernel<__half><<<grid_of(work), 256, 0, st>>>(static_cast<const __half*>(gate_up), static_cast<__half*>(out), rows, F);
-    else silu_mul_kernel<__nv_bfloat16><<<grid_of(work), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, F);
-    TFP8B_LAUNCH_CHECK("tfp8b_silu_mul");
-    return TFP8B_OK;
+    if (dtype == TFP8B_F16)
+        return launch_pdl("tfp8b_silu_mul", silu_mul_kernel<__half>, grid_of(work), 256, st, static_cast<const __half*>(gate_up),
+                          static_cast<__half*>(out), rows, F);
+    return launch_pdl("tfp8b_silu_mul", silu_mul_kernel<__nv_bfloat16>, grid_of(work), 256, st, static_cast<const __nv_bfloat16*>(gate_up),
+                      static_cast<__nv_bfloat16*>(out), rows, F);
+}
+
+extern "C" int tfp8b_add_rmsnorm(void* x, const void* delta, const void* weight, void* out, int dtype, long long rows, int dim,
+                                 float eps, tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(dtype == TFP8B_F16 || dtype == TFP8B_BF16, TFP8B_ERR_UNSUPPORTED, "tfp8b_add_rmsnorm: f16 / bf16 only");
+    TFP8B_REQUIRE(rows >= 0 && rows <= 0x7fffffffll && dim > 0 && dim % 8 == 0, TFP8B_ERR_INVALID,
+                  "tfp8b_add_rmsnorm: need dim %% 8 == 0 and rows < 2^31");
+    if (rows == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(x && weight && out, TFP8B_ERR_INVALID, "tfp8b_add_rmsnorm: null pointer");
+    TFP8B_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(weight) |
+                    reinterpret_cast<uintptr_t>(out)) & 15u) == 0, TFP8B_ERR_INVALID, "tfp8b_add_rmsnorm: buffers must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == TFP8B_F16)
+        return launch_pdl("tfp8b_add_rmsnorm", add_rmsnorm_kernel<__half>, static_cast<int>(rows), ADD_NORM_THREADS, st,
+                          static_cast<__half*>(x), static_cast<const __half*>(delta), static_cast<const __half*>(weight),
+                          static_cast<__half*>(out), dim, eps);
+    return launch_pdl("tfp8b_add_rmsnorm", add_rmsnorm_kernel<__nv_bfloat16>, static_cast<int>(rows), ADD_NORM_THREADS, st,
+                      static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(weight),
+                      static_cast<__nv_bfloat16*>(out), dim, eps);
+}
+
+extern "C" int tfp8b_argmax(const void* logits, int dtype, long long* out, long long rows, long long n, long long row_pitch,
+                            tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(dtype == TFP8B_F16 || dtype == TFP8B_BF16, TFP8B_ERR_UNSUPPORTED, "tfp8b_argmax: f16 / bf16 only");
+    TFP8B_REQUIRE(rows >= 0 && rows <= 0x7fffffffll && n > 0 && row_pitch >= n, TFP8B_ERR_INVALID, "tfp8b_argmax: bad shape");
+    if (rows == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(logits && out, TFP8B_ERR_INVALID, "tfp8b_argmax: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == TFP8B_F16)
+        return launch_pdl("tfp8b_argmax", argmax_kernel<__half>, static_cast<int>(rows), ARGMAX_THREADS, st,
+                          static_cast<const __half*>(logits), out, n, row_pitch);
+    return launch_pdl("tfp8b_argmax", argmax_kernel<__nv_bfloat16>, static_cast<int>(rows), ARGMAX_THREADS, st,
+                      static_cast<const __nv_bfloat16*>(logits), out, n, row_pitch);
 }

@@ -27,8 +27,6 @@
 // No fp16 copy of the weights ever exists outside shared memory. Every mbarrier wait is bounded;
 // a wait that runs out sets a status bit, and the thread keeps walking its loops without waiting
 // so that every barrier is still met and the CTA ends.
-#include <stdlib.h>
-
 #include "common.cuh"
 
 namespace tfp8b {
@@ -528,11 +526,6 @@ static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes,
     return encode_tensor_map(map, dt, 2, base, dims, strides, box, swz);
 }
 
-static int env_int(const char* name, int dflt) {
-    const char* v = getenv(name);
-    return (v && *v) ? atoi(v) : dflt;
-}
-
 template <int FMT>
 static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, size_t smem, cudaStream_t st) {
     static unsigned long long configured = 0ull;
@@ -611,29 +604,31 @@ extern "C" int tfp8b_gemm(const void* x16, const float* xs, const uint8_t* codes
     while (bn < M && bn < 256) bn <<= 1;
     p.BN = bn;
     const int nkb = (K + GM_BK - 1) / GM_BK;
-    static const int env_nmma = env_int("TFP8B_GM_NMMA", 0), env_ns = env_int("TFP8B_GM_NS", 0), env_sr = env_int("TFP8B_GM_SR", 0);
     // Two issuing threads, each with a double-buffered accumulator, while tensor memory has the
     // room: 2 x 2 x BN <= 512 columns. (Two threads accumulating into ONE accumulator is not an
     // option: that variant ended every BN = 256 launch with a launch failure.)
     p.nmma = (bn <= 128 && nkb >= 4) ? 2 : 1;
-    if (env_nmma == 1) p.nmma = 1;
     p.tmem_cols = 2 * p.nmma * bn < 32 ? 32 : 2 * p.nmma * bn;
     p.m_tiles = (M + bn - 1) / bn;
     p.ntiles = p.m_tiles * ((N + GM_BM - 1) / GM_BM);
     // Shared memory: four stages (the groups' tiles in decode, the one in the MMA, one spare), the
     // rest raw codes -- the ring whose depth hides HBM latency. (At BN = 256 that rest is two slots,
     // four k-blocks: there the CTAs of the other activation tiles pull the same stripe through L2.)
+    // Every ring's length is a multiple of the stride its users walk it with (decode groups,
+    // issuing threads), so a slot is always revisited by the same user, in order: a parity wait
+    // can then never be answered by a phase two completions away.
     p.rb = K % 128 == 0 ? 2 : 1;
     p.x_bytes = bn * GM_BK * 2;
     p.stage_bytes = GM_A_BYTES + p.x_bytes;
     const int budget = GM_SMEM_MAX - 1024 - GM_HEADER;
-    p.ns = env_ns > 0 ? env_ns : 4;
+    p.ns = 4;
+    static_assert(4 % GM_NG == 0, "stage ring must be a multiple of the decode groups");
     const int raw_slot = p.rb * GM_RAW_BYTES;
+    const int raw_stride = GM_NG / p.rb;                      // slots between a group's consecutive k-blocks
     p.sr = (budget - p.ns * p.stage_bytes) / raw_slot;
     if (p.sr > GM_MAX_SLOTS) p.sr = GM_MAX_SLOTS;
-    if (env_sr > 0 && env_sr < p.sr) p.sr = env_sr;
-    TFP8B_REQUIRE(p.ns >= GM_NG && p.ns <= GM_MAX_SLOTS && p.sr >= GM_NG, TFP8B_ERR_INVALID,
-                  "tfp8b_gemm: ring sizes ns=%d sr=%d do not fit", p.ns, p.sr);
+    p.sr -= p.sr % raw_stride;
+    TFP8B_REQUIRE(p.sr >= GM_NG, TFP8B_ERR_INVALID, "tfp8b_gemm: ring sizes ns=%d sr=%d do not fit", p.ns, p.sr);
     const size_t smem = 1024 + GM_HEADER + static_cast<size_t>(p.ns) * p.stage_bytes + static_cast<size_t>(p.sr) * raw_slot;
 
     CUtensorMap tw, tx;

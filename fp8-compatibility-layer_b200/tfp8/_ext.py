@@ -44,6 +44,8 @@ _SIGNATURES = {
     "tfp8b_epilogue": ([_P, _P, _P, _P, _I, _I, _I, _I, _P], _I),
     "tfp8b_rope_kv_store": ([_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_silu_mul": ([_P, _P, _I, ctypes.c_longlong, _I, _P], _I),
+    "tfp8b_add_rmsnorm": ([_P, _P, _P, _P, _I, ctypes.c_longlong, _I, ctypes.c_float, _P], _I),
+    "tfp8b_argmax": ([_P, _I, _P, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _P], _I),
 }
 
 
@@ -346,4 +348,28 @@ def silu_mul(gate_up):
         rc = load().tfp8b_silu_mul(gate_up.data_ptr(), out.data_ptr(), _DT[gate_up.dtype], gate_up.numel() // (2 * F), F,
                                    _stream(dev))
     _check(rc, "tfp8b_silu_mul")
+    return out
+
+
+def add_rmsnorm(x, delta, weight, eps):
+    """x += delta (in place; delta may be None), returns RMSNorm(x) * weight. x, delta [..., dim]
+    f16 / bf16 contiguous; weight [dim] of the same dtype."""
+    dev = _need_cuda(x, weight) if delta is None else _need_cuda(x, delta, weight)
+    dim = x.shape[-1]
+    out = torch.empty_like(x)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_add_rmsnorm(x.data_ptr(), None if delta is None else delta.data_ptr(), weight.data_ptr(),
+                                      out.data_ptr(), _DT[x.dtype], x.numel() // dim, dim, float(eps), _stream(dev))
+    _check(rc, "tfp8b_add_rmsnorm")
+    return out
+
+
+def argmax_into(out, logits):
+    """out[r] = argmax(logits[r, :]) for a 2-D f16 / bf16 tensor whose rows are contiguous; `out` is
+    an int64 tensor with one element per row."""
+    dev = _need_cuda(out, logits)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_argmax(logits.data_ptr(), _DT[logits.dtype], out.data_ptr(), logits.shape[0], logits.shape[1],
+                                 logits.stride(0), _stream(dev))
+    _check(rc, "tfp8b_argmax")
     return out

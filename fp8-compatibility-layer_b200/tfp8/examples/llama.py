@@ -82,14 +82,20 @@ class Block(nn.Module):
         self.k_cache = torch.zeros(shape, device=device, dtype=dtype)
         self.v_cache = torch.zeros(shape, device=device, dtype=dtype)
 
-    def forward(self, x, pos, cos, sin, mask):
-        """x [B, T, d]; pos int64 [T] (device) = cache positions of these tokens; mask additive
-        [T, max_seq] or None (prefill from position 0 uses the causal flag)."""
+    def forward(self, x, delta, pos, cos, sin, mask):
+        """x [B, T, d] the residual stream and delta the previous block's MLP output not yet added
+        to it (None for the first block); pos int64 [T] (device) = cache positions of these tokens;
+        mask additive [T, max_seq] or None (prefill from position 0 uses the causal flag).
+        Returns (x, delta) in the same convention: the add is fused with the next RMSNorm."""
         B, T, _ = x.shape
         hd = self.cfg.head_dim
-        h = self.input_layernorm(x)
-        qkv = self.qkv_proj(h).to(x.dtype)
         fused = x.is_cuda and x.dtype in (torch.float16, torch.bfloat16)
+        if fused:      # one kernel: x += delta (in place), h = RMSNorm(x)
+            h = _ext.add_rmsnorm(x, delta, self.input_layernorm.weight, self.cfg.eps)
+        else:
+            x = x if delta is None else x + delta
+            h = self.input_layernorm(x)
+        qkv = self.qkv_proj(h).to(x.dtype)
         if fused:      # one kernel: rotate Q and K, write K and V into the cache, lay Q out head-major
             q = _ext.rope_kv_store(qkv.contiguous(), pos, self.cos_table, self.sin_table, self.k_cache, self.v_cache,
                                    self.h_local, self.kv_local)
@@ -104,15 +110,19 @@ class Block(nn.Module):
             a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         else:
             a = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask, enable_gqa=True)
-        x = x + self.o_proj(a.transpose(1, 2).reshape(B, T, self.h_local * hd)).to(x.dtype)
-        h = self.post_attention_layernorm(x)
+        o = self.o_proj(a.transpose(1, 2).reshape(B, T, self.h_local * hd)).to(x.dtype)
+        if fused:
+            h = _ext.add_rmsnorm(x, o.contiguous(), self.post_attention_layernorm.weight, self.cfg.eps)
+        else:
+            x = x + o
+            h = self.post_attention_layernorm(x)
         gu = self.gate_up_proj(h)
         if fused and gu.dtype == x.dtype:
             act = _ext.silu_mul(gu.contiguous())
         else:
             f = gu.shape[-1] // 2
             act = F.silu(gu[..., :f]) * gu[..., f:]
-        return x + self.down_proj(act).to(x.dtype)
+        return x, self.down_proj(act).to(x.dtype)
 
 
 class Llama(nn.Module):
@@ -134,17 +144,25 @@ class Llama(nn.Module):
             l.alloc_cache(batch, p.device, p.dtype)
             l.cos_table, l.sin_table = self.cos, self.sin
 
-    def forward(self, tokens, pos, prefill=False):
-        """tokens int64 [B, T]; pos int64 [T] on the same device. Returns logits [B, T, vocab]."""
+    def forward(self, tokens, pos, prefill=False, last_only=False):
+        """tokens int64 [B, T]; pos int64 [T] on the same device. Returns logits [B, T, vocab], or
+        [B, 1, vocab] of the last position with last_only (all a prefill needs to pick a token)."""
         x = self.embed(tokens)
         cos, sin = self.cos[pos], self.sin[pos]
         mask = None
         if not prefill:
             seq = torch.arange(self.cfg.max_seq, device=pos.device)
             mask = torch.where(seq[None, :] <= pos[:, None], 0.0, float("-inf")).to(x.dtype)
+        delta = None
         for l in self.layers:
-            x = l(x, pos, cos, sin, mask)
-        return self.lm_head(self.norm(x))
+            x, delta = l(x, delta, pos, cos, sin, mask)
+        if last_only:
+            x, delta = x[:, -1:].contiguous(), delta[:, -1:].contiguous()
+        if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16):
+            h = _ext.add_rmsnorm(x, delta, self.norm.weight, self.cfg.eps)
+        else:
+            h = self.norm(x + delta)
+        return self.lm_head(h)
 
 
 def build_fp8_llama(cfg: LlamaConfig, device, dtype=torch.float16, fp8: FP8Config | None = None, group=None, seed=0,
@@ -211,15 +229,22 @@ class DecodeRunner:
     def prefill(self, tokens):
         T = tokens.shape[1]
         pos = torch.arange(T, device=tokens.device)
-        logits = self.model(tokens, pos, prefill=True)
-        self.tok.copy_(logits[:, -1:].argmax(-1))
+        logits = self.model(tokens, pos, prefill=True, last_only=True)
+        self._pick(logits)
         self.pos.fill_(T)
         return logits
+
+    def _pick(self, logits):
+        """Greedy choice of the next token from logits [B, 1, vocab] into self.tok."""
+        if logits.is_cuda and logits.dtype in (torch.float16, torch.bfloat16):
+            _ext.argmax_into(self.tok, logits.view(logits.shape[0], -1))
+        else:
+            self.tok.copy_(logits[:, -1:].argmax(-1))
 
     @torch.no_grad()
     def _step(self):
         logits = self.model(self.tok, self.pos, prefill=False)
-        self.tok.copy_(logits[:, -1:].argmax(-1))
+        self._pick(logits)
         self.pos.add_(1)
 
     @torch.no_grad()

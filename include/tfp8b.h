@@ -176,6 +176,20 @@ TFP8B_API int tfp8b_rope_kv_store(const void* qkv, int dtype, const long long* p
 TFP8B_API int tfp8b_silu_mul(const void* gate_up, void* out, int dtype, long long rows, int F,
                   tfp8b_stream_t stream);
 
+/* x[r, :] += delta[r, :] (delta may be NULL), then out[r, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps)
+ * * weight: the residual update and the RMSNorm that follows it in a decoder block, one launch
+ * (reference: RMSNorm and the residual adds of tfp8/examples/demo_llm.py:30-39, 98-101; same
+ * arithmetic: FP32 inside, one rounding to the activation type). f16 or bf16, dim % 8 == 0,
+ * all buffers 16-byte aligned; x is updated in place. */
+TFP8B_API int tfp8b_add_rmsnorm(void* x, const void* delta, const void* weight, void* out, int dtype,
+                  long long rows, int dim, float eps, tfp8b_stream_t stream);
+
+/* out[r] = argmax over logits[r, 0:n] (row pitch in elements), int64; the lowest index among equal
+ * values, NaN counts as largest -- the greedy sampling step of the reference's demo
+ * (tfp8/examples/demo_llm.py:149). f16 or bf16. */
+TFP8B_API int tfp8b_argmax(const void* logits, int dtype, long long* out, long long rows, long long n,
+                  long long row_pitch, tfp8b_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

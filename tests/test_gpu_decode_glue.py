@@ -46,6 +46,50 @@ def test_silu_mul_matches_torch(dtype):
     assert ((got - want).abs() <= tol * want.abs() + 1e-4).all()
 
 
+@pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16))
+@pytest.mark.parametrize("dim", (256, 4096, 11008))
+def test_add_rmsnorm(dtype, dim):
+    """Residual update + RMSNorm against the same arithmetic in torch: the sum rounded to the
+    activation type (and stored), the norm in FP32 with one final rounding."""
+    from tfp8 import _ext
+    torch.manual_seed(2)
+    x = torch.randn(5, 3, dim, device="cuda").to(dtype)
+    d = (torch.randn(5, 3, dim, device="cuda") * 0.5).to(dtype)
+    w = (1 + 0.1 * torch.randn(dim, device="cuda")).to(dtype)
+    want_x = (x.float() + d.float()).to(dtype)
+    xf = want_x.float()
+    want = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float())
+    got = _ext.add_rmsnorm(x, d, w, 1e-5)
+    assert torch.equal(x, want_x)                                     # in-place residual, bit for bit
+    tol = 2.0 ** -9 if dtype == torch.float16 else 2.0 ** -7
+    assert ((got.float() - want).abs() <= tol * want.abs() + 1e-5).all()
+    # no delta: plain RMSNorm, x untouched
+    keep = x.clone()
+    got2 = _ext.add_rmsnorm(x, None, w, 1e-5)
+    assert torch.equal(x, keep) and torch.equal(got2, got)
+
+
+@pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16))
+def test_argmax(dtype):
+    from tfp8 import _ext
+    torch.manual_seed(3)
+    for n in (7, 1000, 128256):
+        logits = torch.randn(4, n, device="cuda").to(dtype)
+        logits[1, n // 2] = 100.0
+        logits[2, 3] = logits[2].max()                                # a tie: the lowest index wins
+        logits[2, min(5, n - 1)] = logits[2, 3]
+        out = torch.empty(4, dtype=torch.int64, device="cuda")
+        _ext.argmax_into(out, logits)
+        want = torch.stack([(row == row.max()).nonzero()[0, 0] for row in logits.float()])
+        assert torch.equal(out, want), n
+        logits[3, n - 1] = float("nan")                               # NaN counts as the largest
+        _ext.argmax_into(out, logits)
+        assert int(out[3]) == n - 1
+        sl = logits[:, 1:]                                            # rows no longer 16-byte aligned
+        _ext.argmax_into(out, sl)
+        assert int(out[1]) == n // 2 - 1 or n < 3
+
+
 def test_harness_decode_matches_prefill_on_gpu():
     from tfp8 import FP8Config, _ext
     from tfp8.examples.llama import TINY, DecodeRunner, build_fp8_llama
@@ -57,7 +101,7 @@ def test_harness_decode_matches_prefill_on_gpu():
     run.prefill(toks[:, :8])
     run.tok.copy_(toks[:, 8:9])
     logits = model(run.tok, run.pos, prefill=False).float()
-    assert (logits[:, 0] - full[:, 8]).abs().max() <= 2e-2 * full.abs().max()
+    assert (logits[:, 0] - full[:, 0]).abs().max() <= 2e-2 * full.abs().max()
     run.capture()
     out = run.decode(4)
     assert out.shape == (2, 4) and int(run.pos) == 8 + 4

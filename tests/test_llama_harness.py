@@ -14,11 +14,12 @@ def test_decode_step_matches_prefill():
     assert sum(isinstance(m, FP8Linear) for m in model.modules()) == 4 * TINY.n_layers
     assert isinstance(model.lm_head, torch.nn.Linear)
     toks = torch.randint(0, TINY.vocab, (2, 9))
-    full = DecodeRunner(model, 2).prefill(toks)                      # logits for positions 0..8
+    full = DecodeRunner(model, 2).prefill(toks)                      # logits of the last position (8)
     run = DecodeRunner(model, 2)
     run.prefill(toks[:, :8])
     run.tok.copy_(toks[:, 8:9])                                      # feed the true 9th token
     logits = model(run.tok, run.pos, prefill=False)
-    assert torch.allclose(logits[:, 0], full[:, 8], rtol=1e-3, atol=1e-3)          # fp16 projection outputs
+    assert full.shape == (2, 1, TINY.vocab)
+    assert torch.allclose(logits[:, 0], full[:, 0], rtol=1e-3, atol=1e-3)          # fp16 projection outputs
     out = run.decode(3)
     assert out.shape == (2, 3) and int(run.pos) == 8 + 3
