@@ -136,8 +136,18 @@ __device__ __forceinline__ void dec4(uint32_t w, uint32_t& p01, uint32_t& p23) {
     } else
 #endif
     {
+#ifndef TFP8B_DECODE_BITMOVES
+        // the word is split into its 16-bit halves inside the asm block, so no mask / shift
+        // instructions stand between the load and the two conversions
+        asm("{\n\t.reg .b16 lo, hi;\n\t"
+            "mov.b32 {lo, hi}, %2;\n\t"
+            "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+            "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}"
+            : "=r"(p01), "=r"(p23) : "r"(w));
+#else
         p01 = dec2_f16<FMT>(w & 0xFFFFu);
         p23 = dec2_f16<FMT>(w >> 16);
+#endif
     }
     if (BF16) { p01 = f16x2_to_bf16x2(p01); p23 = f16x2_to_bf16x2(p23); }
 }

@@ -126,10 +126,20 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
+__device__ __forceinline__ uint4 gm_lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void gm_sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // max over one row's K-group scales, entries [g0, g1). The loads are independent and issued in
 // batches (16-byte vectors where the row allows it): a one-load-at-a-time loop costs an L2 round
 // trip per scale, which for 256 groups is longer than the tile's whole main loop.
-__device__ __forceinline__ float row_scale_max(const void* scale, size_t row_off, int g0, int g1, int kind) {
+__device__ __forceinline__ float row_scale_max(const void* scale, size_t row_off, int g0, int g1, int kind,
+                                               uint32_t* bmax_out = nullptr) {
     const int esz = kind == TFP8B_SCALE_UE8M0 ? 1 : 4;
     const uint8_t* base = reinterpret_cast<const uint8_t*>(scale) + (row_off + g0) * esz;
     const int n = g1 - g0;
@@ -165,6 +175,7 @@ __device__ __forceinline__ float row_scale_max(const void* scale, size_t row_off
         else mx = fmaxf(mx, reinterpret_cast<const float*>(base)[i]);
     }
     if (kind == TFP8B_SCALE_UE8M0) mx = n > 0 ? ue8m0_to_f32(bmax) : 0.f;
+    if (bmax_out) *bmax_out = bmax;
     return mx;
 }
 
@@ -322,7 +333,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         // ---------------------------------------------------------------- decode warps
         // The CTA's k-blocks are numbered through all its tiles; group g owns numbers g, g + NG, ...
         // so NG k-blocks are in decode at once and a group's fixed costs per k-block (barrier
-        // round trips, the proxy fence) overlap another group's work.
+        // round trips, the proxy fence) overlap another group's work. The loop is kept lean on
+        // purpose (32-bit shared addresses, per-thread offsets computed once, ring cursors
+        // advanced by addition): with K-group scales this role is bound by instruction issue.
         constexpr int RPT = GM_RPT;
         constexpr int RSTEP = GM_BM / RPT;           // distance between a thread's rows
         const int td = threadIdx.x - GM_DEC_WARP0 * 32;   // 0 .. GM_DEC_THREADS-1
@@ -330,19 +343,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         const int tg = td % GM_GROUP_THREADS;
         const int c = tg & 3;                        // 16-code chunk of the 64-wide K block
         const int r0 = tg >> 2;                      // rows r0 + RSTEP * h
-        const int r_step = GM_NG / p.rb;             // raw slots between this group's consecutive k-blocks
-        int a_slot = group, r_slot = group / p.rb;   // positions of the group's first k-block (NG <= ns, sr)
-        uint32_t a_par = 0, r_par = 0;
+        const uint32_t rpitch = p.rb == 2 ? 128u : 64u;
+        uint32_t roff[RPT], aoff0[RPT], aoff1[RPT];  // this thread's byte offsets inside a raw slot / a decoded tile
+#pragma unroll
+        for (int h2 = 0; h2 < RPT; ++h2) {
+            const uint32_t r = static_cast<uint32_t>(r0 + RSTEP * h2);
+            roff[h2] = r * rpitch + static_cast<uint32_t>(c) * 16u;
+            aoff0[h2] = r * 128u + (((2u * c) ^ (r & 7u)) << 4);
+            aoff1[h2] = r * 128u + (((2u * c + 1u) ^ (r & 7u)) << 4);
+        }
+        const uint32_t stages_u32 = smem_u32(stages), raw_u32 = smem_u32(raw_ring);
+        const uint32_t full0 = smem_u32(&hd->full[0]), empty0 = smem_u32(&hd->empty[0]);
+        const uint32_t rfull0 = smem_u32(&hd->raw_full[0]), rempty0 = smem_u32(&hd->raw_empty[0]);
+        // ring cursors of the group's next k-block: byte offset of its stage / raw slot, the offset
+        // of their barriers, the parity to wait for
+        const uint32_t a_step = static_cast<uint32_t>(GM_NG * p.stage_bytes), a_ring = static_cast<uint32_t>(p.ns * p.stage_bytes);
+        const uint32_t r_slots = static_cast<uint32_t>(GM_NG / p.rb);           // raw slots between the group's k-blocks
+        const uint32_t r_step = r_slots * raw_slot_bytes, r_ring = static_cast<uint32_t>(p.sr) * raw_slot_bytes;
+        uint32_t a_off = static_cast<uint32_t>(group * p.stage_bytes), a_bar = static_cast<uint32_t>(group * 8), a_par = 0;
+        uint32_t r_off = static_cast<uint32_t>(group / p.rb) * raw_slot_bytes, r_bar = static_cast<uint32_t>(group / p.rb) * 8u, r_par = 0;
         int done = group;                            // CTA-wide number of the group's next k-block
         bool ok = true;
+        const bool e8 = p.scale_kind == TFP8B_SCALE_UE8M0;
+        // K-group of a k-block: (kb * 2 + c / 2) 32-code units / (G / 32); a shift when that is a power of two
+        const int g32 = p.G / 32;
+        const int g_shift = (g32 & (g32 - 1)) == 0 ? __ffs(g32) - 1 : -1;
         constexpr int PF = 4;                        // the group's k-blocks whose scale ratios are fetched ahead
         for (int i = 0; i < my_tiles; ++i) {
             const int n0 = tile_n0(i);
+            // per row: 1 / max_g scale (float scales) or the largest exponent byte (UE8M0)
             float binv[RPT];
+            int bmax[RPT];
             size_t srow[RPT];
 #pragma unroll
             for (int h2 = 0; h2 < RPT; ++h2) {
                 binv[h2] = 1.f;
+                bmax[h2] = 0;
                 srow[h2] = static_cast<size_t>(min(n0 + r0 + RSTEP * h2, p.N - 1)) * ng;
             }
             if (ng > 1) {
@@ -351,61 +387,73 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 const int row = td / TPR, part = td % TPR;
                 const size_t off = static_cast<size_t>(min(n0 + row, p.N - 1)) * ng;
                 const int g0 = (ng * part) / TPR, g1 = (ng * (part + 1)) / TPR;
-                float mx = row_scale_max(p.scale, off, g0, g1, p.scale_kind);
+                uint32_t bm = 0u;
+                float mx = row_scale_max(p.scale, off, g0, g1, p.scale_kind, &bm);
 #pragma unroll
-                for (int o = 1; o < TPR; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-                if (part == 0) hd->binv[i & 1][row] = mx > 0.f ? 1.f / mx : 0.f;
+                for (int o = 1; o < TPR; o <<= 1) {
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                    bm = max(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+                }
+                if (part == 0) hd->binv[i & 1][row] = e8 ? __uint_as_float(bm) : (mx > 0.f ? 1.f / mx : 0.f);
                 named_barrier_sync(1, GM_DEC_THREADS);
 #pragma unroll
-                for (int h2 = 0; h2 < RPT; ++h2) binv[h2] = hd->binv[i & 1][r0 + RSTEP * h2];
+                for (int h2 = 0; h2 < RPT; ++h2) {
+                    binv[h2] = hd->binv[i & 1][r0 + RSTEP * h2];
+                    bmax[h2] = static_cast<int>(__float_as_uint(binv[h2]));
+                }
             }
             // this group's k-blocks inside the tile: first, first + NG, ... (nloc of them)
             const int first = done - i * nkb;
             const int nloc = first < nkb ? (nkb - first + GM_NG - 1) / GM_NG : 0;
-            // scale / rowmax of this thread's rows for PF of the group's k-blocks, loaded one batch
-            // ahead of their use: a global load in the k-block loop itself would stall every
-            // decode warp for an L2 round trip per k-block.
-            auto load_ratios = [&](int l0, float (*dst)[RPT]) {
+            const uint32_t half_off = (p.rb == 2 && (first & 1)) ? 64u : 0u;       // NG is even: the parity of kb is fixed
+            // The fold factor scale / rowmax of this thread's rows for PF of the group's k-blocks,
+            // loaded one batch ahead of their use (a global load inside the k-block loop would stall
+            // every decode warp for an L2 round trip). UE8M0: the factor is 2^e with e the byte
+            // difference, kept as an integer; float scales: the factor itself, as float bits.
+            auto load_ratios = [&](int l0, uint32_t (*dst)[RPT]) {
 #pragma unroll
                 for (int j = 0; j < PF; ++j) {
 #pragma unroll
-                    for (int h2 = 0; h2 < RPT; ++h2) dst[j][h2] = 1.f;
+                    for (int h2 = 0; h2 < RPT; ++h2) dst[j][h2] = e8 ? 0u : 0x3F800000u;
                     if (ng > 1 && l0 + j < nloc) {
-                        const int gi = min(((first + (l0 + j) * GM_NG) * GM_BK + c * 16) / p.G, ng - 1);
+                        const int u32 = (first + (l0 + j) * GM_NG) * 2 + (c >> 1);
+                        const int gi = min(g_shift >= 0 ? (u32 >> g_shift) : (u32 / g32), ng - 1);
 #pragma unroll
-                        for (int h2 = 0; h2 < RPT; ++h2) dst[j][h2] = load_scale(p.scale, srow[h2] + gi, p.scale_kind) * binv[h2];
+                        for (int h2 = 0; h2 < RPT; ++h2) {
+                            if (e8) dst[j][h2] = static_cast<uint32_t>(static_cast<int>(reinterpret_cast<const uint8_t*>(p.scale)[srow[h2] + gi]) - bmax[h2]);
+                            else dst[j][h2] = __float_as_uint(reinterpret_cast<const float*>(p.scale)[srow[h2] + gi] * binv[h2]);
+                        }
                     }
                 }
             };
-            float rcur[PF][RPT], rnext[PF][RPT];
+            uint32_t rcur[PF][RPT], rnext[PF][RPT];
             load_ratios(0, rcur);
             for (int l0 = 0; l0 < nloc; l0 += PF) {
                 load_ratios(l0 + PF, rnext);
 #pragma unroll
                 for (int j = 0; j < PF; ++j) {
                     if (l0 + j >= nloc) break;
-                    const int kb = first + (l0 + j) * GM_NG;
-                    const int acur = a_slot, rcur_slot = r_slot;
+                    const uint32_t st = stages_u32 + a_off, raw = raw_u32 + r_off + half_off;
+                    const uint32_t bar_full = full0 + a_bar, bar_empty = empty0 + a_bar;
+                    const uint32_t bar_rfull = rfull0 + r_bar, bar_rempty = rempty0 + r_bar;
                     const uint32_t apar = a_par, rpar = r_par;
                     const bool fresh = done < p.ns;          // the stage's first use: nothing to wait for
                     done += GM_NG;
-                    a_slot += GM_NG; if (a_slot >= p.ns) { a_slot -= p.ns; a_par ^= 1u; }
-                    r_slot += r_step; if (r_slot >= p.sr) { r_slot -= p.sr; r_par ^= 1u; }
-                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->raw_full[rcur_slot]), rpar, STATUS_GEMM_WAIT));
-                    if (ok && !fresh) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->empty[acur]), apar ^ 1u, STATUS_GEMM_WAIT));
+                    a_off += a_step; a_bar += GM_NG * 8;
+                    if (a_off >= a_ring) { a_off -= a_ring; a_bar -= static_cast<uint32_t>(p.ns * 8); a_par ^= 1u; }
+                    r_off += r_step; r_bar += r_slots * 8u;
+                    if (r_off >= r_ring) { r_off -= r_ring; r_bar -= static_cast<uint32_t>(p.sr * 8); r_par ^= 1u; }
+                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_rfull, rpar, STATUS_GEMM_WAIT));
+                    if (ok && !fresh) ok = __all_sync(0xffffffffu, mbar_wait(bar_empty, apar ^ 1u, STATUS_GEMM_WAIT));
                     if (!ok) continue;
-                    if (tg == 0) GM_TRACE(1, i * nkb + kb);
-                    uint8_t* st = stages + static_cast<size_t>(acur) * p.stage_bytes;
-                    const uint8_t* raw = raw_ring + static_cast<size_t>(rcur_slot) * raw_slot_bytes + (p.rb == 2 ? (kb & 1) * 64 : 0);
-                    const int rpitch = p.rb == 2 ? 128 : 64;
+                    if (tg == 0) GM_TRACE(1, i * nkb + first + (l0 + j) * GM_NG);
                     // all loads, then all conversions, then all stores: the rows of a thread are
                     // independent, and kept apart like this their latencies overlap
                     uint32_t h[RPT][8];
                     {
                         uint4 q[RPT];
 #pragma unroll
-                        for (int h2 = 0; h2 < RPT; ++h2)
-                            q[h2] = *reinterpret_cast<const uint4*>(raw + (r0 + RSTEP * h2) * rpitch + c * 16);
+                        for (int h2 = 0; h2 < RPT; ++h2) q[h2] = gm_lds128(raw + roff[h2]);
 #pragma unroll
                         for (int h2 = 0; h2 < RPT; ++h2) {
                             const uint32_t w[4] = {q[h2].x, q[h2].y, q[h2].z, q[h2].w};
@@ -414,19 +462,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         }
                     }
                     if (ng > 1) {
-                        // fold scale / rowmax in. A power of two inside fp16's normal range (1 included)
-                        // is one packed multiply with the same rounding as the general path: an FP32
-                        // multiply and one fp16 rounding. The choice is made for the whole warp.
+                        // Fold scale / rowmax in. A power of two inside fp16's normal range (1 included)
+                        // is one packed multiply with the same rounding as the general path (an FP32
+                        // multiply and one fp16 rounding); the choice is made for the whole warp.
+                        // UE8M0 factors are powers of two by construction: 2^e, e <= 0, whose fp16
+                        // bit pattern is (e + 15) << 10 while e >= -14.
                         bool pow2 = true;
 #pragma unroll
                         for (int h2 = 0; h2 < RPT; ++h2) {
-                            const uint32_t rb = __float_as_uint(rcur[j][h2]);
-                            pow2 = pow2 && (rb & 0x007FFFFFu) == 0u && rb >= 0x38800000u && rb <= 0x47000000u;
+                            const uint32_t rb = rcur[j][h2];
+                            pow2 = pow2 && (e8 ? static_cast<int>(rb) >= -14
+                                               : ((rb & 0x007FFFFFu) == 0u && rb >= 0x38800000u && rb <= 0x47000000u));
                         }
                         if (__all_sync(0xffffffffu, pow2)) {
 #pragma unroll
                             for (int h2 = 0; h2 < RPT; ++h2) {
-                                const __half2 r2 = __float2half2_rn(rcur[j][h2]);
+                                const uint32_t rb = rcur[j][h2];
+                                // fp16 bits of the factor, in both halves: from the exponent directly
+                                const uint32_t hb = e8 ? (rb + 15u) << 10 : ((rb >> 23) - 112u) << 10;
+                                const uint32_t r2u = hb * 0x00010001u;
+                                const __half2 r2 = *reinterpret_cast<const __half2*>(&r2u);
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) {
                                     __half2 o = __hmul2(*reinterpret_cast<__half2*>(&h[h2][e]), r2);
@@ -436,7 +491,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         } else {
 #pragma unroll
                             for (int h2 = 0; h2 < RPT; ++h2) {
-                                const float rt = rcur[j][h2];
+                                const uint32_t rb = rcur[j][h2];
+                                const float rt = e8 ? __uint_as_float(static_cast<uint32_t>(max(static_cast<int>(rb) + 127, 0)) << 23)
+                                                    : __uint_as_float(rb);
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) {
                                     float2 f = __half22float2(*reinterpret_cast<__half2*>(&h[h2][e]));
@@ -448,18 +505,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     }
 #pragma unroll
                     for (int h2 = 0; h2 < RPT; ++h2) {
-                        const int r = r0 + RSTEP * h2;
-                        uint8_t* arow = st + r * 128;
-                        *reinterpret_cast<uint4*>(arow + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(h[h2][0], h[h2][1], h[h2][2], h[h2][3]);
-                        *reinterpret_cast<uint4*>(arow + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(h[h2][4], h[h2][5], h[h2][6], h[h2][7]);
+                        gm_sts128(st + aoff0[h2], h[h2][0], h[h2][1], h[h2][2], h[h2][3]);
+                        gm_sts128(st + aoff1[h2], h[h2][4], h[h2][5], h[h2][6], h[h2][7]);
                     }
-                    if (tg == 0) GM_TRACE(7, i * nkb + kb);
+                    if (tg == 0) GM_TRACE(7, i * nkb + first + (l0 + j) * GM_NG);
                     fence_proxy_async_smem();        // generic-proxy stores -> visible to the tensor core
                     __syncwarp();
-                    if (tg == 0) GM_TRACE(2, i * nkb + kb);
+                    if (tg == 0) GM_TRACE(2, i * nkb + first + (l0 + j) * GM_NG);
                     if (lane == 0) {
-                        mbar_arrive(smem_u32(&hd->full[acur]));
-                        mbar_arrive(smem_u32(&hd->raw_empty[rcur_slot]));   // this warp has read its part of the raw slot
+                        mbar_arrive(bar_full);
+                        mbar_arrive(bar_rempty);     // this warp has read its part of the raw slot
                     }
                 }
 #pragma unroll
