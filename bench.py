@@ -445,8 +445,9 @@ def llama_decode_measurements(device, peaks, world, batches=(1, 4, 8), prompt=20
 
 def tp_gemm_measurements(device, peaks, world, rank):
     """Config 4: 28672 x 8192 E4M3FN weight with 32-wide UE8M0 K-groups, column-sharded across the
-    ranks, bf16 activations replicated, outputs all-gathered (NCCL). TFLOP/s of the whole job,
-    with and without the gather."""
+    ranks, bf16 activations replicated. TFLOP/s of the whole job three ways: shard only, shard +
+    NCCL all-gather, and the gather fused into the GEMM epilogue (peer stores into every rank's
+    symmetric-memory output, then one barrier)."""
     from tfp8 import _ext, synth
     lib = _ext.load()
     N, K = synth.GROUP_GEMM_SHAPE
@@ -455,12 +456,41 @@ def tp_gemm_measurements(device, peaks, world, rank):
     e8 = torch.randint(110, 118, (Nl, K // 32), dtype=torch.uint8, device=device)
     st = lambda: torch.cuda.current_stream().cuda_stream
     rows = []
+    # fused gather: two symmetric-memory outputs (alternating), written by every rank's epilogue
+    import ctypes
+    fused_error = None
+    try:
+        import torch.distributed._symmetric_memory as symm
+        Mmax = max(synth.PREFILL_M)
+        sbufs = [symm.empty((Mmax, N), dtype=torch.float16, device=device) for _ in range(2)]
+        shdls = [symm.rendezvous(b, torch.distributed.group.WORLD) for b in sbufs]
+    except Exception as e:                       # no peer-mapped memory on this box: NCCL numbers only
+        fused_error = f"{type(e).__name__}: {e}"[:200]
+    # every rank must take the same branch
+    flag = torch.tensor([1 if fused_error else 0], device=device)
+    torch.distributed.all_reduce(flag)
+    if int(flag) and not fused_error:
+        fused_error = "symmetric memory unavailable on another rank"
+    turn = [0]
     for M in synth.PREFILL_M:
         x = synth.activations(M, K, dtype=torch.bfloat16).to(device)
         x16 = torch.empty(M, K, dtype=torch.float16, device=device)
         xs = torch.empty(M, dtype=torch.float32, device=device)
         y = torch.empty(M, Nl, dtype=torch.float16, device=device)
         full = torch.empty(world * M, Nl, dtype=torch.float16, device=device)
+
+        def step_fused():
+            t = turn[0]
+            turn[0] = t ^ 1
+            ptrs = [int(shdls[t].buffer_ptrs[r]) for r in range(world)]
+            ptrs = ptrs[rank:] + ptrs[:rank]
+            arr = (ctypes.c_void_p * world)(*ptrs)
+            lib.tfp8b_prep(x.data_ptr(), 1, x16.data_ptr(), xs.data_ptr(), M, K, st())
+            rc = lib.tfp8b_gemm_scatter(x16.data_ptr(), xs.data_ptr(), q.data_ptr(), e8.data_ptr(), 1, None, arr, world, N,
+                                        rank * Nl, 0, M, Nl, K, 32, 0, st())
+            assert rc == 0, lib.tfp8b_last_error_string()
+            shdls[t].barrier()
+            return sbufs[t]
 
         def step(gather):
             lib.tfp8b_prep(x.data_ptr(), 1, x16.data_ptr(), xs.data_ptr(), M, K, st())
@@ -474,9 +504,24 @@ def tp_gemm_measurements(device, peaks, world, rank):
         barrier(world)
         t_n = max_over_ranks(time_eager(lambda: step(False), 4, 3), world, device)
         fl = 2.0 * M * N * K
-        rows.append({"M": M, "N": N, "K": K, "G": 32, "tp": world, "ms_with_gather": t_g * 1e3, "ms_without_gather": t_n * 1e3,
-                     "tflops_with_gather": fl / t_g / 1e12, "tflops_without_gather": fl / t_n / 1e12,
-                     "frac_tensor_peak_all_gpus": fl / t_g / 1e12 / (world * peaks["bf16_tflops"])})
+        row = {"M": M, "N": N, "K": K, "G": 32, "tp": world, "ms_with_gather": t_g * 1e3, "ms_without_gather": t_n * 1e3,
+               "tflops_with_gather": fl / t_g / 1e12, "tflops_without_gather": fl / t_n / 1e12,
+               "frac_tensor_peak_all_gpus": fl / t_g / 1e12 / (world * peaks["bf16_tflops"])}
+        if fused_error is None:
+            barrier(world)
+            t_f = max_over_ranks(time_eager(step_fused, 4, 3), world, device)
+            # the fused result must be what NCCL gathers: rank r's shard in columns [r*Nl, (r+1)*Nl)
+            step(True)
+            got = step_fused()[:M]
+            torch.cuda.synchronize()
+            want = full.view(world, M, Nl).permute(1, 0, 2).reshape(M, N)
+            row.update({"ms_fused_gather": t_f * 1e3, "fused_equals_nccl": bool(torch.equal(got, want)),
+                        "tflops_fused_gather": fl / t_f / 1e12,
+                        "frac_tensor_peak_all_gpus_fused": fl / t_f / 1e12 / (world * peaks["bf16_tflops"])})
+            barrier(world)
+        else:
+            row["fused_gather_unavailable"] = fused_error
+        rows.append(row)
         del x, x16, y, full
     return rows
 

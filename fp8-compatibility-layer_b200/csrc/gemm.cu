@@ -46,6 +46,7 @@ constexpr int GM_DEC_WARP0 = 4;                        // warps 0..3: raw produc
 constexpr int GM_EPI_WARP0 = GM_DEC_WARP0 + GM_DEC_WARPS;
 constexpr int GM_THREADS = (GM_EPI_WARP0 + 4) * 32;
 constexpr int GM_MAX_SLOTS = 8;     // per ring
+constexpr int GM_MAX_DST = 8;       // output destinations of one launch (one per GPU of a tensor-parallel group)
 constexpr int GM_HEADER = 2048;     // barriers, TMEM base, per-row scale reciprocals
 constexpr int GM_A_BYTES = GM_BM * GM_BK * 2;    // decoded fp16 tile
 constexpr int GM_RAW_BYTES = GM_BM * GM_BK;      // raw FP8 tile of one k-block
@@ -56,7 +57,9 @@ struct GemmParams {
     const float* xs;
     const void* scale;
     const float* bias;
-    void* y;
+    void* y[GM_MAX_DST];      // output buffers: this GPU's and, for a fused gather, every peer's
+    long long ldy, col0;      // row pitch of the outputs in elements; column where this call's N columns start
+    int ndst;
     int M, N, K, G, scale_kind, y_dt;
     int BN, tmem_cols, m_tiles, ntiles;
     int ns, sr;          // stages (decoded weight tile + activation tile), slots of the raw-code ring
@@ -554,8 +557,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = m0 + col + j;
-                        if (m < p.M)
-                            store_dt(p.y, static_cast<size_t>(m) * p.N + n, fmaf(__uint_as_float(v[j]) * sm, p.xs[m], b), p.y_dt);
+                        if (m < p.M) {
+                            const float val = fmaf(__uint_as_float(v[j]) * sm, p.xs[m], b);
+                            const size_t at = static_cast<size_t>(m) * p.ldy + p.col0 + n;
+                            store_dt(p.y[0], at, val, p.y_dt);
+                            // fused gather: the same element into every peer's buffer (plain stores over NVLink)
+                            for (int d = 1; d < p.ndst; ++d) store_dt(p.y[d], at, val, p.y_dt);
+                        }
                     }
                 }
             }
@@ -641,19 +649,33 @@ using namespace tfp8b;
 extern "C" int tfp8b_gemm(const void* x16, const float* xs, const uint8_t* codes, const void* scale, int scale_kind,
                           const float* bias, void* y, int y_dtype, int M, int N, int K, int G, int fmt,
                           tfp8b_stream_t stream) {
+    void* dst[1] = {y};
+    return tfp8b_gemm_scatter(x16, xs, codes, scale, scale_kind, bias, dst, 1, N, 0, y_dtype, M, N, K, G, fmt, stream);
+}
+
+extern "C" int tfp8b_gemm_scatter(const void* x16, const float* xs, const uint8_t* codes, const void* scale, int scale_kind,
+                                  const float* bias, void* const* y_dst, int n_dst, long long ldy, long long col0, int y_dtype,
+                                  int M, int N, int K, int G, int fmt, tfp8b_stream_t stream) {
     TFP8B_REQUIRE(M >= 0 && N >= 0 && K > 0 && G > 0, TFP8B_ERR_INVALID, "tfp8b_gemm: bad size M=%d N=%d K=%d G=%d", M, N, K, G);
     TFP8B_REQUIRE(y_dtype >= 0 && y_dtype <= 2, TFP8B_ERR_INVALID, "tfp8b_gemm: bad dtype");
     TFP8B_REQUIRE(fmt == TFP8B_E4M3FN || fmt == TFP8B_E5M2, TFP8B_ERR_INVALID, "tfp8b_gemm: bad fmt %d", fmt);
     TFP8B_REQUIRE(scale_kind == TFP8B_SCALE_F32 || scale_kind == TFP8B_SCALE_UE8M0, TFP8B_ERR_INVALID,
                   "tfp8b_gemm: bad scale_kind %d", scale_kind);
+    TFP8B_REQUIRE(y_dst && n_dst >= 1 && n_dst <= GM_MAX_DST, TFP8B_ERR_INVALID, "tfp8b_gemm: 1..%d output buffers, got %d",
+                  GM_MAX_DST, n_dst);
+    TFP8B_REQUIRE(col0 >= 0 && ldy >= col0 + N, TFP8B_ERR_INVALID,
+                  "tfp8b_gemm: columns [%lld, %lld) do not fit a row pitch of %lld", col0, col0 + N, ldy);
     if (M == 0 || N == 0) return TFP8B_OK;
-    TFP8B_REQUIRE(x16 && xs && codes && scale && y, TFP8B_ERR_INVALID, "tfp8b_gemm: null pointer");
+    TFP8B_REQUIRE(x16 && xs && codes && scale, TFP8B_ERR_INVALID, "tfp8b_gemm: null pointer");
+    for (int d = 0; d < n_dst; ++d) TFP8B_REQUIRE(y_dst[d], TFP8B_ERR_INVALID, "tfp8b_gemm: null output pointer %d", d);
     TFP8B_REQUIRE(K % 32 == 0 && G % 32 == 0 && K % G == 0, TFP8B_ERR_UNSUPPORTED,
                   "tfp8b_gemm: need K %% 32 == 0, G %% 32 == 0, K %% G == 0 (K=%d G=%d)", K, G);
     TFP8B_REQUIRE(((reinterpret_cast<uintptr_t>(x16) | reinterpret_cast<uintptr_t>(codes)) & 15u) == 0, TFP8B_ERR_INVALID,
                   "tfp8b_gemm: x16 and codes must be 16-byte aligned");
     GemmParams p;
-    p.xs = xs; p.scale = scale; p.bias = bias; p.y = y;
+    p.xs = xs; p.scale = scale; p.bias = bias;
+    for (int d = 0; d < GM_MAX_DST; ++d) p.y[d] = d < n_dst ? y_dst[d] : nullptr;
+    p.ndst = n_dst; p.ldy = ldy; p.col0 = col0;
     p.M = M; p.N = N; p.K = K; p.G = G; p.scale_kind = scale_kind; p.y_dt = y_dtype;
     int bn = 16;
     while (bn < M && bn < 256) bn <<= 1;

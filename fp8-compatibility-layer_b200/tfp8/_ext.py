@@ -40,6 +40,7 @@ _SIGNATURES = {
     "tfp8b_gemv": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_gemv_ex": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.c_uint, _P], _I),
     "tfp8b_gemm": ([_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
+    "tfp8b_gemm_scatter": ([_P, _P, _P, _P, _I, _P, _P, _I, ctypes.c_longlong, ctypes.c_longlong, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_linear_static": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_epilogue": ([_P, _P, _P, _P, _I, _I, _I, _I, _P], _I),
     "tfp8b_rope_kv_store": ([_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
@@ -304,6 +305,23 @@ def gemm_prepared(x16, xs, qweight, lut16, wscale, bias, out_dtype, group_size, 
         with torch.cuda.device(dev):
             _gemm(x16.contiguous(), xs, qweight, wscale, bias, y, M, N, K, group_size, fmt, dev)
     return y
+
+
+def gemm_scatter(x16, xs, qweight, wscale, bias, dst_ptrs, ldy, col0, out_dtype, group_size, fmt="e4m3fn"):
+    """Tile GEMM on prepared activations whose N output columns are written at columns
+    [col0, col0 + N) of every buffer in `dst_ptrs` (device addresses of [M, ldy] arrays of
+    `out_dtype`: this GPU's and, for a fused all-gather, the peers' mapped buffers)."""
+    dev = _need_cuda(x16, xs, qweight, wscale, bias)
+    M, K = x16.shape
+    N = qweight.shape[0]
+    if M == 0 or N == 0:
+        return
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_gemm_scatter(x16.contiguous().data_ptr(), xs.data_ptr(), qweight.data_ptr(), wscale.data_ptr(),
+                                       _scale_kind(wscale), bias.data_ptr() if bias is not None else 0, arr, len(dst_ptrs),
+                                       int(ldy), int(col0), _DT[out_dtype], M, N, K, group_size, FMT_ID[fmt], _stream(dev))
+    _check(rc, "tfp8b_gemm_scatter")
 
 
 def epilogue_into(y, acc, xs, bias, n0=0):

@@ -14,6 +14,13 @@ single-GPU layer has:
 One process per GPU; the collectives are NCCL over NVLink on CUDA tensors (gloo on CPU tensors,
 which is how the host logic is tested without GPUs). Summation order differs from one GPU, so
 row-parallel results match within the float32 tolerance, not bit for bit.
+
+Fused gather (`gather_output="fused"`, CUDA, more than 8 activation rows): the column-parallel
+layer's tile GEMM stores its column shard from the epilogue straight into every rank's full
+output buffer -- symmetric memory, plain peer stores over NVLink -- so the all-gather overlaps
+the main loop instead of following it as a separate NCCL call; one barrier orders the ranks
+before the result is read. Two output buffers alternate, so a call never overwrites a result a
+peer may still be reading.
 """
 import torch
 import torch.distributed as dist
@@ -68,9 +75,50 @@ class ColumnParallelFP8Linear(nn.Module):
         per = N // world
         return cls(_slice_layer(full, rows=(rank * per, (rank + 1) * per)), N, group, gather_output)
 
+    # ------------------------------------------------------------------ fused gather
+    def _symm_buffers(self, rows, dtype, device):
+        """Two [rows, out_features] symmetric-memory outputs and their handles, grown on demand.
+        Every rank calls this with the same arguments in the same order (it is a collective)."""
+        import torch.distributed._symmetric_memory as symm
+        st = getattr(self, "_symm", None)
+        if st is None or st["rows"] < rows or st["dtype"] != dtype:
+            group = self.group if self.group is not None else dist.group.WORLD
+            bufs, hdls = [], []
+            for _ in range(2):
+                b = symm.empty((rows, self.out_features), dtype=dtype, device=device)
+                hdls.append(symm.rendezvous(b, group.group_name))
+                bufs.append(b)
+            st = self._symm = {"rows": rows, "dtype": dtype, "bufs": bufs, "hdls": hdls, "turn": 0}
+        return st
+
+    def _forward_fused(self, x):
+        from . import _ext
+        loc = self.local
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        M = x2.shape[0]
+        rank, world = _world(self.group)
+        st = self._symm_buffers(M, loc.out_dtype, x.device)
+        turn = st["turn"]
+        st["turn"] = turn ^ 1
+        buf, hdl = st["bufs"][turn], st["hdls"][turn]
+        if x2.dtype not in _ext._TAG:
+            x2 = x2.float()
+        x16, xs = _ext.prepare_activations(x2)
+        ptrs = [int(hdl.buffer_ptrs[r]) for r in range(world)]
+        ptrs = ptrs[rank:] + ptrs[:rank]                       # own buffer first
+        _ext.gemm_scatter(x16, xs, loc.qweight, loc._kernel_scale(), loc.bias_f32, ptrs, self.out_features,
+                          rank * loc.out_features, loc.out_dtype, loc.group_size, loc.fmt)
+        loc.stats["gemm"] += 1
+        hdl.barrier()                                          # every rank's shard has landed everywhere
+        return buf[:M].view(*lead, self.out_features)
+
     def forward(self, x):
-        y = self.local(x)
         _, world = _world(self.group)
+        if (self.gather_output == "fused" and world > 1 and x.is_cuda and x.numel() // x.shape[-1] > 8
+                and self.local._shape_ok and world <= 8):
+            return self._forward_fused(x)
+        y = self.local(x)
         if not self.gather_output or world == 1:
             return y
         lead = y.shape[:-1]

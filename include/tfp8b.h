@@ -176,6 +176,17 @@ TFP8B_API int tfp8b_rope_kv_store(const void* qkv, int dtype, const long long* p
 TFP8B_API int tfp8b_silu_mul(const void* gate_up, void* out, int dtype, long long rows, int F,
                   tfp8b_stream_t stream);
 
+/* tfp8b_gemm whose N output columns land at columns [col0, col0 + N) of wider outputs (row pitch
+ * ldy elements), in n_dst buffers at once (1..8; y_dst is a HOST array of device pointers). With
+ * the buffers of every GPU of a tensor-parallel group (peer-mapped memory: CUDA IPC, symmetric
+ * memory) a column-sharded layer writes its shard straight into every rank's full output: the
+ * all-gather happens in the GEMM's epilogue, as plain stores over NVLink, overlapped with the
+ * main loop of the next tiles. The caller orders the ranks afterwards (a barrier) before anyone
+ * reads. No counterpart in the reference (single GPU). */
+TFP8B_API int tfp8b_gemm_scatter(const void* x16, const float* xs, const uint8_t* codes, const void* scale,
+                  int scale_kind, const float* bias, void* const* y_dst, int n_dst, long long ldy,
+                  long long col0, int y_dtype, int M, int N, int K, int G, int fmt, tfp8b_stream_t stream);
+
 /* x[r, :] += delta[r, :] (delta may be NULL), then out[r, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps)
  * * weight: the residual update and the RMSNorm that follows it in a decoder block, one launch
  * (reference: RMSNorm and the residual adds of tfp8/examples/demo_llm.py:30-39, 98-101; same

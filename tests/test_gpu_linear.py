@@ -102,6 +102,27 @@ def test_gemm_many_stages_and_tiles():
     _check(64, 1000, 8192, 32, torch.float32)
 
 
+def test_gemm_scatter_window_and_destinations():
+    """The scatter form of the tile GEMM (the fused all-gather of a column-parallel layer): the N
+    columns land in a column window of wider outputs, in several buffers at once, bit-identical
+    to the plain call, and nothing outside the window is touched."""
+    from tfp8 import _ext
+    for (M, N, K, G, dt) in ((40, 256, 512, None, torch.float16), (300, 136, 1024, 128, torch.bfloat16)):
+        f = _layer(N, K, G, seed=M)
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        x16, xs = _ext.prepare_activations(x)
+        want = _ext.gemm_prepared(x16, xs, f.qweight, None, f.weight_scale, f.bias_f32, dt, f.group_size, f.fmt)
+        ldy, col0 = 3 * N + 8, N + 8
+        bufs = [torch.full((M, ldy), 7.0, dtype=dt, device="cuda") for _ in range(3)]
+        _ext.gemm_scatter(x16, xs, f.qweight, f.weight_scale, f.bias_f32, [b.data_ptr() for b in bufs], ldy, col0, dt,
+                          f.group_size, f.fmt)
+        for b in bufs:
+            assert torch.equal(b[:, col0:col0 + N], want)
+            assert bool((b[:, :col0] == 7.0).all()) and bool((b[:, col0 + N:] == 7.0).all())
+    with pytest.raises(RuntimeError):                               # window wider than the row pitch
+        _ext.gemm_scatter(x16, xs, f.qweight, f.weight_scale, f.bias_f32, [bufs[0].data_ptr()], N, 8, dt, f.group_size, f.fmt)
+
+
 def test_folded_group_scales():
     """Random codes, scales spanning 2^-20: power-of-two scales must stay at FP32-accumulation
     error, arbitrary scales within one fp16 rounding of the folded weight."""
