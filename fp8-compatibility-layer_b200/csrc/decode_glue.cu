@@ -6,7 +6,9 @@
 //                  at the tokens' positions -- one launch instead of ~16;
 //   silu_mul       silu(gate) * up on the fused gate/up projection -- one launch instead of 2-3;
 //   add_rmsnorm    residual += delta, then RMSNorm of the residual -- one launch instead of 2;
-//   argmax         greedy token choice over the vocabulary, one CTA per row.
+//   argmax         greedy token choice over the vocabulary, one CTA per row;
+//   attn_decode    one-query attention over the static KV cache (grouped-query heads), the KV
+//                  range split across CTAs and merged by a second small kernel.
 // All are plain bandwidth- or latency-bound kernels on 16-bit activations. They are launched
 // with programmatic stream serialization and release their dependents at once: the FP8 GEMV
 // that follows starts streaming its weights while the helper is still running, and waits for
@@ -229,6 +231,191 @@ __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const T* __restr
     }
 }
 
+// ------------------------------------------------------------------ decode attention
+// One query token per sequence against cache positions [0, pos]: out[b, h, :] = softmax(q . K^T
+// / sqrt(hd)) V. The KV range of one (sequence, KV head) is split into chunks of at most 64
+// positions, one CTA each, so that a batch-1 step still fills the machine; a CTA serves up to
+// four of the query heads that share its KV head, and writes an unnormalised partial (running
+// maximum, sum, weighted V) that attn_merge_kernel combines. Every global load of a phase is
+// issued before its first use (the chunk is short: one memory round trip per phase). FP32
+// arithmetic throughout. hd = 128.
+constexpr int ATT_THREADS = 128;
+constexpr int ATT_HD = 128;
+constexpr int ATT_G = 4;             // query heads per CTA (a KV head with more is served by several CTAs)
+constexpr int ATT_CHUNK = 64;        // positions per CTA at most
+constexpr int ATT_PW = ATT_CHUNK / (ATT_THREADS / 32);      // positions per warp: 16
+template <typename T>
+__global__ void __launch_bounds__(ATT_THREADS) attn_partial_kernel(const T* __restrict__ q, const T* __restrict__ kc,
+                                                                   const T* __restrict__ vc, const long long* __restrict__ pos,
+                                                                   float* __restrict__ part, int H, int KV, int S, int nsplit,
+                                                                   float scale_log2e) {
+    using P = typename pair_of<T>::type;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int G = H / KV, ngrp = (G + ATT_G - 1) / ATT_G;
+    int id = blockIdx.x;
+    const int split = id % nsplit; id /= nsplit;
+    const int grp = id % ngrp; id /= ngrp;
+    const int kvh = id % KV, b = id / KV;
+    const int h0 = kvh * G + grp * ATT_G, nh = min(ATT_G, G - grp * ATT_G);      // this CTA's query heads
+    const int len = static_cast<int>(min(static_cast<long long>(S), pos[0] + 1));
+    const int chunk = min(ATT_CHUNK, (len + nsplit - 1) / nsplit);
+    const int s0 = split * chunk, n = max(0, min(len, s0 + chunk) - s0);
+    __shared__ float s_sc[ATT_G][ATT_CHUNK];
+    __shared__ float s_m[ATT_G], s_l[ATT_G];
+    __shared__ float s_acc[ATT_THREADS / 32][ATT_G][ATT_HD];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const T* kbase = kc + ((static_cast<size_t>(b) * KV + kvh) * S + s0) * ATT_HD;
+    const T* vbase = vc + ((static_cast<size_t>(b) * KV + kvh) * S + s0) * ATT_HD;
+    // ---- scores: warp w takes positions [16 w, 16 w + 16); 8 lanes per position, 16 dims per lane
+    {
+        const int sub = lane & 7, slot = lane >> 3;
+        uint4 kr[ATT_PW / 4][2];
+#pragma unroll
+        for (int it = 0; it < ATT_PW / 4; ++it) {
+            const int j = warp * ATT_PW + it * 4 + slot;
+            if (j < n) {
+                const uint4* kp = reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(j) * ATT_HD + sub * 16);
+                kr[it][0] = kp[0]; kr[it][1] = kp[1];
+            } else {
+                kr[it][0] = kr[it][1] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        float qf[ATT_G][16];
+#pragma unroll
+        for (int g = 0; g < ATT_G; ++g) {
+            const T* qp = q + (static_cast<size_t>(b) * H + h0 + min(g, nh - 1)) * ATT_HD + sub * 16;
+            const uint4 a0 = reinterpret_cast<const uint4*>(qp)[0], a1 = reinterpret_cast<const uint4*>(qp)[1];
+            const P* p0 = reinterpret_cast<const P*>(&a0);
+            const P* p1 = reinterpret_cast<const P*>(&a1);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f0 = unpack2(p0[i]), f1 = unpack2(p1[i]);
+                qf[g][2 * i] = f0.x * scale_log2e; qf[g][2 * i + 1] = f0.y * scale_log2e;
+                qf[g][8 + 2 * i] = f1.x * scale_log2e; qf[g][9 + 2 * i] = f1.y * scale_log2e;
+            }
+        }
+#pragma unroll
+        for (int it = 0; it < ATT_PW / 4; ++it) {
+            const int j = warp * ATT_PW + it * 4 + slot;
+            float kf[16];
+            const P* p0 = reinterpret_cast<const P*>(&kr[it][0]);
+            const P* p1 = reinterpret_cast<const P*>(&kr[it][1]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f0 = unpack2(p0[i]), f1 = unpack2(p1[i]);
+                kf[2 * i] = f0.x; kf[2 * i + 1] = f0.y; kf[8 + 2 * i] = f1.x; kf[9 + 2 * i] = f1.y;
+            }
+#pragma unroll
+            for (int g = 0; g < ATT_G; ++g) {
+                float d = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) d = fmaf(qf[g][i], kf[i], d);
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                if (sub == 0 && j < n) s_sc[g][j] = d;
+            }
+        }
+    }
+    // ---- the V rows of this warp's positions, requested now, used after the softmax
+    uint2 vr[ATT_PW];                                  // lane owns dims 4 lane .. 4 lane + 3
+#pragma unroll
+    for (int it = 0; it < ATT_PW; ++it) {
+        const int j = warp * ATT_PW + it;
+        vr[it] = j < n ? *reinterpret_cast<const uint2*>(vbase + static_cast<size_t>(j) * ATT_HD + lane * 4) : make_uint2(0u, 0u);
+    }
+    __syncthreads();
+    // ---- per head: maximum, exponentials, sum (warp g serves head g)
+    if (warp < nh) {
+        const int g = warp;
+        float m = -INFINITY;
+        for (int j = lane; j < n; j += 32) m = fmaxf(m, s_sc[g][j]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float l = 0.f;
+        for (int j = lane; j < n; j += 32) {
+            const float e = exp2f(s_sc[g][j] - m);
+            s_sc[g][j] = e;
+            l += e;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        if (lane == 0) { s_m[g] = m; s_l[g] = l; }
+    }
+    __syncthreads();
+    // ---- weighted V over this warp's positions, then the four warps' sums are added
+    float acc[ATT_G][4];
+#pragma unroll
+    for (int g = 0; g < ATT_G; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+#pragma unroll
+    for (int it = 0; it < ATT_PW; ++it) {
+        const int j = warp * ATT_PW + it;
+        if (j < n) {
+            const P* vp = reinterpret_cast<const P*>(&vr[it]);
+            const float2 v01 = unpack2(vp[0]), v23 = unpack2(vp[1]);
+#pragma unroll
+            for (int g = 0; g < ATT_G; ++g) {
+                const float w = s_sc[g][j];
+                acc[g][0] = fmaf(w, v01.x, acc[g][0]); acc[g][1] = fmaf(w, v01.y, acc[g][1]);
+                acc[g][2] = fmaf(w, v23.x, acc[g][2]); acc[g][3] = fmaf(w, v23.y, acc[g][3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < ATT_G; ++g)
+        *reinterpret_cast<float4*>(&s_acc[warp][g][lane * 4]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    __syncthreads();
+    // partial record per (b, head, split): [m, l, acc[128]]
+    for (int g = 0; g < nh; ++g) {
+        float* rec = part + ((static_cast<size_t>(b) * H + h0 + g) * nsplit + split) * (ATT_HD + 2);
+        rec[2 + threadIdx.x] = s_acc[0][g][threadIdx.x] + s_acc[1][g][threadIdx.x] + s_acc[2][g][threadIdx.x] + s_acc[3][g][threadIdx.x];
+        if (threadIdx.x == 0) { rec[0] = n > 0 ? s_m[g] : -INFINITY; rec[1] = n > 0 ? s_l[g] : 0.f; }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ATT_HD) attn_merge_kernel(const float* __restrict__ part, T* __restrict__ out, int nsplit) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* rec = part + static_cast<size_t>(blockIdx.x) * nsplit * (ATT_HD + 2);     // blockIdx.x = b * H + h
+    __shared__ float s_w[128];                          // weight of each chunk (nsplit <= 128)
+    __shared__ float s_norm;
+    // the chunks' maxima and sums, one per thread, then the weights exp2(m_s - m) and the normaliser
+    float ms = -INFINITY, ls = 0.f;
+    if (static_cast<int>(threadIdx.x) < nsplit) { ms = rec[threadIdx.x * (ATT_HD + 2)]; ls = rec[threadIdx.x * (ATT_HD + 2) + 1]; }
+    float m = ms;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __shared__ float s_red[4];
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    const float w = ms == -INFINITY ? 0.f : exp2f(ms - m);
+    s_w[threadIdx.x] = w;
+    float l = w * ls;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = l;
+    __syncthreads();
+    if (threadIdx.x == 0) s_norm = 1.f / (s_red[0] + s_red[1] + s_red[2] + s_red[3]);
+    __syncthreads();
+    // thread d: weighted sum of the chunks' dim d, loads eight at a time
+    float a = 0.f;
+    const float* col = rec + 2 + threadIdx.x;
+    int s = 0;
+    for (; s + 8 <= nsplit; s += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = col[static_cast<size_t>(s + u) * (ATT_HD + 2)];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) a = fmaf(s_w[s + u], v[u], a);
+    }
+    for (; s < nsplit; ++s) a = fmaf(s_w[s], col[static_cast<size_t>(s) * (ATT_HD + 2)], a);
+    store_as(out + static_cast<size_t>(blockIdx.x) * ATT_HD + threadIdx.x, a * s_norm);
+}
+
 // Launch with programmatic stream serialization (the kernel may start while its predecessor is
 // finishing and waits for it itself); TFP8B_NO_PDL=1 in the environment makes it a plain launch.
 template <typename... KArgs, typename... Args>
@@ -308,6 +495,42 @@ extern "C" int tfp8b_add_rmsnorm(void* x, const void* delta, const void* weight,
     return launch_pdl("tfp8b_add_rmsnorm", add_rmsnorm_kernel<__nv_bfloat16>, static_cast<int>(rows), ADD_NORM_THREADS, st,
                       static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(weight),
                       static_cast<__nv_bfloat16*>(out), dim, eps);
+}
+
+extern "C" int tfp8b_attn_decode(const void* q, const void* k_cache, const void* v_cache, const long long* pos, void* out,
+                                 float* scratch, long long scratch_floats, int dtype, int B, int H, int KV, int hd, int max_seq,
+                                 tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(dtype == TFP8B_F16 || dtype == TFP8B_BF16, TFP8B_ERR_UNSUPPORTED, "tfp8b_attn_decode: f16 / bf16 only");
+    TFP8B_REQUIRE(hd == ATT_HD, TFP8B_ERR_UNSUPPORTED, "tfp8b_attn_decode: head_dim %d (only %d is built)", hd, ATT_HD);
+    TFP8B_REQUIRE(B >= 0 && H > 0 && KV > 0 && H % KV == 0 && max_seq > 0, TFP8B_ERR_INVALID,
+                  "tfp8b_attn_decode: bad shape (H=%d KV=%d)", H, KV);
+    if (B == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(q && k_cache && v_cache && pos && out && scratch, TFP8B_ERR_INVALID, "tfp8b_attn_decode: null pointer");
+    TFP8B_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache)) & 15u) == 0, TFP8B_ERR_INVALID,
+                  "tfp8b_attn_decode: q and k_cache must be 16-byte aligned");
+    // chunks of at most ATT_CHUNK positions cover the whole cache
+    const int nsplit = (max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
+    TFP8B_REQUIRE(nsplit <= 128, TFP8B_ERR_UNSUPPORTED, "tfp8b_attn_decode: max_seq %d (at most %d is built)", max_seq, 128 * ATT_CHUNK);
+    const int ngrp = (H / KV + ATT_G - 1) / ATT_G;
+    const long long need = static_cast<long long>(B) * H * nsplit * (ATT_HD + 2);
+    TFP8B_REQUIRE(scratch_floats >= need, TFP8B_ERR_INVALID, "tfp8b_attn_decode: scratch of %lld floats, %lld needed", scratch_floats, need);
+    const float scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(hd));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc;
+    if (dtype == TFP8B_F16) {
+        rc = launch_pdl("tfp8b_attn_decode", attn_partial_kernel<__half>, B * KV * ngrp * nsplit, ATT_THREADS, st, static_cast<const __half*>(q),
+                        static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), pos, scratch, H, KV, max_seq, nsplit,
+                        scale_log2e);
+        if (rc != TFP8B_OK) return rc;
+        return launch_pdl("tfp8b_attn_decode", attn_merge_kernel<__half>, B * H, ATT_HD, st, static_cast<const float*>(scratch),
+                          static_cast<__half*>(out), nsplit);
+    }
+    rc = launch_pdl("tfp8b_attn_decode", attn_partial_kernel<__nv_bfloat16>, B * KV * ngrp * nsplit, ATT_THREADS, st,
+                    static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
+                    static_cast<const __nv_bfloat16*>(v_cache), pos, scratch, H, KV, max_seq, nsplit, scale_log2e);
+    if (rc != TFP8B_OK) return rc;
+    return launch_pdl("tfp8b_attn_decode", attn_merge_kernel<__nv_bfloat16>, B * H, ATT_HD, st, static_cast<const float*>(scratch),
+                      static_cast<__nv_bfloat16*>(out), nsplit);
 }
 
 extern "C" int tfp8b_argmax(const void* logits, int dtype, long long* out, long long rows, long long n, long long row_pitch,

@@ -27,6 +27,8 @@
 // No fp16 copy of the weights ever exists outside shared memory. Every mbarrier wait is bounded;
 // a wait that runs out sets a status bit, and the thread keeps walking its loops without waiting
 // so that every barrier is still met and the CTA ends.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace tfp8b {
@@ -60,6 +62,7 @@ struct GemmParams {
     void* y[GM_MAX_DST];      // output buffers: this GPU's and, for a fused gather, every peer's
     long long ldy, col0;      // row pitch of the outputs in elements; column where this call's N columns start
     int ndst;
+    int push;                 // peers are served by the push warp (16-byte copies of whole tile rows), not by the epilogue
     int M, N, K, G, scale_kind, y_dt;
     int BN, tmem_cols, m_tiles, ntiles;
     int ns, sr;          // stages (decoded weight tile + activation tile), slots of the raw-code ring
@@ -75,7 +78,7 @@ struct GemmHeader {
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint32_t tmem_base;
-    uint32_t pad;
+    uint32_t tiles_stored;    // epilogue warps that have finished writing a tile to the local output (4 per tile)
     float binv[2][GM_BM];   // per weight row: 1 / max_g scale[n,g], double-buffered by tile parity
 };
 static_assert(sizeof(GemmHeader) <= GM_HEADER, "header too large");
@@ -216,6 +219,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             mbar_init(smem_u32(&hd->acc_full[b]), p.nmma);
             mbar_init(smem_u32(&hd->acc_empty[b]), 4);
         }
+        hd->tiles_stored = 0u;
         mbar_fence_init();
         fence_proxy_async_smem();
         tma_prefetch_desc(&tm_w);
@@ -526,6 +530,52 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     for (int h2 = 0; h2 < RPT; ++h2) rcur[j][h2] = rnext[j][h2];
             }
         }
+    } else if (warp == 3) {
+        // ---------------------------------------------------------------- push warp (fused gather)
+        // The accumulator is transposed (a warp owns 32 output columns), so an epilogue store is
+        // 64 contiguous bytes: too small to keep NVLink busy, and the epilogue would stall the
+        // MMA behind it. The epilogue therefore writes the tile to the LOCAL output only, and this
+        // warp copies each finished tile to the peers from there (L2-hot), 16 bytes per lane,
+        // whole 256-byte tile rows per request, while the next tile's main loop runs. (Warp 3 is
+        // the second MMA issuer of narrow tiles; they keep the element-wise peer stores.)
+        if (p.push) {
+            const int esz = p.y_dt == TFP8B_F32 ? 4 : 2;
+            const long long t0 = clock64();
+            bool ok = true;
+            for (int i = 0; i < my_tiles && ok; ++i) {
+                const uint32_t need = 4u * static_cast<uint32_t>(i + 1);
+                while (*reinterpret_cast<volatile uint32_t*>(&hd->tiles_stored) < need) {      // bounded wait
+                    __nanosleep(200);
+                    if (clock64() - t0 > (1ll << 34)) { ok = false; break; }
+                }
+                if (!ok) { if (lane == 0) atomicOr(&g_status, STATUS_GEMM_WAIT); break; }
+                __threadfence_block();
+                const int m0 = tile_m0(i), n0 = tile_n0(i);
+                const int rows = min(p.BN, p.M - m0), cols = min(GM_BM, p.N - n0);
+                const int cpr = cols * esz / 16;                                    // 16-byte chunks per tile row
+                const int total = rows * cpr;
+                const size_t row_pitch = static_cast<size_t>(p.ldy) * esz;
+                const size_t base = (static_cast<size_t>(m0) * p.ldy + p.col0 + n0) * esz;
+                const uint8_t* src = reinterpret_cast<const uint8_t*>(p.y[0]) + base;
+                for (int c0 = lane; c0 < total; c0 += 32 * 4) {
+                    uint4 v[4];
+                    size_t off[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int c = c0 + 32 * u;
+                        const int r = c / cpr, k = c - r * cpr;
+                        off[u] = static_cast<size_t>(r) * row_pitch + static_cast<size_t>(k) * 16;
+                        if (c < total) v[u] = __ldcg(reinterpret_cast<const uint4*>(src + off[u]));
+                    }
+                    for (int d = 1; d < p.ndst; ++d) {
+                        uint8_t* dst = reinterpret_cast<uint8_t*>(p.y[d]) + base;
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            if (c0 + 32 * u < total) *reinterpret_cast<uint4*>(dst + off[u]) = v[u];
+                    }
+                }
+            }
+        }
     } else if (warp >= GM_EPI_WARP0) {
         // ---------------------------------------------------------------- epilogue warps
         const int quarter = warp & 3;                           // TMEM lanes this warp may read
@@ -561,15 +611,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                             const float val = fmaf(__uint_as_float(v[j]) * sm, p.xs[m], b);
                             const size_t at = static_cast<size_t>(m) * p.ldy + p.col0 + n;
                             store_dt(p.y[0], at, val, p.y_dt);
-                            // fused gather: the same element into every peer's buffer (plain stores over NVLink)
-                            for (int d = 1; d < p.ndst; ++d) store_dt(p.y[d], at, val, p.y_dt);
+                            // fused gather without the push warp (unaligned windows): element-wise peer stores
+                            if (!p.push)
+                                for (int d = 1; d < p.ndst; ++d) store_dt(p.y[d], at, val, p.y_dt);
                         }
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&hd->acc_empty[buf]));
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&hd->acc_empty[buf]));
+                if (p.push) { __threadfence_block(); atomicAdd(&hd->tiles_stored, 1u); }   // this warp's part of the tile is in the local output
+            }
         }
     }
     tc_fence_before();
@@ -676,6 +730,14 @@ extern "C" int tfp8b_gemm_scatter(const void* x16, const float* xs, const uint8_
     p.xs = xs; p.scale = scale; p.bias = bias;
     for (int d = 0; d < GM_MAX_DST; ++d) p.y[d] = d < n_dst ? y_dst[d] : nullptr;
     p.ndst = n_dst; p.ldy = ldy; p.col0 = col0;
+    // whole 16-byte chunks and 16-byte aligned rows everywhere: the push warp serves the peers
+    {
+        const long long esz = y_dtype == TFP8B_F32 ? 4 : 2;
+        bool aligned = (ldy * esz) % 16 == 0 && (col0 * esz) % 16 == 0 && (static_cast<long long>(N) * esz) % 16 == 0;
+        for (int d = 0; d < n_dst; ++d) aligned = aligned && (reinterpret_cast<uintptr_t>(y_dst[d]) & 15u) == 0;
+        static const int use_push = [] { const char* v = getenv("TFP8B_GEMM_PUSH"); return v && v[0] == '1'; }();
+        p.push = (use_push && n_dst > 1 && aligned) ? 1 : 0;
+    }
     p.M = M; p.N = N; p.K = K; p.G = G; p.scale_kind = scale_kind; p.y_dt = y_dtype;
     int bn = 16;
     while (bn < M && bn < 256) bn <<= 1;
@@ -686,6 +748,7 @@ extern "C" int tfp8b_gemm_scatter(const void* x16, const float* xs, const uint8_
     // option: that variant ended every BN = 256 launch with a launch failure.)
     p.nmma = (bn <= 128 && nkb >= 4) ? 2 : 1;
     p.tmem_cols = 2 * p.nmma * bn < 32 ? 32 : 2 * p.nmma * bn;
+    if (p.nmma != 1) p.push = 0;                             // warp 3 issues MMAs there
     p.m_tiles = (M + bn - 1) / bn;
     p.ntiles = p.m_tiles * ((N + GM_BM - 1) / GM_BM);
     // Shared memory: four stages (the groups' tiles in decode, the one in the MMA, one spare), the

@@ -46,6 +46,7 @@ _SIGNATURES = {
     "tfp8b_rope_kv_store": ([_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_silu_mul": ([_P, _P, _I, ctypes.c_longlong, _I, _P], _I),
     "tfp8b_add_rmsnorm": ([_P, _P, _P, _P, _I, ctypes.c_longlong, _I, ctypes.c_float, _P], _I),
+    "tfp8b_attn_decode": ([_P, _P, _P, _P, _P, _P, ctypes.c_longlong, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_argmax": ([_P, _I, _P, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _P], _I),
 }
 
@@ -390,4 +391,28 @@ def argmax_into(out, logits):
         rc = load().tfp8b_argmax(logits.data_ptr(), _DT[logits.dtype], out.data_ptr(), logits.shape[0], logits.shape[1],
                                  logits.stride(0), _stream(dev))
     _check(rc, "tfp8b_argmax")
+    return out
+
+
+def attn_scratch_floats(batch, n_heads, max_seq, head_dim=128):
+    """Size of the split-KV scratch of `attn_decode`: one (max, sum, weighted V) record per head and
+    64-position chunk of the cache."""
+    return batch * n_heads * ((max_seq + 63) // 64) * (head_dim + 2)
+
+
+def attn_decode(q, k_cache, v_cache, pos, scratch=None):
+    """Attention of one query token per sequence over cache positions [0, pos]: q [B, H, 1, hd] or
+    [B, H, hd] (f16 / bf16, contiguous), caches [B, KV, max_seq, hd], pos a one-element int64 device
+    tensor. Returns [B, H, hd]. `scratch` (float32, `attn_scratch_floats(B, H, max_seq, hd)` elements)
+    is allocated when not given; pass one to stay allocation-free inside a captured step."""
+    dev = _need_cuda(q, k_cache, v_cache, pos, scratch)
+    B, H, hd = q.shape[0], q.shape[1], q.shape[-1]
+    KV, S = k_cache.shape[1], k_cache.shape[2]
+    if scratch is None:
+        scratch = torch.empty(attn_scratch_floats(B, H, S, hd), dtype=torch.float32, device=q.device)
+    out = torch.empty(B, H, hd, dtype=q.dtype, device=q.device)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(), out.data_ptr(),
+                                      scratch.data_ptr(), scratch.numel(), _DT[q.dtype], B, H, KV, hd, S, _stream(dev))
+    _check(rc, "tfp8b_attn_decode")
     return out

@@ -41,6 +41,7 @@ class LlamaConfig:
 
 LLAMA3_8B = LlamaConfig()
 TINY = LlamaConfig(n_layers=2, d_model=256, n_heads=8, n_kv_heads=2, ffn=512, vocab=1000, max_seq=64)
+TINY_HD128 = LlamaConfig(n_layers=2, d_model=512, n_heads=4, n_kv_heads=2, ffn=512, vocab=1000, max_seq=64)   # head_dim 128
 
 
 class RMSNorm(nn.Module):
@@ -81,11 +82,14 @@ class Block(nn.Module):
         shape = (batch, self.kv_local, self.cfg.max_seq, self.cfg.head_dim)
         self.k_cache = torch.zeros(shape, device=device, dtype=dtype)
         self.v_cache = torch.zeros(shape, device=device, dtype=dtype)
+        # split-KV partial results of the decode attention; one buffer can serve all blocks
+        self.attn_scratch = None
 
     def forward(self, x, delta, pos, cos, sin, mask):
         """x [B, T, d] the residual stream and delta the previous block's MLP output not yet added
         to it (None for the first block); pos int64 [T] (device) = cache positions of these tokens;
-        mask additive [T, max_seq] or None (prefill from position 0 uses the causal flag).
+        mask additive [T, max_seq], None (prefill from position 0 uses the causal flag) or False (one
+        decode token on the GPU: the split-KV attention kernel reads the position itself).
         Returns (x, delta) in the same convention: the add is fused with the next RMSNorm."""
         B, T, _ = x.shape
         hd = self.cfg.head_dim
@@ -108,9 +112,14 @@ class Block(nn.Module):
             self.v_cache.index_copy_(2, pos, v)
         if mask is None:
             a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+            a = a.transpose(1, 2).reshape(B, T, self.h_local * hd)
+        elif mask is False:
+            # decode step: split-KV attention over the static cache, [B, H, hd] is already [B, 1, H * hd]
+            a = _ext.attn_decode(q, self.k_cache, self.v_cache, pos, self.attn_scratch).view(B, 1, self.h_local * hd)
         else:
             a = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask, enable_gqa=True)
-        o = self.o_proj(a.transpose(1, 2).reshape(B, T, self.h_local * hd)).to(x.dtype)
+            a = a.transpose(1, 2).reshape(B, T, self.h_local * hd)
+        o = self.o_proj(a).to(x.dtype)
         if fused:
             h = _ext.add_rmsnorm(x, o.contiguous(), self.post_attention_layernorm.weight, self.cfg.eps)
         else:
@@ -129,6 +138,8 @@ class Llama(nn.Module):
     def __init__(self, cfg: LlamaConfig = LLAMA3_8B, device="cpu", dtype=torch.float16, tp=1):
         super().__init__()
         self.cfg, self.tp = cfg, tp
+        # decode attention: torch SDPA (cuDNN) by default; True selects the library's split-KV kernel
+        self.attn_kernel = False
         self.embed = nn.Embedding(cfg.vocab, cfg.d_model, device=device, dtype=dtype)
         self.layers = nn.ModuleList([Block(cfg, tp, device, dtype) for _ in range(cfg.n_layers)])
         self.norm = RMSNorm(cfg.d_model, cfg.eps, device, dtype)
@@ -140,25 +151,35 @@ class Llama(nn.Module):
 
     def alloc_cache(self, batch):
         p = self.embed.weight
+        scratch = None
+        if p.is_cuda:
+            scratch = torch.empty(_ext.attn_scratch_floats(batch, self.cfg.n_heads // self.tp, self.cfg.max_seq, self.cfg.head_dim),
+                                  dtype=torch.float32, device=p.device)
         for l in self.layers:
             l.alloc_cache(batch, p.device, p.dtype)
             l.cos_table, l.sin_table = self.cos, self.sin
+            l.attn_scratch = scratch
 
     def forward(self, tokens, pos, prefill=False, last_only=False):
         """tokens int64 [B, T]; pos int64 [T] on the same device. Returns logits [B, T, vocab], or
         [B, 1, vocab] of the last position with last_only (all a prefill needs to pick a token)."""
         x = self.embed(tokens)
-        cos, sin = self.cos[pos], self.sin[pos]
+        fused = x.is_cuda and x.dtype in (torch.float16, torch.bfloat16)
+        cos, sin = (None, None) if fused else (self.cos[pos], self.sin[pos])     # the fused kernels index the tables
         mask = None
         if not prefill:
-            seq = torch.arange(self.cfg.max_seq, device=pos.device)
-            mask = torch.where(seq[None, :] <= pos[:, None], 0.0, float("-inf")).to(x.dtype)
+            hd, blk = self.cfg.head_dim, self.layers[0]
+            if self.attn_kernel and fused and tokens.shape[1] == 1 and hd == 128:
+                mask = False             # decode attention kernel: reads the position itself, no mask tensor
+            else:
+                seq = torch.arange(self.cfg.max_seq, device=pos.device)
+                mask = torch.where(seq[None, :] <= pos[:, None], 0.0, float("-inf")).to(x.dtype)
         delta = None
         for l in self.layers:
             x, delta = l(x, delta, pos, cos, sin, mask)
         if last_only:
             x, delta = x[:, -1:].contiguous(), delta[:, -1:].contiguous()
-        if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16):
+        if fused:
             h = _ext.add_rmsnorm(x, delta, self.norm.weight, self.cfg.eps)
         else:
             h = self.norm(x + delta)

@@ -195,6 +195,17 @@ TFP8B_API int tfp8b_gemm_scatter(const void* x16, const float* xs, const uint8_t
 TFP8B_API int tfp8b_add_rmsnorm(void* x, const void* delta, const void* weight, void* out, int dtype,
                   long long rows, int dim, float eps, tfp8b_stream_t stream);
 
+/* One-query attention over the static KV cache, grouped-query heads: for every sequence b and head h,
+ * out[b, h, :] = softmax(q[b, h, :] . K[b, h / (H/KV), 0:pos+1, :]^T / sqrt(hd)) V[...]. q and out are
+ * [B, H, hd]; the caches [B, KV, max_seq, hd]; pos is ONE int64 on the device (the cache position of
+ * the current token, already written by tfp8b_rope_kv_store). scratch: at least
+ * B * H * ceil(max_seq / 64) * (hd + 2) floats of device memory for the split-KV partial results
+ * (one record per head and 64-position chunk of the cache). f16 or bf16, hd = 128. (Reference: the torch attention of
+ * tfp8/examples/demo_llm.py:64-76.) */
+TFP8B_API int tfp8b_attn_decode(const void* q, const void* k_cache, const void* v_cache, const long long* pos,
+                  void* out, float* scratch, long long scratch_floats, int dtype, int B, int H, int KV, int hd,
+                  int max_seq, tfp8b_stream_t stream);
+
 /* out[r] = argmax over logits[r, 0:n] (row pitch in elements), int64; the lowest index among equal
  * values, NaN counts as largest -- the greedy sampling step of the reference's demo
  * (tfp8/examples/demo_llm.py:149). f16 or bf16. */

@@ -90,11 +90,34 @@ def test_argmax(dtype):
         assert int(out[1]) == n // 2 - 1 or n < 3
 
 
-def test_harness_decode_matches_prefill_on_gpu():
+@pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16))
+def test_attn_decode_matches_sdpa(dtype):
+    """Split-KV decode attention against torch SDPA in float32 on the same cache contents, for
+    several positions (one CTA chunk, many chunks, the last cache slot) and head groupings."""
+    from tfp8 import _ext
+    torch.manual_seed(4)
+    for (B, H, KV, S) in ((2, 8, 2, 300), (1, 32, 8, 2304), (3, 4, 4, 64)):
+        q = torch.randn(B, H, 1, 128, device="cuda").to(dtype)
+        k = torch.randn(B, KV, S, 128, device="cuda").to(dtype)
+        v = torch.randn(B, KV, S, 128, device="cuda").to(dtype)
+        for p in (0, 5, S // 2 + 3, S - 1):
+            pos = torch.tensor([p], device="cuda")
+            got = _ext.attn_decode(q, k, v, pos).float()
+            want = F.scaled_dot_product_attention(q.float(), k[:, :, :p + 1].float(), v[:, :, :p + 1].float(),
+                                                  enable_gqa=True)[:, :, 0]
+            tol = 2e-3 if dtype == torch.float16 else 1.6e-2
+            assert (got - want).abs().max() <= tol * max(1.0, float(want.abs().max())), (B, H, KV, S, p)
+
+
+@pytest.mark.parametrize("cfg_name", ("TINY", "TINY_HD128"))
+def test_harness_decode_matches_prefill_on_gpu(cfg_name):
     from tfp8 import FP8Config, _ext
-    from tfp8.examples.llama import TINY, DecodeRunner, build_fp8_llama
+    from tfp8.examples import llama
+    from tfp8.examples.llama import DecodeRunner, build_fp8_llama
+    TINY = getattr(llama, cfg_name)          # head_dim 32 (torch SDPA decode) and 128 (the decode attention kernel)
     torch.manual_seed(0)
     model = build_fp8_llama(TINY, torch.device("cuda"), torch.float16, fp8=FP8Config(min_features=64, nan_check=False))
+    model.attn_kernel = cfg_name == "TINY_HD128"
     toks = torch.randint(0, TINY.vocab, (2, 9), device="cuda")
     full = DecodeRunner(model, 2).prefill(toks).float()
     run = DecodeRunner(model, 2)
