@@ -735,7 +735,8 @@ extern "C" int tfp8b_gemm_scatter(const void* x16, const float* xs, const uint8_
         const long long esz = y_dtype == TFP8B_F32 ? 4 : 2;
         bool aligned = (ldy * esz) % 16 == 0 && (col0 * esz) % 16 == 0 && (static_cast<long long>(N) * esz) % 16 == 0;
         for (int d = 0; d < n_dst; ++d) aligned = aligned && (reinterpret_cast<uintptr_t>(y_dst[d]) & 15u) == 0;
-        static const int use_push = [] { const char* v = getenv("TFP8B_GEMM_PUSH"); return v && v[0] == '1'; }();
+        // TFP8B_GEMM_PUSH=0 in the environment falls back to element-wise peer stores from the epilogue
+        static const int use_push = [] { const char* v = getenv("TFP8B_GEMM_PUSH"); return !(v && v[0] == '0'); }();
         p.push = (use_push && n_dst > 1 && aligned) ? 1 : 0;
     }
     p.M = M; p.N = N; p.K = K; p.G = G; p.scale_kind = scale_kind; p.y_dt = y_dtype;
