@@ -359,15 +359,22 @@ def extra_measurements(args, device, peaks, world):
             x16 = torch.empty(M, K, dtype=torch.float16, device=device)
             xsc = torch.empty(M, dtype=torch.float32, device=device)
 
-            def step(with_prep=True):
+            ws = torch.empty(M * N, dtype=torch.float32, device=device) if M <= _ext.SPLITK_MAX_M else None
+
+            def step(with_prep=True, split=True):
                 if with_prep:
                     lib.tfp8b_prep(x.data_ptr(), 0 if xdt == torch.float16 else 1, x16.data_ptr(), xsc.data_ptr(), M, K, st())
-                rc = lib.tfp8b_gemm(x16.data_ptr(), xsc.data_ptr(), q.data_ptr(), e8.data_ptr(), 1, None, y.data_ptr(), 0,
-                                    M, N, K, G, 0, st())
+                if ws is not None and split:        # what FP8Linear calls for few rows: K may be split across SMs
+                    rc = lib.tfp8b_gemm_splitk(x16.data_ptr(), xsc.data_ptr(), q.data_ptr(), e8.data_ptr(), 1, None, y.data_ptr(), 0,
+                                               M, N, K, G, 0, ws.data_ptr(), ws.numel(), st())
+                else:
+                    rc = lib.tfp8b_gemm(x16.data_ptr(), xsc.data_ptr(), q.data_ptr(), e8.data_ptr(), 1, None, y.data_ptr(), 0,
+                                        M, N, K, G, 0, st())
                 assert rc == 0, lib.tfp8b_last_error_string()
             iters = 10 if M <= 1024 else 4
             sec = time_eager(step, iters, 3)
             sec_mm = time_eager(lambda: step(False), iters, 2)
+            sec_whole_k = time_eager(lambda: step(False, False), iters, 2) if ws is not None else None
             fl = 2.0 * M * N * K
             byt = N * K + N * (K // G) + M * K * 2 + M * N * 2
             bound_s = max(fl / (peaks["bf16_tflops"] * 1e12), byt / (peaks["hbm_gbs"] * 1e9))
@@ -379,8 +386,9 @@ def extra_measurements(args, device, peaks, world):
                                 # power cap: the seconds-long cuBLAS loop is the like-for-like peak there
                                 "frac_tensor_peak_sustained": (fl / sec_mm / 1e12 / peaks["bf16_tflops_sustained"]
                                                                if peaks.get("bf16_tflops_sustained") else None),
-                                "frac_of_bound": bound_s / sec_mm})
-            del x, y, x16
+                                "frac_of_bound": bound_s / sec_mm,
+                                "ms_gemm_without_split_k": sec_whole_k * 1e3 if sec_whole_k else None})
+            del x, y, x16, ws
     del q
     # --- encoder and fused quantizer on a 256 Mi-element fp16 tensor (512 MB in, 256 MB out)
     n = 1 << 28
@@ -546,10 +554,14 @@ def run_probe(args):
     xs = torch.empty(M, dtype=torch.float32, device=device)
     st = lambda: torch.cuda.current_stream().cuda_stream
     lib.tfp8b_prep(x.data_ptr(), 0, x16.data_ptr(), xs.data_ptr(), M, K, st())
+    ws = torch.empty(M * N, dtype=torch.float32, device=device) if M <= _ext.SPLITK_MAX_M else None   # as FP8Linear calls it
 
     def step():
         for q in qs:
-            if kind == "gemm":
+            if kind == "gemm" and ws is not None:
+                rc = lib.tfp8b_gemm_splitk(x16.data_ptr(), xs.data_ptr(), q.data_ptr(), sc.data_ptr(), skind, None, y.data_ptr(), 0,
+                                           M, N, K, G, 0, ws.data_ptr(), ws.numel(), st())
+            elif kind == "gemm":
                 rc = lib.tfp8b_gemm(x16.data_ptr(), xs.data_ptr(), q.data_ptr(), sc.data_ptr(), skind, None, y.data_ptr(), 0,
                                     M, N, K, G, 0, st())
             else:

@@ -70,6 +70,8 @@ struct GemmParams {
     int x_bytes;         // one activation tile: BN x 64 fp16
     int stage_bytes;
     int nmma;            // MMA-issuing threads; thread t takes k-blocks t, t + nmma, ... into its own accumulator
+    int ks, nkbu;        // split-K: every tile is cut into ks units of nkbu k-blocks; ntiles counts units
+    float* ws;           // ks > 1: FP32 [M, N] workspace the units add their partial tiles into
 };
 
 struct GemmHeader {
@@ -197,14 +199,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     uint8_t* raw_ring = stages + static_cast<size_t>(p.ns) * p.stage_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nkb = (p.K + GM_BK - 1) / GM_BK;
+    const int nkb = p.nkbu;                               // k-blocks of one unit of work (the whole K unless split)
     const int raw_slot_bytes = p.rb * GM_RAW_BYTES;
     const int ng = p.K / p.G;
     const int my_tiles = (p.ntiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-    // Tile i of this CTA is global tile blockIdx.x + i * gridDim.x; the activation-row tile is the
-    // fast index, so CTAs that run together share one weight stripe through L2.
-    auto tile_m0 = [&](int i) { return ((static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x)) % p.m_tiles) * p.BN; };
-    auto tile_n0 = [&](int i) { return ((static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x)) / p.m_tiles) * GM_BM; };
+    // Unit i of this CTA is global unit blockIdx.x + i * gridDim.x = (tile, K part), the part the
+    // fast index; within the tiles the activation-row tile is the fast index, so CTAs that run
+    // together share one weight stripe through L2.
+    auto unit_of = [&](int i) { return static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x); };
+    auto tile_m0 = [&](int i) { return ((unit_of(i) / p.ks) % p.m_tiles) * p.BN; };
+    auto tile_n0 = [&](int i) { return ((unit_of(i) / p.ks) / p.m_tiles) * GM_BM; };
+    auto unit_kb0 = [&](int i) { return (unit_of(i) % p.ks) * nkb; };              // first k-block of the unit
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.ns; ++s) {
@@ -244,15 +249,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             uint32_t phase = 1;               // ring position (no divisions): the first pass over the ring does not wait
             bool ok = true, first_pass = true;
             for (int i = 0; i < my_tiles && ok; ++i) {
-                const int n0 = tile_n0(i);
+                const int n0 = tile_n0(i), kb0 = unit_kb0(i);
                 for (int kb = 0; kb < nkb; kb += p.rb) {
                     if (!first_pass && !mbar_wait(smem_u32(&hd->raw_empty[slot]), phase, STATUS_GEMM_WAIT)) { ok = false; break; }
                     GM_TRACE(0, i * nkb + kb);
                     const uint32_t bar = smem_u32(&hd->raw_full[slot]);
                     const uint32_t dst = smem_u32(raw_ring + static_cast<size_t>(slot) * raw_slot_bytes);
                     mbar_expect_tx(bar, static_cast<uint32_t>(raw_slot_bytes));
-                    if (p.rb == 2) tma_load_3d(dst, &tm_w, 0, n0, kb >> 1, bar, pol_w);     // [row][128 bytes]
-                    else tma_load_2d(dst, &tm_w, kb * GM_BK, n0, bar, pol_w);               // [row][64 bytes]
+                    if (p.rb == 2) tma_load_3d(dst, &tm_w, 0, n0, (kb0 + kb) >> 1, bar, pol_w);     // [row][128 bytes]
+                    else tma_load_2d(dst, &tm_w, (kb0 + kb) * GM_BK, n0, bar, pol_w);               // [row][64 bytes]
                     if (++slot == p.sr) { slot = 0; phase ^= 1u; first_pass = false; }
                 }
             }
@@ -266,12 +271,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             uint32_t phase = 1;
             bool ok = true, first_pass = true;
             for (int i = 0; i < my_tiles && ok; ++i) {
-                const int m0 = tile_m0(i);
+                const int m0 = tile_m0(i), kb0 = unit_kb0(i);
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!first_pass && !mbar_wait(smem_u32(&hd->empty[slot]), phase, STATUS_GEMM_WAIT)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&hd->full[slot]);
                     mbar_expect_tx(bar, static_cast<uint32_t>(p.x_bytes));
-                    tma_load_2d(smem_u32(stages + static_cast<size_t>(slot) * p.stage_bytes + GM_A_BYTES), &tm_x, kb * GM_BK, m0, bar, pol_x);
+                    tma_load_2d(smem_u32(stages + static_cast<size_t>(slot) * p.stage_bytes + GM_A_BYTES), &tm_x, (kb0 + kb) * GM_BK, m0, bar, pol_x);
                     if (++slot == p.ns) { slot = 0; phase ^= 1u; first_pass = false; }
                 }
             }
@@ -412,7 +417,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             // this group's k-blocks inside the tile: first, first + NG, ... (nloc of them)
             const int first = done - i * nkb;
             const int nloc = first < nkb ? (nkb - first + GM_NG - 1) / GM_NG : 0;
-            const uint32_t half_off = (p.rb == 2 && (first & 1)) ? 64u : 0u;       // NG is even: the parity of kb is fixed
+            const int kabs = unit_kb0(i) + first;                                  // absolute k-block of the group's first one
+            const uint32_t half_off = (p.rb == 2 && (kabs & 1)) ? 64u : 0u;        // NG is even: the parity of kb is fixed
             // The fold factor scale / rowmax of this thread's rows for PF of the group's k-blocks,
             // loaded one batch ahead of their use (a global load inside the k-block loop would stall
             // every decode warp for an L2 round trip). UE8M0: the factor is 2^e with e the byte
@@ -423,7 +429,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 #pragma unroll
                     for (int h2 = 0; h2 < RPT; ++h2) dst[j][h2] = e8 ? 0u : 0x3F800000u;
                     if (ng > 1 && l0 + j < nloc) {
-                        const int u32 = (first + (l0 + j) * GM_NG) * 2 + (c >> 1);
+                        const int u32 = (kabs + (l0 + j) * GM_NG) * 2 + (c >> 1);
                         const int gi = min(g_shift >= 0 ? (u32 >> g_shift) : (u32 / g32), ng - 1);
 #pragma unroll
                         for (int h2 = 0; h2 < RPT; ++h2) {
@@ -607,7 +613,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = m0 + col + j;
-                        if (m < p.M) {
+                        if (m < p.M && p.ks > 1) {
+                            // split-K: this unit's share of the dot products, weight scale applied; the
+                            // activation scale and the bias follow once all parts are in
+                            atomicAdd(p.ws + static_cast<size_t>(m) * p.N + n, __uint_as_float(v[j]) * sm);
+                        } else if (m < p.M) {
                             const float val = fmaf(__uint_as_float(v[j]) * sm, p.xs[m], b);
                             const size_t at = static_cast<size_t>(m) * p.ldy + p.col0 + n;
                             store_dt(p.y[0], at, val, p.y_dt);
@@ -707,9 +717,26 @@ extern "C" int tfp8b_gemm(const void* x16, const float* xs, const uint8_t* codes
     return tfp8b_gemm_scatter(x16, xs, codes, scale, scale_kind, bias, dst, 1, N, 0, y_dtype, M, N, K, G, fmt, stream);
 }
 
+static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, const void* scale, int scale_kind,
+                     const float* bias, void* const* y_dst, int n_dst, long long ldy, long long col0, int y_dtype,
+                     int M, int N, int K, int G, int fmt, float* workspace, long long workspace_floats, tfp8b_stream_t stream);
+
 extern "C" int tfp8b_gemm_scatter(const void* x16, const float* xs, const uint8_t* codes, const void* scale, int scale_kind,
                                   const float* bias, void* const* y_dst, int n_dst, long long ldy, long long col0, int y_dtype,
                                   int M, int N, int K, int G, int fmt, tfp8b_stream_t stream) {
+    return gemm_impl(x16, xs, codes, scale, scale_kind, bias, y_dst, n_dst, ldy, col0, y_dtype, M, N, K, G, fmt, nullptr, 0, stream);
+}
+
+extern "C" int tfp8b_gemm_splitk(const void* x16, const float* xs, const uint8_t* codes, const void* scale, int scale_kind,
+                                 const float* bias, void* y, int y_dtype, int M, int N, int K, int G, int fmt, float* workspace,
+                                 long long workspace_floats, tfp8b_stream_t stream) {
+    void* dst[1] = {y};
+    return gemm_impl(x16, xs, codes, scale, scale_kind, bias, dst, 1, N, 0, y_dtype, M, N, K, G, fmt, workspace, workspace_floats, stream);
+}
+
+static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, const void* scale, int scale_kind,
+                     const float* bias, void* const* y_dst, int n_dst, long long ldy, long long col0, int y_dtype,
+                     int M, int N, int K, int G, int fmt, float* workspace, long long workspace_floats, tfp8b_stream_t stream) {
     TFP8B_REQUIRE(M >= 0 && N >= 0 && K > 0 && G > 0, TFP8B_ERR_INVALID, "tfp8b_gemm: bad size M=%d N=%d K=%d G=%d", M, N, K, G);
     TFP8B_REQUIRE(y_dtype >= 0 && y_dtype <= 2, TFP8B_ERR_INVALID, "tfp8b_gemm: bad dtype");
     TFP8B_REQUIRE(fmt == TFP8B_E4M3FN || fmt == TFP8B_E5M2, TFP8B_ERR_INVALID, "tfp8b_gemm: bad fmt %d", fmt);
@@ -747,18 +774,45 @@ extern "C" int tfp8b_gemm_scatter(const void* x16, const float* xs, const uint8_
     // Two issuing threads, each with a double-buffered accumulator, while tensor memory has the
     // room: 2 x 2 x BN <= 512 columns. (Two threads accumulating into ONE accumulator is not an
     // option: that variant ended every BN = 256 launch with a launch failure.)
-    p.nmma = (bn <= 128 && nkb >= 4) ? 2 : 1;
-    p.tmem_cols = 2 * p.nmma * bn < 32 ? 32 : 2 * p.nmma * bn;
-    if (p.nmma != 1) p.push = 0;                             // warp 3 issues MMAs there
     p.m_tiles = (M + bn - 1) / bn;
     p.ntiles = p.m_tiles * ((N + GM_BM - 1) / GM_BM);
+    p.rb = K % 128 == 0 ? 2 : 1;
+    // Split-K (one activation tile, a workspace given): a CTA's k-loop is serial, about 0.3 us per
+    // k-block whatever the tile width, so with few tiles of a long K the busiest CTA sets the time
+    // (64 tiles of K = 8192 on 148 SMs: 84 SMs idle). Every tile is cut into ks units along K; the
+    // units add their partial tiles into the FP32 workspace (atomics, L2 resident) and a final pass
+    // applies the activation scale and the bias. The cost model counts k-blocks on the busiest CTA
+    // plus a fixed turn-over per unit; it splits only where that clearly pays (fewer tiles than
+    // half the SMs and a long K).
+    p.ks = 1; p.nkbu = nkb; p.ws = nullptr;
+    int sms = 148;
+    {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    static const int use_splitk = [] { const char* v = getenv("TFP8B_GEMM_SPLITK"); return !(v && v[0] == '0'); }();
+    if (use_splitk && workspace && n_dst == 1 && p.m_tiles == 1 && workspace_floats >= static_cast<long long>(M) * N) {
+        // measured on B200: a unit costs about 32 k-blocks of turn-over (scale scan, pipeline fill
+        // and drain, atomics), and the extra memset + final pass as much again
+        constexpr int TURNOVER = 32, EXTRA_PASSES = 32;
+        auto cost = [&](int ks) { return ((p.ntiles * ks + sms - 1) / sms) * (nkb / ks + TURNOVER) + (ks > 1 ? EXTRA_PASSES : 0); };
+        int best = 1;
+        for (int ks = 2; ks <= 16; ks <<= 1)
+            if (nkb % ks == 0 && nkb / ks >= 8 && (p.rb == 1 || (nkb / ks) % 2 == 0) && cost(ks) < cost(best) &&
+                cost(ks) * 6 < cost(1) * 5)                     // only for a clear gain: the split costs determinism
+                best = ks;
+        if (best > 1) { p.ks = best; p.nkbu = nkb / best; p.ws = workspace; p.ntiles *= best; }
+    }
+    p.nmma = (bn <= 128 && p.nkbu >= 4) ? 2 : 1;
+    p.tmem_cols = 2 * p.nmma * bn < 32 ? 32 : 2 * p.nmma * bn;
+    if (p.nmma != 1) p.push = 0;                             // warp 3 issues MMAs there
     // Shared memory: four stages (the groups' tiles in decode, the one in the MMA, one spare), the
     // rest raw codes -- the ring whose depth hides HBM latency. (At BN = 256 that rest is two slots,
     // four k-blocks: there the CTAs of the other activation tiles pull the same stripe through L2.)
     // Every ring's length is a multiple of the stride its users walk it with (decode groups,
     // issuing threads), so a slot is always revisited by the same user, in order: a parity wait
     // can then never be answered by a phase two completions away.
-    p.rb = K % 128 == 0 ? 2 : 1;
     p.x_bytes = bn * GM_BK * 2;
     p.stage_bytes = GM_A_BYTES + p.x_bytes;
     const int budget = GM_SMEM_MAX - 1024 - GM_HEADER;
@@ -789,8 +843,14 @@ extern "C" int tfp8b_gemm_scatter(const void* x16, const float* xs, const uint8_
                      GM_BK, static_cast<uint32_t>(bn), CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TFP8B_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (fmt == TFP8B_E4M3FN) return launch_gemm<TFP8B_E4M3FN>(tw, tx, p, smem, st);
-    return launch_gemm<TFP8B_E5M2>(tw, tx, p, smem, st);
+    if (p.ks > 1) {
+        cudaError_t e = cudaMemsetAsync(workspace, 0, static_cast<size_t>(M) * N * sizeof(float), st);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(split-K workspace)");
+    }
+    rc = fmt == TFP8B_E4M3FN ? launch_gemm<TFP8B_E4M3FN>(tw, tx, p, smem, st) : launch_gemm<TFP8B_E5M2>(tw, tx, p, smem, st);
+    if (rc != TFP8B_OK || p.ks == 1) return rc;
+    // y = workspace * xs[m] + bias[n], rounded once to the output type
+    return tfp8b_epilogue(workspace, xs, bias, y_dst[0], y_dtype, M, N, static_cast<int>(ldy), stream);
 }
 
 extern "C" int tfp8b_linear_static(const void* x, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind,

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "tfp8b_gemv": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_gemv_ex": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.c_uint, _P], _I),
     "tfp8b_gemm": ([_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
+    "tfp8b_gemm_splitk": ([_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P], _I),
     "tfp8b_gemm_scatter": ([_P, _P, _P, _P, _I, _P, _P, _I, ctypes.c_longlong, ctypes.c_longlong, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_linear_static": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_epilogue": ([_P, _P, _P, _P, _I, _I, _I, _I, _P], _I),
@@ -266,7 +267,19 @@ def _gemv(x, qweight, wscale, bias, y, M, N, K, group_size, fmt, dev):
     _check(rc, "tfp8b_gemv")
 
 
+SPLITK_MAX_M = 64          # above this the tiles are wide enough that whole-K tiles keep the SMs busy
+
+
 def _gemm(x16, xs, qweight, wscale, bias, y, M, N, K, group_size, fmt, dev):
+    if M <= SPLITK_MAX_M and N * K >= (1 << 24):
+        # few, long tiles: let the library split K across SMs (it decides; the workspace is only
+        # touched if it does). Partial sums meet in FP32 atomics, so the last bit may vary.
+        ws = torch.empty(M * N, dtype=torch.float32, device=y.device)
+        rc = load().tfp8b_gemm_splitk(x16.data_ptr(), xs.data_ptr(), qweight.data_ptr(), wscale.data_ptr(), _scale_kind(wscale),
+                                      bias.data_ptr() if bias is not None else 0, y.data_ptr(), _DT[y.dtype], M, N, K,
+                                      group_size, FMT_ID[fmt], ws.data_ptr(), ws.numel(), _stream(dev))
+        _check(rc, "tfp8b_gemm_splitk")
+        return
     rc = load().tfp8b_gemm(x16.data_ptr(), xs.data_ptr(), qweight.data_ptr(), wscale.data_ptr(), _scale_kind(wscale),
                            bias.data_ptr() if bias is not None else 0, y.data_ptr(), _DT[y.dtype], M, N, K,
                            group_size, FMT_ID[fmt], _stream(dev))

@@ -187,6 +187,17 @@ TFP8B_API int tfp8b_gemm_scatter(const void* x16, const float* xs, const uint8_t
                   int scale_kind, const float* bias, void* const* y_dst, int n_dst, long long ldy,
                   long long col0, int y_dtype, int M, int N, int K, int G, int fmt, tfp8b_stream_t stream);
 
+/* tfp8b_gemm with an FP32 workspace of at least M * N floats. With one activation tile (M <= 256)
+ * and few 128-row weight tiles of a long K, the call cuts every tile into units along K that
+ * run on different SMs, adds their partial results into the workspace (atomic adds: the last
+ * bits of a result can differ from run to run) and applies activation scale and bias in a final
+ * pass; whether and how far it splits follows a cost model, and TFP8B_GEMM_SPLITK=0 in the
+ * environment turns it off. Without a split the workspace is not touched and the result is
+ * tfp8b_gemm's, bit for bit. No counterpart in the reference. */
+TFP8B_API int tfp8b_gemm_splitk(const void* x16, const float* xs, const uint8_t* codes, const void* scale,
+                  int scale_kind, const float* bias, void* y, int y_dtype, int M, int N, int K, int G,
+                  int fmt, float* workspace, long long workspace_floats, tfp8b_stream_t stream);
+
 /* x[r, :] += delta[r, :] (delta may be NULL), then out[r, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps)
  * * weight: the residual update and the RMSNorm that follows it in a decoder block, one launch
  * (reference: RMSNorm and the residual adds of tfp8/examples/demo_llm.py:30-39, 98-101; same

@@ -123,6 +123,30 @@ def test_gemm_scatter_window_and_destinations():
         _ext.gemm_scatter(x16, xs, f.qweight, f.weight_scale, f.bias_f32, [bufs[0].data_ptr()], N, 8, dt, f.group_size, f.fmt)
 
 
+def test_split_k_matches_whole_k():
+    """Few rows against few, long weight tiles: the library splits K across SMs (partial tiles meet
+    in FP32 atomics). Same gates as every GEMM case, and within float32 rounding of the whole-K
+    result; with the environment switch semantics checked through the C entry point: no
+    workspace, no split, bit-identical to tfp8b_gemm."""
+    from tfp8 import _ext
+    for (M, N, K, G) in ((16, 2048, 8192, 128), (64, 4096, 4096, None), (40, 1024, 16384, 32)):
+        f = _check(M, N, K, G, torch.float16)                          # FP8Linear routes through the split-K entry
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        x16, xs = _ext.prepare_activations(x)
+        y_split = torch.empty(M, N, dtype=torch.float32, device="cuda")
+        y_whole = torch.empty(M, N, dtype=torch.float32, device="cuda")
+        ws = torch.empty(M * N, dtype=torch.float32, device="cuda")
+        lib, st = _ext.load(), torch.cuda.current_stream().cuda_stream
+        args = (x16.data_ptr(), xs.data_ptr(), f.qweight.data_ptr(), f.weight_scale.data_ptr(), 0, f.bias_f32.data_ptr())
+        tail = (2, M, N, K, f.group_size, 0)
+        assert lib.tfp8b_gemm_splitk(*args, y_split.data_ptr(), *tail, ws.data_ptr(), ws.numel(), st) == 0
+        assert lib.tfp8b_gemm(*args, y_whole.data_ptr(), *tail, st) == 0
+        assert torch.allclose(y_split, y_whole, rtol=2e-5, atol=2e-5 * float(y_whole.abs().max()))
+        y_none = torch.empty_like(y_whole)
+        assert lib.tfp8b_gemm_splitk(*args, y_none.data_ptr(), *tail, None, 0, st) == 0
+        assert torch.equal(y_none, y_whole)
+
+
 def test_folded_group_scales():
     """Random codes, scales spanning 2^-20: power-of-two scales must stay at FP32-accumulation
     error, arbitrary scales within one fp16 rounding of the folded weight."""
