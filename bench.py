@@ -422,8 +422,8 @@ def llama_decode_measurements(device, peaks, world, batches=(1, 4, 8), prompt=20
     code_bytes = sum(m.qweight.numel() for m in model.modules() if isinstance(m, FP8Linear))
     stream_bytes = code_bytes + model.lm_head.weight.numel() * 2 // 1          # per rank, per decoded token
     rows = []
-    warm = DecodeRunner(model, 1)                                   # one-time costs (library handles, kernel opt-ins)
-    warm.prefill(torch.randint(0, LLAMA3_8B.vocab, (1, 128), device=device))
+    warm = DecodeRunner(model, 1)        # one-time costs at the real shapes (kernel opt-ins, cuDNN attention plans)
+    warm.prefill(torch.randint(0, LLAMA3_8B.vocab, (1, prompt), device=device))
     del warm
     for B in batches:
         g = torch.Generator(device=device).manual_seed(100 + B)
