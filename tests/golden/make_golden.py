@@ -19,7 +19,7 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.path.abspath(os.path.join(HERE, "..", "..", "..", "reference"))   # sibling checkout
 sys.path.insert(0, REF)
 
 import tfp8 as ref  # noqa: E402  (the reference package)
