@@ -54,6 +54,7 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const 
 
 int gemv_status(unsigned int* out, cudaStream_t st);
 int gemm_status(unsigned int* out, cudaStream_t st);
+int glue_status(unsigned int* out, cudaStream_t st);
 
 }  // namespace tfp8b
 
@@ -68,11 +69,12 @@ extern "C" int tfp8b_device_status(unsigned int* out_status, tfp8b_stream_t stre
     unsigned int v = 0;
     int rc = gemv_status(&v, st);
     if (rc == TFP8B_OK) rc = gemm_status(&v, st);
+    if (rc == TFP8B_OK) rc = glue_status(&v, st);
     if (rc != TFP8B_OK) return rc;
     if (out_status) *out_status = v;
     if (v) {
-        set_error("a kernel gave up on a bounded wait (status 0x%x: %s%s)", v, (v & STATUS_GEMV_WAIT) ? "gemv " : "",
-                  (v & STATUS_GEMM_WAIT) ? "gemm" : "");
+        set_error("a kernel gave up on a bounded wait (status 0x%x: %s%s%s)", v, (v & STATUS_GEMV_WAIT) ? "gemv " : "",
+                  (v & STATUS_GEMM_WAIT) ? "gemm " : "", (v & STATUS_GLUE_WAIT) ? "all-reduce" : "");
         return TFP8B_ERR_DEVICE;
     }
     return TFP8B_OK;

@@ -33,7 +33,7 @@ int cuda_fail(cudaError_t e, const char* what);
 // device code): kernels OR a bit in when a bounded wait runs out; each .cu file that has such
 // waits exports a reader that tfp8b_device_status() combines.
 static __device__ unsigned int g_status;
-constexpr unsigned STATUS_GEMV_WAIT = 1u, STATUS_GEMM_WAIT = 2u;
+constexpr unsigned STATUS_GEMV_WAIT = 1u, STATUS_GEMM_WAIT = 2u, STATUS_GLUE_WAIT = 4u;
 int read_and_clear_status(unsigned int* word_on_device, unsigned int* out, cudaStream_t st);
 
 // Host: fills a tiled tensor map (cuTensorMapEncodeTiled, fetched from the driver at first use).

@@ -176,6 +176,132 @@ __global__ void __launch_bounds__(ADD_NORM_THREADS) add_rmsnorm_kernel(T* __rest
         emit(v, *reinterpret_cast<const uint4*>(x + row + v * 8));       // re-read what this thread stored
 }
 
+// ------------------------------------------------------------------ all-reduce + residual + RMSNorm
+// Tensor-parallel decode: after a row-parallel projection every rank holds an FP32 partial
+// [rows, dim] of the same output. A NCCL all-reduce of those 8-32 KB costs ~19 us inside a decode
+// step, 64 times per token; this kernel does the exchange itself, one CTA per row:
+//   1. push this rank's partial row into every peer's receive slot (peer-mapped memory, plain
+//      16-byte stores over NVLink), fence, then write the call's sequence number into the peer's
+//      flag for (this rank, row);
+//   2. wait (bounded) until every peer's flag for this row shows the same sequence number;
+//   3. add the partials in rank order (every rank computes bit-identical sums), round to the
+//      activation type, add to the residual, RMSNorm.
+// Receive slots and flags are double-buffered by the parity of the sequence number: a rank can
+// run at most one call ahead of a peer (it needs the peer's flag of call k to finish call k), so
+// the slot it overwrites in call k + 2 has been read. The sequence number lives in device memory
+// and is advanced by the last CTA of each call, which is what makes the kernel replayable from a
+// CUDA graph. Every rank must issue the same calls in the same order.
+struct ArParams {
+    float* recv[8];            // recv[r]: rank r's receive area [2][world][max_rows][dim] (recv[rank] is local)
+    unsigned int* flag[8];     // flag[r]: rank r's flags [2][world][max_rows]
+    unsigned int* state;       // local: {sequence number of the last finished call, CTAs done in the running call}
+    int rank, world, max_rows;
+};
+constexpr int AR_THREADS = 256;
+template <typename T>
+__global__ void __launch_bounds__(AR_THREADS) allreduce_add_rmsnorm_kernel(T* __restrict__ x, const float* __restrict__ part,
+                                                                           const T* __restrict__ w, T* __restrict__ out,
+                                                                           int dim, float eps, const ArParams ar) {
+    using P = typename pair_of<T>::type;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x, nvec = dim / 4;
+    const unsigned int seq = *reinterpret_cast<volatile unsigned int*>(ar.state) + 1u;
+    const size_t slot_elems = static_cast<size_t>(ar.max_rows) * dim;
+    const size_t buf_off = static_cast<size_t>(seq & 1u) * ar.world * slot_elems;
+    const size_t flag_off = static_cast<size_t>(seq & 1u) * ar.world * ar.max_rows;
+    const float* mine = part + static_cast<size_t>(row) * dim;
+    // 1. push
+    for (int v = threadIdx.x; v < nvec; v += AR_THREADS) {
+        const float4 a = reinterpret_cast<const float4*>(mine)[v];
+        for (int r = 0; r < ar.world; ++r)
+            if (r != ar.rank)
+                reinterpret_cast<float4*>(ar.recv[r] + buf_off + ar.rank * slot_elems + static_cast<size_t>(row) * dim)[v] = a;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (static_cast<int>(threadIdx.x) < ar.world && static_cast<int>(threadIdx.x) != ar.rank) {
+        unsigned int* f = ar.flag[threadIdx.x] + flag_off + ar.rank * ar.max_rows + row;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(seq) : "memory");
+        // 2. wait for the same peer's row
+        const unsigned int* g = ar.flag[ar.rank] + flag_off + threadIdx.x * ar.max_rows + row;
+        const long long t0 = clock64();
+        unsigned int got;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(g) : "memory");
+            if (got == seq) break;
+            if (clock64() - t0 > (1ll << 32)) { atomicOr(&g_status, STATUS_GLUE_WAIT); break; }   // about two seconds
+            __nanosleep(100);
+        }
+    }
+    __syncthreads();
+    // 3. sum in rank order, residual, norm (rows of up to 4 * AR_THREADS * AR_KEEP floats stay in registers)
+    constexpr int AR_KEEP = 4;
+    float4 keep[AR_KEEP];
+    float ss = 0.f;
+    const size_t xrow = static_cast<size_t>(row) * dim;
+    const float* local = ar.recv[ar.rank] + buf_off + static_cast<size_t>(row) * dim;
+#pragma unroll
+    for (int it = 0; it < AR_KEEP; ++it) {
+        const int v = threadIdx.x + it * AR_THREADS;
+        if (v < nvec) {
+            float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < ar.world; ++r) {
+                const float4 a = r == ar.rank ? reinterpret_cast<const float4*>(mine)[v]
+                                              : __ldcg(reinterpret_cast<const float4*>(local + r * slot_elems) + v);
+                t.x += a.x; t.y += a.y; t.z += a.z; t.w += a.w;
+            }
+            const uint2 xr = *reinterpret_cast<const uint2*>(x + xrow + v * 4);
+            const P* xp = reinterpret_cast<const P*>(&xr);
+            // the reduced projection output is rounded to the activation type, then added (as the
+            // unfused sequence all-reduce -> cast -> add does)
+            const float2 d01 = unpack2(pack2(t.x, t.y, P())), d23 = unpack2(pack2(t.z, t.w, P()));
+            const float2 x01 = unpack2(xp[0]), x23 = unpack2(xp[1]);
+            uint2 xo;
+            P* op = reinterpret_cast<P*>(&xo);
+            op[0] = pack2(x01.x + d01.x, x01.y + d01.y, P());
+            op[1] = pack2(x23.x + d23.x, x23.y + d23.y, P());
+            *reinterpret_cast<uint2*>(x + xrow + v * 4) = xo;
+            const float2 n01 = unpack2(op[0]), n23 = unpack2(op[1]);
+            keep[it] = make_float4(n01.x, n01.y, n23.x, n23.y);
+            ss += n01.x * n01.x + n01.y * n01.y + n23.x * n23.x + n23.y * n23.y;
+        }
+    }
+    __shared__ float s_part[AR_THREADS / 32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < AR_THREADS / 32; ++i) ss += s_part[i];
+    const float rstd = rsqrtf(ss / static_cast<float>(dim) + eps);
+#pragma unroll
+    for (int it = 0; it < AR_KEEP; ++it) {
+        const int v = threadIdx.x + it * AR_THREADS;
+        if (v < nvec) {
+            const uint2 wr = *reinterpret_cast<const uint2*>(w + v * 4);
+            const P* wp = reinterpret_cast<const P*>(&wr);
+            const float2 w01 = unpack2(wp[0]), w23 = unpack2(wp[1]);
+            uint2 o;
+            P* op = reinterpret_cast<P*>(&o);
+            op[0] = pack2(keep[it].x * rstd * w01.x, keep[it].y * rstd * w01.y, P());
+            op[1] = pack2(keep[it].z * rstd * w23.x, keep[it].w * rstd * w23.y, P());
+            *reinterpret_cast<uint2*>(out + xrow + v * 4) = o;
+        }
+    }
+    // the last CTA of the call advances the sequence number
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(ar.state + 1, 1u) == gridDim.x - 1) {
+            ar.state[1] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned int*>(ar.state) = seq;
+        }
+    }
+}
+
 // out[r] = index of the largest logits[r, :]; the lowest index among equals; a NaN counts as the
 // largest value (the first NaN wins), as torch.argmax does. One CTA per row.
 constexpr int ARGMAX_THREADS = 1024;
@@ -436,6 +562,13 @@ static int launch_pdl(const char* what, void (*kernel)(KArgs...), int grid, int 
     return TFP8B_OK;
 }
 
+int glue_status(unsigned int* out, cudaStream_t st) {
+    unsigned int* word = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&word), g_status);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(glue status)");
+    return read_and_clear_status(word, out, st);
+}
+
 static int grid_of(long long work) {
     long long blocks = (work + 255) / 256;
     return static_cast<int>(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
@@ -531,6 +664,33 @@ extern "C" int tfp8b_attn_decode(const void* q, const void* k_cache, const void*
     if (rc != TFP8B_OK) return rc;
     return launch_pdl("tfp8b_attn_decode", attn_merge_kernel<__nv_bfloat16>, B * H, ATT_HD, st, static_cast<const float*>(scratch),
                       static_cast<__nv_bfloat16*>(out), nsplit);
+}
+
+extern "C" int tfp8b_allreduce_add_rmsnorm(void* x, const float* partial, const void* weight, void* out, int dtype, int rows,
+                                           int dim, float eps, float* const* recv, unsigned int* const* flags,
+                                           unsigned int* state, int rank, int world, int max_rows, tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(dtype == TFP8B_F16 || dtype == TFP8B_BF16, TFP8B_ERR_UNSUPPORTED, "tfp8b_allreduce_add_rmsnorm: f16 / bf16 only");
+    TFP8B_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world, TFP8B_ERR_INVALID,
+                  "tfp8b_allreduce_add_rmsnorm: rank %d of %d (1..8 ranks)", rank, world);
+    TFP8B_REQUIRE(rows >= 0 && rows <= max_rows && dim > 0 && dim % 4 == 0 && dim <= 4 * AR_THREADS * 4, TFP8B_ERR_INVALID,
+                  "tfp8b_allreduce_add_rmsnorm: rows=%d (receive area holds %d), dim=%d (a multiple of 4, at most %d)", rows,
+                  max_rows, dim, 4 * AR_THREADS * 4);
+    if (rows == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(x && partial && weight && out && recv && flags && state, TFP8B_ERR_INVALID, "tfp8b_allreduce_add_rmsnorm: null pointer");
+    ArParams ar;
+    for (int r = 0; r < 8; ++r) {
+        ar.recv[r] = r < world ? recv[r] : nullptr;
+        ar.flag[r] = r < world ? flags[r] : nullptr;
+        if (r < world) TFP8B_REQUIRE(ar.recv[r] && ar.flag[r], TFP8B_ERR_INVALID, "tfp8b_allreduce_add_rmsnorm: null peer pointer %d", r);
+    }
+    ar.state = state; ar.rank = rank; ar.world = world; ar.max_rows = max_rows;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == TFP8B_F16)
+        return launch_pdl("tfp8b_allreduce_add_rmsnorm", allreduce_add_rmsnorm_kernel<__half>, rows, AR_THREADS, st,
+                          static_cast<__half*>(x), partial, static_cast<const __half*>(weight), static_cast<__half*>(out), dim, eps, ar);
+    return launch_pdl("tfp8b_allreduce_add_rmsnorm", allreduce_add_rmsnorm_kernel<__nv_bfloat16>, rows, AR_THREADS, st,
+                      static_cast<__nv_bfloat16*>(x), partial, static_cast<const __nv_bfloat16*>(weight),
+                      static_cast<__nv_bfloat16*>(out), dim, eps, ar);
 }
 
 extern "C" int tfp8b_argmax(const void* logits, int dtype, long long* out, long long rows, long long n, long long row_pitch,

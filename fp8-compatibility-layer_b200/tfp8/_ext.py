@@ -47,6 +47,7 @@ _SIGNATURES = {
     "tfp8b_rope_kv_store": ([_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_silu_mul": ([_P, _P, _I, ctypes.c_longlong, _I, _P], _I),
     "tfp8b_add_rmsnorm": ([_P, _P, _P, _P, _I, ctypes.c_longlong, _I, ctypes.c_float, _P], _I),
+    "tfp8b_allreduce_add_rmsnorm": ([_P, _P, _P, _P, _I, _I, _I, ctypes.c_float, _P, _P, _P, _I, _I, _I, _P], _I),
     "tfp8b_attn_decode": ([_P, _P, _P, _P, _P, _P, ctypes.c_longlong, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_argmax": ([_P, _I, _P, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _P], _I),
 }
@@ -428,4 +429,24 @@ def attn_decode(q, k_cache, v_cache, pos, scratch=None):
         rc = load().tfp8b_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(), out.data_ptr(),
                                       scratch.data_ptr(), scratch.numel(), _DT[q.dtype], B, H, KV, hd, S, _stream(dev))
     _check(rc, "tfp8b_attn_decode")
+    return out
+
+
+def allreduce_add_rmsnorm(x, partial, weight, eps, recv_ptrs, flag_ptrs, state, rank, max_rows):
+    """x += (sum over ranks of `partial`).to(x.dtype) in place, returns RMSNorm(x) * weight: the
+    all-reduce of a row-parallel projection fused with the residual update and the norm, for at
+    most `max_rows` rows. partial: this rank's float32 [..., dim]; recv_ptrs / flag_ptrs: device
+    addresses of every rank's receive area and flag array (see include/tfp8b.h); state: two int32
+    of local device memory. A collective: every rank calls it, in the same order."""
+    dev = _need_cuda(x, partial, weight, state)
+    dim = x.shape[-1]
+    rows = x.numel() // dim
+    world = len(recv_ptrs)
+    out = torch.empty_like(x)
+    rp = (ctypes.c_void_p * world)(*[int(p) for p in recv_ptrs])
+    fp = (ctypes.c_void_p * world)(*[int(p) for p in flag_ptrs])
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_allreduce_add_rmsnorm(x.data_ptr(), partial.data_ptr(), weight.data_ptr(), out.data_ptr(), _DT[x.dtype],
+                                                rows, dim, float(eps), rp, fp, state.data_ptr(), rank, world, max_rows, _stream(dev))
+    _check(rc, "tfp8b_allreduce_add_rmsnorm")
     return out

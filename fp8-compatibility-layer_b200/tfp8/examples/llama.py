@@ -60,6 +60,13 @@ def _rope(x, cos, sin):
     return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
 
 
+class _Partial:
+    """A row-parallel projection's output still to be summed over the ranks (float32, this rank's part)."""
+
+    def __init__(self, t):
+        self.t = t
+
+
 class Block(nn.Module):
     def __init__(self, cfg: LlamaConfig, tp: int, device, dtype):
         super().__init__()
@@ -77,6 +84,7 @@ class Block(nn.Module):
         self.post_attention_layernorm = RMSNorm(d, cfg.eps, device, dtype)
         self.k_cache = self.v_cache = None
         self.cos_table = self.sin_table = None      # the model's [max_seq, hd/2] tables, shared by all blocks
+        self.comm = None                            # FusedAllReduceNorm of a tensor-parallel decode, set by the model
 
     def alloc_cache(self, batch, device, dtype):
         shape = (batch, self.kv_local, self.cfg.max_seq, self.cfg.head_dim)
@@ -94,7 +102,11 @@ class Block(nn.Module):
         B, T, _ = x.shape
         hd = self.cfg.head_dim
         fused = x.is_cuda and x.dtype in (torch.float16, torch.bfloat16)
-        if fused:      # one kernel: x += delta (in place), h = RMSNorm(x)
+        # tensor-parallel decode: the all-reduce after o_proj / down_proj rides in the add + norm kernel
+        comm = self.comm if (fused and self.comm is not None and B * T <= self.comm.max_rows) else None
+        if isinstance(delta, _Partial):
+            h = self.comm.add_rmsnorm(x, delta.t, self.input_layernorm.weight, self.cfg.eps)
+        elif fused:      # one kernel: x += delta (in place), h = RMSNorm(x)
             h = _ext.add_rmsnorm(x, delta, self.input_layernorm.weight, self.cfg.eps)
         else:
             x = x if delta is None else x + delta
@@ -119,18 +131,23 @@ class Block(nn.Module):
         else:
             a = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask, enable_gqa=True)
             a = a.transpose(1, 2).reshape(B, T, self.h_local * hd)
-        o = self.o_proj(a).to(x.dtype)
-        if fused:
-            h = _ext.add_rmsnorm(x, o.contiguous(), self.post_attention_layernorm.weight, self.cfg.eps)
+        if comm is not None:
+            h = comm.add_rmsnorm(x, self.o_proj.partial(a), self.post_attention_layernorm.weight, self.cfg.eps)
         else:
-            x = x + o
-            h = self.post_attention_layernorm(x)
+            o = self.o_proj(a).to(x.dtype)
+            if fused:
+                h = _ext.add_rmsnorm(x, o.contiguous(), self.post_attention_layernorm.weight, self.cfg.eps)
+            else:
+                x = x + o
+                h = self.post_attention_layernorm(x)
         gu = self.gate_up_proj(h)
         if fused and gu.dtype == x.dtype:
             act = _ext.silu_mul(gu.contiguous())
         else:
             f = gu.shape[-1] // 2
             act = F.silu(gu[..., :f]) * gu[..., f:]
+        if comm is not None:
+            return x, _Partial(self.down_proj.partial(act))
         return x, self.down_proj(act).to(x.dtype)
 
 
@@ -160,6 +177,12 @@ class Llama(nn.Module):
             l.cos_table, l.sin_table = self.cos, self.sin
             l.attn_scratch = scratch
 
+    def set_comm(self, comm):
+        """Fuse the tensor-parallel all-reduces of the decode step into the add + norm kernels
+        (comm: tfp8.parallel.FusedAllReduceNorm, or None for NCCL all-reduces)."""
+        for l in self.layers:
+            l.comm = comm
+
     def forward(self, tokens, pos, prefill=False, last_only=False):
         """tokens int64 [B, T]; pos int64 [T] on the same device. Returns logits [B, T, vocab], or
         [B, 1, vocab] of the last position with last_only (all a prefill needs to pick a token)."""
@@ -177,6 +200,9 @@ class Llama(nn.Module):
         delta = None
         for l in self.layers:
             x, delta = l(x, delta, pos, cos, sin, mask)
+        if isinstance(delta, _Partial):
+            h = self.layers[0].comm.add_rmsnorm(x, delta.t, self.norm.weight, self.cfg.eps)
+            return self.lm_head(h)
         if last_only:
             x, delta = x[:, -1:].contiguous(), delta[:, -1:].contiguous()
         if fused:
@@ -238,10 +264,14 @@ class DecodeRunner:
     """Prefill, then greedy decode with the whole step (all layers, lm_head, argmax, position bump)
     captured in one CUDA graph."""
 
-    def __init__(self, model: Llama, batch: int):
+    def __init__(self, model: Llama, batch: int, fused_allreduce=True):
         self.model, self.batch = model, batch
         model.alloc_cache(batch)
         dev = model.embed.weight.device
+        model.set_comm(None)
+        if fused_allreduce and model.tp > 1 and dev.type == "cuda" and model.embed.weight.dtype in (torch.float16, torch.bfloat16):
+            from ..parallel import FusedAllReduceNorm
+            model.set_comm(FusedAllReduceNorm(model.cfg.d_model, max_rows=max(8, batch), device=dev))
         self.tok = torch.zeros(batch, 1, dtype=torch.int64, device=dev)
         self.pos = torch.zeros(1, dtype=torch.int64, device=dev)
         self.graph = None

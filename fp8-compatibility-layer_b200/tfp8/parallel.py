@@ -150,6 +150,15 @@ class RowParallelFP8Linear(nn.Module):
         layer.shard = (rank * per, (rank + 1) * per)
         return layer
 
+    def partial(self, x):
+        """This rank's float32 partial product, not reduced (for a caller that fuses the reduction
+        with what follows, see FusedAllReduceNorm); the layer must have no bias."""
+        if self.bias_f32 is not None:
+            raise ValueError("partial() leaves the bias out: use forward() for a layer with bias")
+        if not self.input_is_parallel:
+            x = x[..., self.shard[0]:self.shard[1]]
+        return self.local(x)
+
     def forward(self, x):
         if not self.input_is_parallel:
             x = x[..., self.shard[0]:self.shard[1]]
@@ -160,6 +169,35 @@ class RowParallelFP8Linear(nn.Module):
         if self.bias_f32 is not None:
             part = part + self.bias_f32
         return part.to(self.out_dtype)
+
+
+class FusedAllReduceNorm:
+    """Exchange context of `tfp8b_allreduce_add_rmsnorm` for one tensor-parallel group: the
+    symmetric-memory receive area and flags of every rank, and the local call-sequence state.
+    One context serves every row-parallel layer of a model (calls are ordered by the stream)."""
+
+    def __init__(self, dim, max_rows=8, group=None, device=None):
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.dim, self.max_rows = dim, max_rows
+        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.recv = symm.empty(2 * self.world * max_rows * dim, dtype=torch.float32, device=device)
+        self.flags = symm.empty(2 * self.world * max_rows, dtype=torch.int32, device=device)
+        self.recv.zero_()
+        self.flags.zero_()
+        self._hr = symm.rendezvous(self.recv, group.group_name)
+        self._hf = symm.rendezvous(self.flags, group.group_name)
+        self.recv_ptrs = [int(self._hr.buffer_ptrs[r]) for r in range(self.world)]
+        self.flag_ptrs = [int(self._hf.buffer_ptrs[r]) for r in range(self.world)]
+        self.state = torch.zeros(2, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)                      # nobody pushes before every rank has zeroed its flags
+
+    def add_rmsnorm(self, x, partial, weight, eps):
+        from . import _ext
+        return _ext.allreduce_add_rmsnorm(x, partial, weight, eps, self.recv_ptrs, self.flag_ptrs, self.state, self.rank,
+                                          self.max_rows)
 
 
 def shard_llama_style(model: nn.Module, group=None):

@@ -206,6 +206,21 @@ TFP8B_API int tfp8b_gemm_splitk(const void* x16, const float* xs, const uint8_t*
 TFP8B_API int tfp8b_add_rmsnorm(void* x, const void* delta, const void* weight, void* out, int dtype,
                   long long rows, int dim, float eps, tfp8b_stream_t stream);
 
+/* tfp8b_add_rmsnorm whose addend is the SUM over the ranks of a tensor-parallel group of FP32 partial
+ * results [rows, dim] (the output of a row-parallel projection): the all-reduce, the residual
+ * update and the RMSNorm in one launch, for the few rows of a decode step. Each rank pushes its
+ * partial rows into every peer's receive area with plain peer stores, raises a per-row flag, waits
+ * (bounded) for the peers' flags and adds the partials in rank order, so every rank computes the
+ * same bits. recv[r] / flags[r] (HOST arrays of `world` device pointers, peer-mapped memory) are
+ * rank r's receive area, 2 * world * max_rows * dim floats, and flag array, 2 * world * max_rows
+ * uint32, both zeroed once before the first call; state is two zeroed uint32 of local device
+ * memory (the call sequence number lives there, which keeps the call replayable from a CUDA
+ * graph). Every rank issues the same calls in the same order; world <= 8, dim <= 4096.
+ * No counterpart in the reference (single GPU). */
+TFP8B_API int tfp8b_allreduce_add_rmsnorm(void* x, const float* partial, const void* weight, void* out, int dtype,
+                  int rows, int dim, float eps, float* const* recv, unsigned int* const* flags,
+                  unsigned int* state, int rank, int world, int max_rows, tfp8b_stream_t stream);
+
 /* One-query attention over the static KV cache, grouped-query heads: for every sequence b and head h,
  * out[b, h, :] = softmax(q[b, h, :] . K[b, h / (H/KV), 0:pos+1, :]^T / sqrt(hd)) V[...]. q and out are
  * [B, H, hd]; the caches [B, KV, max_seq, hd]; pos is ONE int64 on the device (the cache position of

@@ -70,6 +70,41 @@ def test_add_rmsnorm(dtype, dim):
 
 
 @pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16))
+def test_allreduce_add_rmsnorm_single_rank(dtype):
+    """The fused all-reduce + residual + RMSNorm with a group of one rank (no peers to wait for):
+    the same residual as add_rmsnorm on the partial rounded to the activation type and the same
+    norm within a rounding of the output type, call after call (the sequence number advances in device memory), also replayed from a CUDA graph."""
+    from tfp8 import _ext
+    torch.manual_seed(5)
+    dim, rows = 4096, 3
+    w = (1 + 0.1 * torch.randn(dim, device="cuda")).to(dtype)
+    recv = torch.zeros(2 * 1 * 8 * dim, dtype=torch.float32, device="cuda")
+    flags = torch.zeros(2 * 1 * 8, dtype=torch.int32, device="cuda")
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    for call in range(3):
+        x = torch.randn(rows, 1, dim, device="cuda").to(dtype)
+        part = torch.randn(rows, 1, dim, device="cuda")
+        x_ref = x.clone()
+        want = _ext.add_rmsnorm(x_ref, part.to(dtype), w, 1e-5)
+        got = _ext.allreduce_add_rmsnorm(x, part, w, 1e-5, [recv.data_ptr()], [flags.data_ptr()], state, 0, 8)
+        assert torch.equal(x, x_ref)                                  # the residual, bit for bit
+        tol = 2.0 ** -9 if dtype == torch.float16 else 2.0 ** -7        # the sum of squares is grouped differently
+        assert ((got.float() - want.float()).abs() <= tol * want.float().abs() + 1e-5).all()
+        assert state.tolist() == [call + 1, 0]
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        x.copy_(x_ref)                                              # restore, then capture one call
+        with torch.cuda.graph(g, stream=s):
+            out = _ext.allreduce_add_rmsnorm(x, part, w, 1e-5, [recv.data_ptr()], [flags.data_ptr()], state, 0, 8)
+        g.replay(); g.replay()
+    torch.cuda.synchronize()
+    assert state.tolist() == [5, 0] and bool(torch.isfinite(out.float()).all())
+    assert _ext.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16))
 def test_argmax(dtype):
     from tfp8 import _ext
     torch.manual_seed(3)
