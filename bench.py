@@ -438,7 +438,10 @@ def llama_decode_measurements(device, peaks, world, batches=(1, 4, 8), prompt=20
         e0.record(); out = run.decode(new_tokens); e1.record(); torch.cuda.synchronize()
         dec_s = max_over_ranks(e0.elapsed_time(e1) / 1e3, world, device)
         ms_tok = dec_s / new_tokens * 1e3
-        rows.append({"batch": B, "tp": world, "prefill_tokens": prompt, "prefill_ms": prefill_s * 1e3,
+        rows.append({"batch": B, "tp": world,
+                     "allreduce": None if world == 1 else ("fused into add+norm (peer stores)" if model.layers[0].comm is not None
+                                                            else "nccl"),
+                     "prefill_tokens": prompt, "prefill_ms": prefill_s * 1e3,
                      "prefill_tok_s": B * prompt / prefill_s, "decode_tokens": new_tokens, "ms_per_step": ms_tok,
                      "decode_tok_s": B * new_tokens / dec_s,
                      "hbm_bound_ms_per_step": stream_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3,

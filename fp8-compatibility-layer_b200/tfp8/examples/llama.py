@@ -271,7 +271,14 @@ class DecodeRunner:
         model.set_comm(None)
         if fused_allreduce and model.tp > 1 and dev.type == "cuda" and model.embed.weight.dtype in (torch.float16, torch.bfloat16):
             from ..parallel import FusedAllReduceNorm
-            model.set_comm(FusedAllReduceNorm(model.cfg.d_model, max_rows=max(8, batch), device=dev))
+            comm = None
+            try:
+                comm = FusedAllReduceNorm(model.cfg.d_model, max_rows=max(8, batch), device=dev)
+            except Exception as e:               # no peer-mapped memory here: NCCL all-reduces instead
+                self.fused_allreduce_error = f"{type(e).__name__}: {e}"
+            ok = torch.tensor([0 if comm is None else 1], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)               # every rank takes the same path
+            model.set_comm(comm if int(ok) else None)
         self.tok = torch.zeros(batch, 1, dtype=torch.int64, device=dev)
         self.pos = torch.zeros(1, dtype=torch.int64, device=dev)
         self.graph = None
