@@ -4,6 +4,8 @@
 // loads and stores, 16 elements per thread per step, grids sized in multiples of the SM count.
 #include <float.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace tfp8b {
@@ -159,9 +161,21 @@ __global__ void __launch_bounds__(EW_THREADS) decode_kernel(const uint8_t* __res
     const int64_t nvec = vec_ok ? n / 16 : 0;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-        float v[16];
-        decode16<FMT>(reinterpret_cast<const uint4*>(codes)[i], v);
-        store16<T>(out + i * 16, v);
+        const uint4 raw = reinterpret_cast<const uint4*>(codes)[i];
+        if (sizeof(T) == 2) {
+            // 16-bit outputs: the packed conversion result is the output (every FP8 value is exact in
+            // fp16 and bf16; a NaN code stays a NaN), no detour through float
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            uint32_t h[8];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dec4<FMT, std::is_same<T, __nv_bfloat16>::value>(w[e], h[2 * e], h[2 * e + 1]);
+            reinterpret_cast<uint4*>(out + i * 16)[0] = make_uint4(h[0], h[1], h[2], h[3]);
+            reinterpret_cast<uint4*>(out + i * 16)[1] = make_uint4(h[4], h[5], h[6], h[7]);
+        } else {
+            float v[16];
+            decode16<FMT>(raw, v);
+            store16<T>(out + i * 16, v);
+        }
     }
     for (int64_t i = nvec * 16 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
         {
@@ -196,7 +210,8 @@ __global__ void __launch_bounds__(EW_THREADS) dequant_kernel(const uint8_t* __re
 // ------------------------------------------------------------------ one-pass weight quantizer
 // One CTA per weight row. Pass 1: per-group amax into shared memory (non-negative floats order
 // like their bit patterns, so an integer atomicMax does it). Pass 2 re-reads the row (now in
-// L1/L2), divides by the group scale and encodes. 16 contiguous elements per thread per step.
+// L1/L2 -- keeping it in shared memory instead measured slower), divides by the group scale and
+// encodes. 16 contiguous elements per thread per step.
 __device__ __forceinline__ float scale_from_amax(float amax, float fmax, int pow2) {
     if (amax == 0.f) return 1.f;
     float s = fmaxf(__fdiv_rn(amax, fmax), FLT_MIN);

@@ -471,7 +471,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         for (int h2 = 0; h2 < RPT; ++h2) {
                             const uint32_t w[4] = {q[h2].x, q[h2].y, q[h2].z, q[h2].w};
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) dec4<FMT, false>(w[e], h[h2][2 * e], h[h2][2 * e + 1]);
+                            for (int e = 0; e < 4; ++e) dec4_split<FMT>(w[e], h[h2][2 * e], h[h2][2 * e + 1]);
                         }
                     }
                     if (ng > 1) {
