@@ -64,6 +64,18 @@ struct GemvParams {
     void* y;
     int M, N, K, G, scale_kind, y_dt;
     int nstages, wpitch, xpitch, wstage_bytes, stage_bytes, x_resident, xres_bytes, ntiles, pdl;
+    // Activations computed by the kernel itself instead of copied (16-bit types, resident rows):
+    //   xmode 1  x = RMSNorm(xa + xb) * xw: the residual update (xb may be null) and the norm of a
+    //            decoder block; the CTA with index 0 also stores the updated residual to xout
+    //   xmode 2  x = silu(xa[:, 0:K]) * xa[:, K:2K]: the gated activation of a fused gate/up output
+    // Every CTA recomputes the few rows (they come from L2); what it saves is a kernel in the
+    // dependent chain of a decode step.
+    int xmode;
+    const void* xa;
+    const void* xb;
+    const void* xw;
+    void* xout;
+    float xeps;
 };
 
 __device__ __forceinline__ void mma16816_f16(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -173,6 +185,98 @@ __device__ __forceinline__ void block32(float (*c)[4], uint32_t wa_addr, uint32_
 }
 
 // Which weight row of the 16-row tile sits in MMA row g (0..7; MMA row g+8 holds that row + 8).
+// 16-bit pair helpers for the computed-activation modes
+__device__ __forceinline__ float2 gv_unpack(__half2 v) { return __half22float2(v); }
+__device__ __forceinline__ float2 gv_unpack(__nv_bfloat162 v) { return __bfloat1622float2(v); }
+__device__ __forceinline__ float2 gv_unpack(float2 v) { return v; }
+template <typename P> __device__ __forceinline__ P gv_pack(float a, float b);
+template <> __device__ __forceinline__ __half2 gv_pack<__half2>(float a, float b) { return __floats2half2_rn(a, b); }
+template <> __device__ __forceinline__ __nv_bfloat162 gv_pack<__nv_bfloat162>(float a, float b) { return __floats2bfloat162_rn(a, b); }
+template <> __device__ __forceinline__ float2 gv_pack<float2>(float a, float b) { return make_float2(a, b); }
+template <typename XT> struct gv_pair { using type = float2; };
+template <> struct gv_pair<__half> { using type = __half2; };
+template <> struct gv_pair<__nv_bfloat16> { using type = __nv_bfloat162; };
+
+// The consumer warps (GV_WARPS * 32 threads) fill the resident activation rows themselves. `scratch`
+// is the (still unused) reduction area of the header. Named barrier 2 is theirs alone.
+template <typename XT>
+__device__ __forceinline__ void compute_activations(const GemvParams& p, uint8_t* xres, float* scratch, int warp, int lane) {
+    using P = typename gv_pair<XT>::type;
+    constexpr int NT = GV_WARPS * 32;
+    const int tid = warp * 32 + lane, nvec = p.K / 8;
+    if (sizeof(XT) != 2) return;                                   // 16-bit activations only (checked on the host)
+    if (p.xmode == 2) {
+        const XT* gu = reinterpret_cast<const XT*>(p.xa);
+        for (int m = 0; m < p.M; ++m) {
+            const XT* row = gu + static_cast<size_t>(m) * 2 * p.K;
+            for (int v = tid; v < nvec; v += NT) {
+                const uint4 g = *reinterpret_cast<const uint4*>(row + v * 8);
+                const uint4 u = *reinterpret_cast<const uint4*>(row + p.K + v * 8);
+                const P* gp = reinterpret_cast<const P*>(&g);
+                const P* up = reinterpret_cast<const P*>(&u);
+                uint4 o;
+                P* op = reinterpret_cast<P*>(&o);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 a = gv_unpack(gp[i]), b = gv_unpack(up[i]);
+                    op[i] = gv_pack<P>(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+                }
+                *reinterpret_cast<uint4*>(xres + m * p.xpitch + v * 16) = o;
+            }
+        }
+        named_barrier_sync(2, NT);
+        return;
+    }
+    // xmode 1: residual (+ delta), rounded to the activation type, kept in shared memory; sum of squares
+    const XT* ra = reinterpret_cast<const XT*>(p.xa);
+    const XT* rb = reinterpret_cast<const XT*>(p.xb);
+    XT* ro = reinterpret_cast<XT*>(p.xout);
+    for (int m = 0; m < p.M; ++m) {
+        float ss = 0.f;
+        for (int v = tid; v < nvec; v += NT) {
+            uint4 a = *reinterpret_cast<const uint4*>(ra + static_cast<size_t>(m) * p.K + v * 8);
+            P* ap = reinterpret_cast<P*>(&a);
+            if (rb) {
+                const uint4 d = *reinterpret_cast<const uint4*>(rb + static_cast<size_t>(m) * p.K + v * 8);
+                const P* dp = reinterpret_cast<const P*>(&d);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = gv_unpack(ap[i]), g = gv_unpack(dp[i]);
+                    ap[i] = gv_pack<P>(f.x + g.x, f.y + g.y);
+                }
+            }
+            if (ro && blockIdx.x == 0) *reinterpret_cast<uint4*>(ro + static_cast<size_t>(m) * p.K + v * 8) = a;
+            *reinterpret_cast<uint4*>(xres + m * p.xpitch + v * 16) = a;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = gv_unpack(ap[i]); ss += f.x * f.x + f.y * f.y; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) scratch[m * GV_WARPS + warp] = ss;
+    }
+    named_barrier_sync(2, NT);
+    const XT* wv = reinterpret_cast<const XT*>(p.xw);
+    for (int m = 0; m < p.M; ++m) {
+        float ss = 0.f;
+#pragma unroll
+        for (int w = 0; w < GV_WARPS; ++w) ss += scratch[m * GV_WARPS + w];
+        const float rstd = rsqrtf(ss / static_cast<float>(p.K) + p.xeps);
+        for (int v = tid; v < nvec; v += NT) {
+            uint4 a = *reinterpret_cast<const uint4*>(xres + m * p.xpitch + v * 16);
+            const uint4 wq = *reinterpret_cast<const uint4*>(wv + v * 8);
+            P* ap = reinterpret_cast<P*>(&a);
+            const P* wp = reinterpret_cast<const P*>(&wq);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = gv_unpack(ap[i]), g = gv_unpack(wp[i]);
+                ap[i] = gv_pack<P>(f.x * rstd * g.x, f.y * rstd * g.y);
+            }
+            *reinterpret_cast<uint4*>(xres + m * p.xpitch + v * 16) = a;
+        }
+    }
+    named_barrier_sync(2, NT);
+}
+
 // With the tensor-map layout the rows of a tile are 128 bytes apart and the 16-byte pieces of a
 // row are XOR-swizzled with (row & 7): the permutation puts rows that differ in the right bit
 // into the lanes that load together, which makes the loads bank-conflict free (128-bit loads go
@@ -198,7 +302,10 @@ __device__ __forceinline__ int tile_row_of(int g) {
 // SMODE 0: one scale per output channel (applied once, at the end)
 //       1: K-groups that are multiples of 64 (applied per 64-code block)
 //       2: K-groups that are multiples of 32 only (32-code blocks)
-template <typename XT, int FMT, int SMODE, bool TMA>
+// XF: the activations are computed by the kernel (GemvParams::xmode) instead of copied. A template
+// parameter, not a run-time branch: the plain kernel stays exactly the code it was (the branch
+// alone cost it 1 % of its bandwidth).
+template <typename XT, int FMT, int SMODE, bool TMA, bool XF>
 __global__ void __launch_bounds__(GV_THREADS, 2)
 gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemvParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -282,7 +389,7 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             if (++c == nchunks) { c = 0; ++t; }
         }
         if (p.pdl == 1) pdl_wait();                      // activations may be the predecessor's output
-        if (p.x_resident) {
+        if (p.x_resident && !XF) {
             // resident activations: plain rows (pitch xpitch), loaded once per CTA by bulk copies
             if (lane == 0) mbar_expect_tx(bar_x, static_cast<uint32_t>(p.M * p.K * SZ));
             __syncwarp();
@@ -291,7 +398,7 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 for (int off = 0; off < p.K * SZ; off += 16384)
                     bulk_g2s(smem_u32(xres + xm * p.xpitch + off), xrow + off, min(16384, p.K * SZ - off), bar_x, pol_x);
             }
-        } else {
+        } else if (!p.x_resident) {
             int cx = 0;
             for (int i = 0; i < pre; ++i) {
                 issue_x(cx, i);
@@ -336,7 +443,12 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         }
         const uint32_t stages_u32 = smem_u32(stages), xres_u32 = smem_u32(xres);
         bool ok = true;
-        if (p.x_resident) ok = mbar_wait(bar_x, 0, STATUS_GEMV_WAIT);
+        if (XF) {
+            if (p.pdl) pdl_wait();                       // the inputs are the predecessor's output
+            compute_activations<XT>(p, xres, red, warp, lane);
+        } else if (p.x_resident) {
+            ok = mbar_wait(bar_x, 0, STATUS_GEMV_WAIT);
+        }
         int slot = 0;
         uint32_t phase = 0;                              // ring position: no divisions in the loop
         // A wait that runs out clears `ok`; the warp then stops waiting and computing but keeps
@@ -458,7 +570,7 @@ static int sm_count_of_current_device() {
     return n;
 }
 
-template <typename XT, int FMT, int SMODE, bool TMA>
+template <typename XT, int FMT, int SMODE, bool TMA, bool XF>
 static int launch_gemv(const CUtensorMap& tw, const CUtensorMap& tx, const GemvParams& p, size_t smem, cudaStream_t st) {
     // The opt-in to more than 48 KB of dynamic shared memory is per device and per kernel.
     static unsigned long long configured = 0ull;        // bit d set: done on device d
@@ -466,7 +578,7 @@ static int launch_gemv(const CUtensorMap& tw, const CUtensorMap& tx, const GemvP
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (dev >= 64 || !((configured >> dev) & 1ull)) {
-        e = cudaFuncSetAttribute(gemv_kernel<XT, FMT, SMODE, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        e = cudaFuncSetAttribute(gemv_kernel<XT, FMT, SMODE, TMA, XF>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemv)");
         if (dev < 64) __atomic_fetch_or(&configured, 1ull << dev, __ATOMIC_RELAXED);
     }
@@ -481,7 +593,7 @@ static int launch_gemv(const CUtensorMap& tw, const CUtensorMap& tx, const GemvP
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = p.pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, gemv_kernel<XT, FMT, SMODE, TMA>, tw, tx, p);
+    e = cudaLaunchKernelEx(&cfg, gemv_kernel<XT, FMT, SMODE, TMA, XF>, tw, tx, p);
     if (e != cudaSuccess) return cuda_fail(e, "tfp8b_gemv launch");
     return TFP8B_OK;
 }
@@ -489,9 +601,19 @@ static int launch_gemv(const CUtensorMap& tw, const CUtensorMap& tx, const GemvP
 template <typename XT>
 static int dispatch_gemv(const CUtensorMap& tw, const CUtensorMap& tx, const GemvParams& p, int fmt, int smode, bool tma,
                          size_t smem, cudaStream_t st) {
+    if (p.xmode != 0) {          // computed activations: 16-bit types on the tensor-map layout only (checked by the caller)
+        if (sizeof(XT) == 2) {
+#define GV_CASE(F, S) if (fmt == F && smode == S) return launch_gemv<XT, F, S, true, (sizeof(XT) == 2)>(tw, tx, p, smem, st)
+            GV_CASE(TFP8B_E4M3FN, 0); GV_CASE(TFP8B_E4M3FN, 1); GV_CASE(TFP8B_E4M3FN, 2);
+            GV_CASE(TFP8B_E5M2, 0);   GV_CASE(TFP8B_E5M2, 1);   GV_CASE(TFP8B_E5M2, 2);
+#undef GV_CASE
+        }
+        set_error("tfp8b_gemv: computed activations need f16 / bf16");
+        return TFP8B_ERR_UNSUPPORTED;
+    }
 #define GV_CASE(F, S)                                                                   \
     if (fmt == F && smode == S)                                                         \
-        return tma ? launch_gemv<XT, F, S, true>(tw, tx, p, smem, st) : launch_gemv<XT, F, S, false>(tw, tx, p, smem, st)
+        return tma ? launch_gemv<XT, F, S, true, false>(tw, tx, p, smem, st) : launch_gemv<XT, F, S, false, false>(tw, tx, p, smem, st)
     GV_CASE(TFP8B_E4M3FN, 0); GV_CASE(TFP8B_E4M3FN, 1); GV_CASE(TFP8B_E4M3FN, 2);
     GV_CASE(TFP8B_E5M2, 0);   GV_CASE(TFP8B_E5M2, 1);   GV_CASE(TFP8B_E5M2, 2);
 #undef GV_CASE
@@ -516,9 +638,44 @@ extern "C" int tfp8b_gemv(const void* x, int x_dtype, const uint8_t* codes, cons
     return tfp8b_gemv_ex(x, x_dtype, codes, scale, scale_kind, bias, y, y_dtype, M, N, K, G, fmt, 0u, stream);
 }
 
+static int gemv_impl(const void* x, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind, const float* bias,
+                     void* y, int y_dtype, int M, int N, int K, int G, int fmt, unsigned int flags, int xmode, const void* xa,
+                     const void* xb, const void* xw, void* xout, float xeps, tfp8b_stream_t stream);
+
 extern "C" int tfp8b_gemv_ex(const void* x, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind,
                              const float* bias, void* y, int y_dtype, int M, int N, int K, int G, int fmt,
                              unsigned int flags, tfp8b_stream_t stream) {
+    return gemv_impl(x, x_dtype, codes, scale, scale_kind, bias, y, y_dtype, M, N, K, G, fmt, flags, 0, nullptr, nullptr, nullptr,
+                     nullptr, 0.f, stream);
+}
+
+extern "C" int tfp8b_gemv_normed(void* residual_out, const void* residual, const void* delta, const void* norm_weight, float eps,
+                                 int x_dtype, const uint8_t* codes, const void* scale, int scale_kind, const float* bias, void* y,
+                                 int y_dtype, int M, int N, int K, int G, int fmt, tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(x_dtype == TFP8B_F16 || x_dtype == TFP8B_BF16, TFP8B_ERR_UNSUPPORTED, "tfp8b_gemv_normed: f16 / bf16 activations only");
+    if (M == 0 || N == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(residual && norm_weight, TFP8B_ERR_INVALID, "tfp8b_gemv_normed: null pointer");
+    TFP8B_REQUIRE(residual_out != residual || !delta, TFP8B_ERR_INVALID,
+                  "tfp8b_gemv_normed: the updated residual needs a buffer of its own (every CTA reads the old one)");
+    TFP8B_REQUIRE(((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(norm_weight) |
+                    reinterpret_cast<uintptr_t>(residual_out)) & 15u) == 0, TFP8B_ERR_INVALID, "tfp8b_gemv_normed: buffers must be 16-byte aligned");
+    return gemv_impl(residual, x_dtype, codes, scale, scale_kind, bias, y, y_dtype, M, N, K, G, fmt, 0u, 1, residual, delta, norm_weight,
+                     residual_out, eps, stream);
+}
+
+extern "C" int tfp8b_gemv_gated(const void* gate_up, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind,
+                                const float* bias, void* y, int y_dtype, int M, int N, int K, int G, int fmt,
+                                tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(x_dtype == TFP8B_F16 || x_dtype == TFP8B_BF16, TFP8B_ERR_UNSUPPORTED, "tfp8b_gemv_gated: f16 / bf16 activations only");
+    if (M == 0 || N == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(gate_up && (reinterpret_cast<uintptr_t>(gate_up) & 15u) == 0, TFP8B_ERR_INVALID, "tfp8b_gemv_gated: gate_up null or unaligned");
+    return gemv_impl(gate_up, x_dtype, codes, scale, scale_kind, bias, y, y_dtype, M, N, K, G, fmt, 0u, 2, gate_up, nullptr, nullptr,
+                     nullptr, 0.f, stream);
+}
+
+static int gemv_impl(const void* x, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind, const float* bias,
+                     void* y, int y_dtype, int M, int N, int K, int G, int fmt, unsigned int flags, int xmode, const void* xa,
+                     const void* xb, const void* xw, void* xout, float xeps, tfp8b_stream_t stream) {
     TFP8B_REQUIRE(M >= 0 && N >= 0 && K > 0 && G > 0, TFP8B_ERR_INVALID, "tfp8b_gemv: bad size M=%d N=%d K=%d G=%d", M, N, K, G);
     TFP8B_REQUIRE(x_dtype >= 0 && x_dtype <= 2 && y_dtype >= 0 && y_dtype <= 2, TFP8B_ERR_INVALID, "tfp8b_gemv: bad dtype");
     TFP8B_REQUIRE(fmt == TFP8B_E4M3FN || fmt == TFP8B_E5M2, TFP8B_ERR_INVALID, "tfp8b_gemv: bad fmt %d", fmt);
@@ -537,6 +694,7 @@ extern "C" int tfp8b_gemv_ex(const void* x, int x_dtype, const uint8_t* codes, c
     p.x = x; p.w = codes; p.scale = scale; p.bias = bias; p.y = y;
     p.M = M; p.N = N; p.K = K; p.G = G; p.scale_kind = scale_kind; p.y_dt = y_dtype;
     p.ntiles = (N + GV_ROWS - 1) / GV_ROWS;
+    p.xmode = xmode; p.xa = xa; p.xb = xb; p.xw = xw; p.xout = xout; p.xeps = xeps;
     // TFP8B_NO_PDL=1 turns programmatic dependent launch off (profilers serialise kernels anyway);
     // TFP8B_GEMV_BULK=1 forces the bulk-copy layout.
     static const int no_pdl = [] { const char* v = getenv("TFP8B_NO_PDL"); return v && v[0] == '1'; }();
@@ -586,6 +744,8 @@ extern "C" int tfp8b_gemv_ex(const void* x, int x_dtype, const uint8_t* codes, c
         p.xres_bytes = p.x_resident ? ((M * p.xpitch + 1023) & ~1023) : 0;
         p.stage_bytes = (p.wstage_bytes + (p.x_resident ? 0 : M * p.xpitch) + 127) & ~127;
     }
+    TFP8B_REQUIRE(xmode == 0 || (p.x_resident && tma), TFP8B_ERR_UNSUPPORTED,
+                  "tfp8b_gemv: computed activations need K %% 128 == 0 and M * K small enough to stay resident (M=%d K=%d)", M, K);
     const int target = (p.x_resident && p.xres_bytes <= GV_XRES_SMALL) ? GV_SMEM_TARGET : GV_SMEM_LARGE;
     int S = (target - 1024 - GV_HEADER - p.xres_bytes) / p.stage_bytes;
     S = S < 2 ? 2 : (S > GV_MAX_STAGES ? GV_MAX_STAGES : S);

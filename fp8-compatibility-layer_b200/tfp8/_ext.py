@@ -40,6 +40,8 @@ _SIGNATURES = {
     "tfp8b_gemv": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_gemv_ex": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.c_uint, _P], _I),
     "tfp8b_gemm": ([_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
+    "tfp8b_gemv_normed": ([_P, _P, _P, _P, ctypes.c_float, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
+    "tfp8b_gemv_gated": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_gemm_splitk": ([_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P], _I),
     "tfp8b_gemm_scatter": ([_P, _P, _P, _P, _I, _P, _P, _I, ctypes.c_longlong, ctypes.c_longlong, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_linear_static": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
@@ -450,3 +452,39 @@ def allreduce_add_rmsnorm(x, partial, weight, eps, recv_ptrs, flag_ptrs, state, 
                                                 rows, dim, float(eps), rp, fp, state.data_ptr(), rank, world, max_rows, _stream(dev))
     _check(rc, "tfp8b_allreduce_add_rmsnorm")
     return out
+
+
+def gemv_normed(residual, delta, norm_weight, eps, qweight, wscale, bias, out_dtype, group_size, fmt="e4m3fn"):
+    """(residual + delta, RMSNorm(residual + delta) * norm_weight @ W^T) for at most 8 rows in one
+    GEMV launch: the activations are computed inside the kernel. residual, delta [..., K] f16 / bf16
+    (delta may be None); returns the NEW residual (a fresh tensor) and y [..., N]."""
+    dev = _need_cuda(residual, delta, norm_weight, qweight, wscale, bias)
+    K = residual.shape[-1]
+    M = residual.numel() // K
+    N = qweight.shape[0]
+    new_res = torch.empty_like(residual) if delta is not None else residual
+    y = torch.empty(*residual.shape[:-1], N, dtype=out_dtype, device=residual.device)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_gemv_normed(new_res.data_ptr() if delta is not None else None, residual.data_ptr(),
+                                      None if delta is None else delta.data_ptr(), norm_weight.data_ptr(), float(eps),
+                                      _DT[residual.dtype], qweight.data_ptr(), wscale.data_ptr(), _scale_kind(wscale),
+                                      bias.data_ptr() if bias is not None else None, y.data_ptr(), _DT[out_dtype], M, N, K,
+                                      group_size, FMT_ID[fmt], _stream(dev))
+    _check(rc, "tfp8b_gemv_normed")
+    return new_res, y
+
+
+def gemv_gated(gate_up, qweight, wscale, bias, out_dtype, group_size, fmt="e4m3fn"):
+    """(silu(gate) * up) @ W^T for a fused gate/up output [..., 2K] (f16 / bf16, at most 8 rows) in one
+    GEMV launch."""
+    dev = _need_cuda(gate_up, qweight, wscale, bias)
+    K = gate_up.shape[-1] // 2
+    M = gate_up.numel() // (2 * K)
+    N = qweight.shape[0]
+    y = torch.empty(*gate_up.shape[:-1], N, dtype=out_dtype, device=gate_up.device)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_gemv_gated(gate_up.data_ptr(), _DT[gate_up.dtype], qweight.data_ptr(), wscale.data_ptr(), _scale_kind(wscale),
+                                     bias.data_ptr() if bias is not None else None, y.data_ptr(), _DT[out_dtype], M, N, K,
+                                     group_size, FMT_ID[fmt], _stream(dev))
+    _check(rc, "tfp8b_gemv_gated")
+    return y

@@ -60,6 +60,18 @@ def _rope(x, cos, sin):
     return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
 
 
+# Decode steps of at most this many rows take the path whose GEMVs compute their own activations
+# (norm + residual, SwiGLU): three kernels fewer per block in the dependent chain. Every CTA of
+# such a GEMV recomputes the rows from L2, which stops paying beyond a couple of rows.
+FUSE_ROWS = 2
+
+
+def _w8(layer, fn, *args):
+    """Call a computed-activation GEMV of the library with an FP8Linear's buffers."""
+    layer.stats["gemv"] += 1
+    return fn(*args, layer.qweight, layer._kernel_scale(), layer.bias_f32, layer.out_dtype, layer.group_size, layer.fmt)
+
+
 class _Partial:
     """A row-parallel projection's output still to be summed over the ranks (float32, this rank's part)."""
 
@@ -93,6 +105,21 @@ class Block(nn.Module):
         # split-KV partial results of the decode attention; one buffer can serve all blocks
         self.attn_scratch = None
 
+    def _decode_few_rows(self, x, delta, pos, mask):
+        """Block.forward for one or two decode rows on one GPU: 7 kernels instead of 10."""
+        B, T, _ = x.shape
+        hd, eps = self.cfg.head_dim, self.cfg.eps
+        x, qkv = _w8(self.qkv_proj, _ext.gemv_normed, x, delta, self.input_layernorm.weight, eps)
+        q = _ext.rope_kv_store(qkv, pos, self.cos_table, self.sin_table, self.k_cache, self.v_cache, self.h_local, self.kv_local)
+        if mask is False:
+            a = _ext.attn_decode(q, self.k_cache, self.v_cache, pos, self.attn_scratch).view(B, 1, self.h_local * hd)
+        else:
+            a = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask, enable_gqa=True)
+            a = a.transpose(1, 2).reshape(B, T, self.h_local * hd)
+        o = self.o_proj(a)
+        x, gu = _w8(self.gate_up_proj, _ext.gemv_normed, x, o, self.post_attention_layernorm.weight, eps)
+        return x, _w8(self.down_proj, _ext.gemv_gated, gu)
+
     def forward(self, x, delta, pos, cos, sin, mask):
         """x [B, T, d] the residual stream and delta the previous block's MLP output not yet added
         to it (None for the first block); pos int64 [T] (device) = cache positions of these tokens;
@@ -102,6 +129,9 @@ class Block(nn.Module):
         B, T, _ = x.shape
         hd = self.cfg.head_dim
         fused = x.is_cuda and x.dtype in (torch.float16, torch.bfloat16)
+        if (fused and self.tp == 1 and B * T <= FUSE_ROWS and mask is not None and not isinstance(delta, _Partial)
+                and isinstance(self.qkv_proj, FP8Linear) and self.qkv_proj._kernels_ok):
+            return self._decode_few_rows(x, delta, pos, mask)
         # tensor-parallel decode: the all-reduce after o_proj / down_proj rides in the add + norm kernel
         comm = self.comm if (fused and self.comm is not None and B * T <= self.comm.max_rows) else None
         if isinstance(delta, _Partial):

@@ -176,6 +176,24 @@ TFP8B_API int tfp8b_rope_kv_store(const void* qkv, int dtype, const long long* p
 TFP8B_API int tfp8b_silu_mul(const void* gate_up, void* out, int dtype, long long rows, int F,
                   tfp8b_stream_t stream);
 
+/* Decode GEMVs that compute their activations instead of reading them, which takes one kernel out
+ * of the dependent chain of a decode step each (every CTA recomputes the M <= 8 rows from L2):
+ *   tfp8b_gemv_normed  x = RMSNorm(residual + delta) * norm_weight (delta may be NULL), y = x W^T;
+ *                      the updated residual is also stored to residual_out (NULL to skip), which
+ *                      must not be `residual` itself when delta is given;
+ *   tfp8b_gemv_gated   x = silu(gate_up[:, 0:K]) * gate_up[:, K:2K] for a fused gate/up output
+ *                      [M, 2K], y = x W^T.
+ * f16 / bf16 activations, rows short enough to stay in shared memory (M * K * 2 <= 96 KB); the
+ * other arguments as tfp8b_gemv. (Reference: RMSNorm, residual adds and SwiGLU of
+ * tfp8/examples/demo_llm.py:30-39, 86-87, 98-101 around its FP8Linear calls.) */
+TFP8B_API int tfp8b_gemv_normed(void* residual_out, const void* residual, const void* delta, const void* norm_weight,
+                  float eps, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind,
+                  const float* bias, void* y, int y_dtype, int M, int N, int K, int G, int fmt,
+                  tfp8b_stream_t stream);
+TFP8B_API int tfp8b_gemv_gated(const void* gate_up, int x_dtype, const uint8_t* codes, const void* scale,
+                  int scale_kind, const float* bias, void* y, int y_dtype, int M, int N, int K, int G,
+                  int fmt, tfp8b_stream_t stream);
+
 /* tfp8b_gemm whose N output columns land at columns [col0, col0 + N) of wider outputs (row pitch
  * ldy elements), in n_dst buffers at once (1..8; y_dst is a HOST array of device pointers). With
  * the buffers of every GPU of a tensor-parallel group (peer-mapped memory: CUDA IPC, symmetric

@@ -105,6 +105,39 @@ def test_allreduce_add_rmsnorm_single_rank(dtype):
 
 
 @pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16))
+@pytest.mark.parametrize("G", (None, 128))
+def test_gemv_with_computed_activations(dtype, G):
+    """The GEMVs that build their activations inside the kernel (residual + RMSNorm; SwiGLU) against
+    the unfused sequence add_rmsnorm / silu_mul -> FP8Linear on the same inputs."""
+    import torch.nn as nn
+    from tfp8 import FP8Linear, _ext
+    torch.manual_seed(6)
+    K, N = 4096, 1536
+    lin = nn.Linear(K, N, bias=False, device="cuda", dtype=dtype)
+    f = FP8Linear.from_linear(lin, group_size=G, nan_check=False)
+    w = (1 + 0.1 * torch.randn(K, device="cuda")).to(dtype)
+    for M in (1, 2, 5):
+        x = torch.randn(M, 1, K, device="cuda").to(dtype)
+        d = (torch.randn(M, 1, K, device="cuda") * 0.5).to(dtype)
+        x_ref = x.clone()
+        h = _ext.add_rmsnorm(x_ref, d, w, 1e-5)
+        want = f(h).float()
+        new_res, got = _ext.gemv_normed(x, d, w, 1e-5, f.qweight, f.weight_scale, None, f.out_dtype, f.group_size, f.fmt)
+        assert torch.equal(new_res, x_ref)                            # the updated residual, bit for bit
+        tol = 4e-3 if dtype == torch.float16 else 2e-2                 # the norm may differ by a rounding of the type
+        assert (got.float() - want).abs().max() <= tol * max(1.0, float(want.abs().max()))
+        # no delta: the residual is only normalised, and not copied
+        res2, got2 = _ext.gemv_normed(x_ref, None, w, 1e-5, f.qweight, f.weight_scale, None, f.out_dtype, f.group_size, f.fmt)
+        assert res2 is x_ref
+        assert (got2.float() - want).abs().max() <= tol * max(1.0, float(want.abs().max()))
+        gu = (torch.randn(M, 1, 2 * K, device="cuda") * 2).to(dtype)
+        want_g = f(_ext.silu_mul(gu)).float()
+        got_g = _ext.gemv_gated(gu, f.qweight, f.weight_scale, None, f.out_dtype, f.group_size, f.fmt).float()
+        assert (got_g - want_g).abs().max() <= tol * max(1.0, float(want_g.abs().max()))
+    assert _ext.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16))
 def test_argmax(dtype):
     from tfp8 import _ext
     torch.manual_seed(3)
