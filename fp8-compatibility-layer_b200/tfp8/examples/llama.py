@@ -175,6 +175,9 @@ class Block(nn.Module):
                 x = x + o
                 h = self.post_attention_layernorm(x)
         gu = self.gate_up_proj(h)
+        if comm is not None and B * T <= FUSE_ROWS_GATED and gu.dtype == x.dtype and self.down_proj.bias_f32 is None:
+            # this rank's partial of the down projection with SwiGLU computed inside the GEMV
+            return x, _Partial(_w8(self.down_proj.local, _ext.gemv_gated, gu.contiguous()))
         if fused and gu.dtype == x.dtype:
             act = _ext.silu_mul(gu.contiguous())
         else:
