@@ -188,13 +188,23 @@ __device__ __forceinline__ float row_scale_max(const void* scale, size_t row_off
 }
 
 // ------------------------------------------------------------------ the kernel
-template <int FMT>
+// OUT selects how a finished tile leaves the CTA; each form is a kernel of its own because the
+// uncommon ones, merely present as untaken branches, slowed the plain one by 4 - 17 % (longer
+// epilogue, different register allocation in the decode loop):
+//   GM_OUT_PLAIN   one output [M, N], whole K                       (every ordinary linear layer)
+//   GM_OUT_SPLITK  FP32 atomics into the workspace; units = (tile, K part)
+//   GM_OUT_WINDOW  1..8 outputs with a row pitch and a column offset, element-wise stores
+//   GM_OUT_PUSH    the same, peers served by the push warp from the local copy
+constexpr int GM_OUT_PLAIN = 0, GM_OUT_SPLITK = 1, GM_OUT_WINDOW = 2, GM_OUT_PUSH = 3;
+
+template <int FMT, int OUT>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment of the tile buffers is required by the swizzled layouts.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     GemmHeader* hd = reinterpret_cast<GemmHeader*>(smem);
+    if (threadIdx.x == 0) GM_TRACE(0, 250);
     uint8_t* stages = smem + GM_HEADER;                                   // [decoded tile 16 KB][activation tile]
     uint8_t* raw_ring = stages + static_cast<size_t>(p.ns) * p.stage_bytes;
 
@@ -207,9 +217,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     // fast index; within the tiles the activation-row tile is the fast index, so CTAs that run
     // together share one weight stripe through L2.
     auto unit_of = [&](int i) { return static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x); };
-    auto tile_m0 = [&](int i) { return ((unit_of(i) / p.ks) % p.m_tiles) * p.BN; };
-    auto tile_n0 = [&](int i) { return ((unit_of(i) / p.ks) / p.m_tiles) * GM_BM; };
-    auto unit_kb0 = [&](int i) { return (unit_of(i) % p.ks) * nkb; };              // first k-block of the unit
+    constexpr bool SPLIT = OUT == GM_OUT_SPLITK;
+    auto tile_of = [&](int i) { return SPLIT ? unit_of(i) / p.ks : unit_of(i); };
+    auto tile_m0 = [&](int i) { return (tile_of(i) % p.m_tiles) * p.BN; };
+    auto tile_n0 = [&](int i) { return (tile_of(i) / p.m_tiles) * GM_BM; };
+    auto unit_kb0 = [&](int i) { return SPLIT ? (unit_of(i) % p.ks) * nkb : 0; };  // first k-block of the unit
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.ns; ++s) {
@@ -237,6 +249,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    if (threadIdx.x == 0) GM_TRACE(0, 251);
     const uint32_t tmem_base = hd->tmem_base;
 
     if (warp == 0) {
@@ -536,7 +549,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     for (int h2 = 0; h2 < RPT; ++h2) rcur[j][h2] = rnext[j][h2];
             }
         }
-    } else if (warp == 3) {
+    } else if (OUT == GM_OUT_PUSH && warp == 3) {
         // ---------------------------------------------------------------- push warp (fused gather)
         // The accumulator is transposed (a warp owns 32 output columns), so an epilogue store is
         // 64 contiguous bytes: too small to keep NVLink busy, and the epilogue would stall the
@@ -544,7 +557,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         // warp copies each finished tile to the peers from there (L2-hot), 16 bytes per lane,
         // whole 256-byte tile rows per request, while the next tile's main loop runs. (Warp 3 is
         // the second MMA issuer of narrow tiles; they keep the element-wise peer stores.)
-        if (p.push) {
+        {
             const int esz = p.y_dt == TFP8B_F32 ? 4 : 2;
             const long long t0 = clock64();
             bool ok = true;
@@ -586,21 +599,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         // ---------------------------------------------------------------- epilogue warps
         const int quarter = warp & 3;                           // TMEM lanes this warp may read
         const int row = quarter * 32 + lane;
+        void* const y0 = p.y[0];
+        // 16-bit outputs with an even N and a 4-byte aligned base: lanes 2i and 2i+1 trade halves
+        // (the even lane keeps the even rows of both columns, the odd lane the odd rows) and
+        // store one word each -- half as many store instructions
+        const bool pair16 = OUT == GM_OUT_PLAIN && p.y_dt != TFP8B_F32 && (p.N & 1) == 0 && (reinterpret_cast<uintptr_t>(y0) & 3u) == 0;
+        const bool odd = lane & 1;
         bool ok = true;
         for (int i = 0; i < my_tiles; ++i) {
             const int buf = i & 1;
             const int m0 = tile_m0(i), n0 = tile_n0(i);
             const int n = n0 + row;
+            const bool live = n < p.N;
             const size_t off = static_cast<size_t>(min(n, p.N - 1)) * ng;
             const float sm = ng == 1 ? load_scale(p.scale, off, p.scale_kind) : row_scale_max(p.scale, off, 0, ng, p.scale_kind);
-            const float b = (p.bias && n < p.N) ? p.bias[n] : 0.f;
+            const float b = (p.bias && live) ? __ldg(p.bias + n) : 0.f;
+            // Activation-row scales: lane l holds the scale of row m0 + 32 k + l, one coalesced
+            // read-only load per 32 accumulator columns issued a step ahead (the first before the
+            // accumulator is waited for), handed out by shuffles. Loaded per column where they
+            // are used, every second group of 16 missed L1 and waited a full L2 round trip, and
+            // as ordinary loads next to stores through an untyped pointer they could not even
+            // be issued ahead of the store before them.
+            auto xs_of = [&](int k) {
+                const int m = m0 + 32 * k + lane;
+                return (OUT != GM_OUT_SPLITK && 32 * k < p.BN && m < p.M) ? __ldg(p.xs + m) : 0.f;
+            };
+            float xcur = 0.f, xnext = xs_of(0);
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->acc_full[buf]), (i >> 1) & 1, STATUS_GEMM_WAIT));
             if (!ok) continue;
             tc_fence_after();
+            if (threadIdx.x == GM_EPI_WARP0 * 32) GM_TRACE(0, 252);
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * p.nmma * p.BN);
             for (int col = 0; col < p.BN; col += 16) {
                 uint32_t v[16];
                 tmem_ld16(taddr + col, v);
+                if ((col & 16) == 0) { xcur = xnext; xnext = xs_of((col >> 5) + 1); }
                 tmem_ld_wait();
                 for (int a = 1; a < p.nmma; ++a) {               // the second issuer's accumulator
                     uint32_t u[16];
@@ -609,30 +642,75 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
                 }
-                if (n < p.N) {
+                const int mrows = min(16, p.M - (m0 + col));     // may be <= 0 in the last activation tile
+                float val[16];
+                if (OUT == GM_OUT_SPLITK) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) val[j] = __uint_as_float(v[j]) * sm;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        val[j] = fmaf(__uint_as_float(v[j]) * sm, __shfl_sync(0xffffffffu, xcur, (col & 16) + j), b);
+                }
+                if (OUT == GM_OUT_PLAIN) {
+                    const size_t at0 = static_cast<size_t>(m0 + col) * p.N + n;
+                    if (pair16) {
+                        uint16_t* yb = reinterpret_cast<uint16_t*>(y0) + at0 - (odd ? 1 : 0) + (odd ? p.N : 0);
+#pragma unroll
+                        for (int j = 0; j < 16; j += 2) {
+                            const float got = __shfl_xor_sync(0xffffffffu, odd ? val[j] : val[j + 1], 1);
+                            const float lo = odd ? got : val[j], hi = odd ? val[j + 1] : got;
+                            uint32_t w;
+                            if (p.y_dt == TFP8B_F16) { __half2 h = __floats2half2_rn(lo, hi); w = *reinterpret_cast<uint32_t*>(&h); }
+                            else { __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi); w = *reinterpret_cast<uint32_t*>(&h); }
+                            if (live && j + (odd ? 1 : 0) < mrows) *reinterpret_cast<uint32_t*>(yb + static_cast<size_t>(j) * p.N) = w;
+                        }
+                    } else if (live) {
+                        if (p.y_dt == TFP8B_F16) {
+                            __half* yp = reinterpret_cast<__half*>(y0) + at0;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) if (j < mrows) yp[static_cast<size_t>(j) * p.N] = __float2half_rn(val[j]);
+                        } else if (p.y_dt == TFP8B_BF16) {
+                            __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(y0) + at0;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) if (j < mrows) yp[static_cast<size_t>(j) * p.N] = __float2bfloat16_rn(val[j]);
+                        } else {
+                            float* yp = reinterpret_cast<float*>(y0) + at0;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) if (j < mrows) yp[static_cast<size_t>(j) * p.N] = val[j];
+                        }
+                    }
+                } else if (OUT == GM_OUT_SPLITK) {
+                    // this unit's share of the dot products, weight scale applied; the activation
+                    // scale and the bias follow once all parts are in
+                    float* w0 = p.ws + static_cast<size_t>(m0 + col) * p.N + n;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (live && j < mrows) atomicAdd(w0 + static_cast<size_t>(j) * p.N, val[j]);
+                } else {
+                    // a window of wider outputs: the local one only when the push warp serves the
+                    // peers, else every destination element by element
+                    const size_t at0 = static_cast<size_t>(m0 + col) * p.ldy + p.col0 + n;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const int m = m0 + col + j;
-                        if (m < p.M && p.ks > 1) {
-                            // split-K: this unit's share of the dot products, weight scale applied; the
-                            // activation scale and the bias follow once all parts are in
-                            atomicAdd(p.ws + static_cast<size_t>(m) * p.N + n, __uint_as_float(v[j]) * sm);
-                        } else if (m < p.M) {
-                            const float val = fmaf(__uint_as_float(v[j]) * sm, p.xs[m], b);
-                            const size_t at = static_cast<size_t>(m) * p.ldy + p.col0 + n;
-                            store_dt(p.y[0], at, val, p.y_dt);
-                            // fused gather without the push warp (unaligned windows): element-wise peer stores
-                            if (!p.push)
-                                for (int d = 1; d < p.ndst; ++d) store_dt(p.y[d], at, val, p.y_dt);
+                        if (!live || j >= mrows) break;
+                        const size_t at = at0 + static_cast<size_t>(j) * p.ldy;
+                        if (OUT == GM_OUT_PUSH) {
+                            store_dt(y0, at, val[j], p.y_dt);
+                        } else {
+#pragma unroll
+                            for (int d = 0; d < GM_MAX_DST; ++d)
+                                if (d < p.ndst) store_dt(p.y[d], at, val[j], p.y_dt);
                         }
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
+            if (threadIdx.x == GM_EPI_WARP0 * 32) GM_TRACE(0, 253);
             if (lane == 0) {
                 mbar_arrive(smem_u32(&hd->acc_empty[buf]));
-                if (p.push) { __threadfence_block(); atomicAdd(&hd->tiles_stored, 1u); }   // this warp's part of the tile is in the local output
+                if (OUT == GM_OUT_PUSH) { __threadfence_block(); atomicAdd(&hd->tiles_stored, 1u); }   // this warp's part of the tile is in the local output
             }
         }
     }
@@ -641,6 +719,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+        if (lane == 0) GM_TRACE(0, 255);
     }
 }
 
@@ -653,22 +732,37 @@ static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes,
     return encode_tensor_map(map, dt, 2, base, dims, strides, box, swz);
 }
 
-template <int FMT>
-static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, size_t smem, cudaStream_t st) {
-    static unsigned long long configured = 0ull;
-    int dev = 0, sms = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+// SM count of a device, asked once per device (the query sits on the launch path of 50 us kernels).
+static int device_sms(int dev) {
+    static int cached[64] = {};
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    if (dev >= 0 && dev < 64) cached[dev] = sms;
+    return sms;
+}
+
+template <int FMT, int OUT>
+static int launch_gemm_as(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, size_t smem, int dev, cudaStream_t st) {
+    static unsigned long long configured = 0ull;             // one per instantiation: bit d = device d is set up
     if (dev >= 64 || !((configured >> dev) & 1ull)) {
-        e = cudaFuncSetAttribute(gemm_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM_MAX);
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<FMT, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM_MAX);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm)");
         if (dev < 64) __atomic_fetch_or(&configured, 1ull << dev, __ATOMIC_RELAXED);
     }
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    const int sms = device_sms(dev);
     const int grid = p.ntiles < sms ? p.ntiles : sms;
-    gemm_kernel<FMT><<<grid, GM_THREADS, smem, st>>>(tw, tx, p);
+    gemm_kernel<FMT, OUT><<<grid, GM_THREADS, smem, st>>>(tw, tx, p);
     TFP8B_LAUNCH_CHECK("tfp8b_gemm");
     return TFP8B_OK;
+}
+
+template <int FMT>
+static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, size_t smem, int dev, cudaStream_t st) {
+    if (p.ks > 1) return launch_gemm_as<FMT, GM_OUT_SPLITK>(tw, tx, p, smem, dev, st);
+    if (p.push) return launch_gemm_as<FMT, GM_OUT_PUSH>(tw, tx, p, smem, dev, st);
+    if (p.ndst > 1 || p.ldy != p.N || p.col0 != 0) return launch_gemm_as<FMT, GM_OUT_WINDOW>(tw, tx, p, smem, dev, st);
+    return launch_gemm_as<FMT, GM_OUT_PLAIN>(tw, tx, p, smem, dev, st);
 }
 
 // ------------------------------------------------------------------ scratch for tfp8b_linear_static
@@ -785,12 +879,12 @@ static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, con
     // plus a fixed turn-over per unit; it splits only where that clearly pays (fewer tiles than
     // half the SMs and a long K).
     p.ks = 1; p.nkbu = nkb; p.ws = nullptr;
-    int sms = 148;
+    int dev = 0;
     {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     }
+    const int sms = device_sms(dev);
     static const int use_splitk = [] { const char* v = getenv("TFP8B_GEMM_SPLITK"); return !(v && v[0] == '0'); }();
     if (use_splitk && workspace && n_dst == 1 && p.m_tiles == 1 && workspace_floats >= static_cast<long long>(M) * N) {
         // measured on B200: a unit costs about 32 k-blocks of turn-over (scale scan, pipeline fill
@@ -847,7 +941,7 @@ static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, con
         cudaError_t e = cudaMemsetAsync(workspace, 0, static_cast<size_t>(M) * N * sizeof(float), st);
         if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(split-K workspace)");
     }
-    rc = fmt == TFP8B_E4M3FN ? launch_gemm<TFP8B_E4M3FN>(tw, tx, p, smem, st) : launch_gemm<TFP8B_E5M2>(tw, tx, p, smem, st);
+    rc = fmt == TFP8B_E4M3FN ? launch_gemm<TFP8B_E4M3FN>(tw, tx, p, smem, dev, st) : launch_gemm<TFP8B_E5M2>(tw, tx, p, smem, dev, st);
     if (rc != TFP8B_OK || p.ks == 1) return rc;
     // y = workspace * xs[m] + bias[n], rounded once to the output type
     return tfp8b_epilogue(workspace, xs, bias, y_dst[0], y_dtype, M, N, static_cast<int>(ldy), stream);
