@@ -600,11 +600,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         const int quarter = warp & 3;                           // TMEM lanes this warp may read
         const int row = quarter * 32 + lane;
         void* const y0 = p.y[0];
-        // 16-bit outputs with an even N and a 4-byte aligned base: lanes 2i and 2i+1 trade halves
-        // (the even lane keeps the even rows of both columns, the odd lane the odd rows) and
-        // store one word each -- half as many store instructions
-        const bool pair16 = OUT == GM_OUT_PLAIN && p.y_dt != TFP8B_F32 && (p.N & 1) == 0 && (reinterpret_cast<uintptr_t>(y0) & 3u) == 0;
-        const bool odd = lane & 1;
+        // 16-bit outputs whose rows are whole 16-byte chunks: the lanes transpose among themselves
+        // and store 8 columns at a time (else one element per store)
+        const bool wide16 = OUT == GM_OUT_PLAIN && p.y_dt != TFP8B_F32 && (p.N & 7) == 0 && (reinterpret_cast<uintptr_t>(y0) & 15u) == 0;
+        const bool b0 = lane & 1, b1 = lane & 2, b2 = lane & 4;
         bool ok = true;
         for (int i = 0; i < my_tiles; ++i) {
             const int buf = i & 1;
@@ -614,17 +613,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             const size_t off = static_cast<size_t>(min(n, p.N - 1)) * ng;
             const float sm = ng == 1 ? load_scale(p.scale, off, p.scale_kind) : row_scale_max(p.scale, off, 0, ng, p.scale_kind);
             const float b = (p.bias && live) ? __ldg(p.bias + n) : 0.f;
-            // Activation-row scales: lane l holds the scale of row m0 + 32 k + l, one coalesced
-            // read-only load per 32 accumulator columns issued a step ahead (the first before the
-            // accumulator is waited for), handed out by shuffles. Loaded per column where they
-            // are used, every second group of 16 missed L1 and waited a full L2 round trip, and
-            // as ordinary loads next to stores through an untyped pointer they could not even
-            // be issued ahead of the store before them.
-            auto xs_of = [&](int k) {
+            // Activation-row scales of the whole tile, fetched before the accumulator is waited
+            // for: register k of lane l holds the scale of row m0 + 32 k + l (coalesced read-only
+            // loads), handed out by shuffles. Every CTA of a wave asks for the same few lines at
+            // the same moment, so a load costs well over a thousand cycles here; fetched where
+            // they are used (and as ordinary loads, which may not pass the stores through the
+            // untyped output pointer) they made up most of the epilogue's time.
+            float xv[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
                 const int m = m0 + 32 * k + lane;
-                return (OUT != GM_OUT_SPLITK && 32 * k < p.BN && m < p.M) ? __ldg(p.xs + m) : 0.f;
-            };
-            float xcur = 0.f, xnext = xs_of(0);
+                xv[k] = (OUT != GM_OUT_SPLITK && 32 * k < p.BN && m < p.M) ? __ldg(p.xs + m) : 0.f;
+            }
+            float xcur = 0.f;
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->acc_full[buf]), (i >> 1) & 1, STATUS_GEMM_WAIT));
             if (!ok) continue;
             tc_fence_after();
@@ -633,7 +634,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             for (int col = 0; col < p.BN; col += 16) {
                 uint32_t v[16];
                 tmem_ld16(taddr + col, v);
-                if ((col & 16) == 0) { xcur = xnext; xnext = xs_of((col >> 5) + 1); }
+                if ((col & 16) == 0) {                           // register col / 32, selected without indexing
+                    const int k = col >> 5;
+                    const float a0 = (k & 1) ? xv[1] : xv[0], a1 = (k & 1) ? xv[3] : xv[2];
+                    const float a2 = (k & 1) ? xv[5] : xv[4], a3 = (k & 1) ? xv[7] : xv[6];
+                    const float b0 = (k & 2) ? a1 : a0, b1 = (k & 2) ? a3 : a2;
+                    xcur = (k & 4) ? b1 : b0;
+                }
                 tmem_ld_wait();
                 for (int a = 1; a < p.nmma; ++a) {               // the second issuer's accumulator
                     uint32_t u[16];
@@ -654,16 +661,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 }
                 if (OUT == GM_OUT_PLAIN) {
                     const size_t at0 = static_cast<size_t>(m0 + col) * p.N + n;
-                    if (pair16) {
-                        uint16_t* yb = reinterpret_cast<uint16_t*>(y0) + at0 - (odd ? 1 : 0) + (odd ? p.N : 0);
+                    if (wide16) {
+                        // Three exchange steps (lane distance 1, 2, 4) turn "16 rows of one
+                        // column per lane" into "2 rows of 8 consecutive columns per lane":
+                        // two 16-byte stores instead of sixteen 2-byte ones.
+                        uint32_t w1[8];                       // row 2t + b0: columns 2 (lane / 2) + {0, 1}
 #pragma unroll
-                        for (int j = 0; j < 16; j += 2) {
-                            const float got = __shfl_xor_sync(0xffffffffu, odd ? val[j] : val[j + 1], 1);
-                            const float lo = odd ? got : val[j], hi = odd ? val[j + 1] : got;
-                            uint32_t w;
-                            if (p.y_dt == TFP8B_F16) { __half2 h = __floats2half2_rn(lo, hi); w = *reinterpret_cast<uint32_t*>(&h); }
-                            else { __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi); w = *reinterpret_cast<uint32_t*>(&h); }
-                            if (live && j + (odd ? 1 : 0) < mrows) *reinterpret_cast<uint32_t*>(yb + static_cast<size_t>(j) * p.N) = w;
+                        for (int t = 0; t < 8; ++t) {
+                            const float got = __shfl_xor_sync(0xffffffffu, b0 ? val[2 * t] : val[2 * t + 1], 1);
+                            const float lo = b0 ? got : val[2 * t], hi = b0 ? val[2 * t + 1] : got;
+                            if (p.y_dt == TFP8B_F16) { __half2 h = __floats2half2_rn(lo, hi); w1[t] = *reinterpret_cast<uint32_t*>(&h); }
+                            else { __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi); w1[t] = *reinterpret_cast<uint32_t*>(&h); }
+                        }
+                        uint32_t w2[4][2];                    // row 4u + 2 b1 + b0: columns 4 (lane / 4) + {0..3}
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const uint32_t got = __shfl_xor_sync(0xffffffffu, b1 ? w1[2 * u] : w1[2 * u + 1], 2);
+                            const uint32_t mine = b1 ? w1[2 * u + 1] : w1[2 * u];
+                            w2[u][0] = b1 ? got : mine;
+                            w2[u][1] = b1 ? mine : got;
+                        }
+                        const int gcol = n0 + quarter * 32 + 8 * (lane >> 3);        // first of this lane's 8 columns
+                        uint16_t* yb = reinterpret_cast<uint16_t*>(y0) + static_cast<size_t>(m0 + col + (lane & 7)) * p.N + gcol;
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {         // row 8q + (lane & 7): columns 8 (lane / 8) + {0..7}
+                            const uint32_t g0 = __shfl_xor_sync(0xffffffffu, b2 ? w2[2 * q][0] : w2[2 * q + 1][0], 4);
+                            const uint32_t g1 = __shfl_xor_sync(0xffffffffu, b2 ? w2[2 * q][1] : w2[2 * q + 1][1], 4);
+                            const uint32_t k0 = b2 ? w2[2 * q + 1][0] : w2[2 * q][0], k1 = b2 ? w2[2 * q + 1][1] : w2[2 * q][1];
+                            const uint4 out = b2 ? make_uint4(g0, g1, k0, k1) : make_uint4(k0, k1, g0, g1);
+                            if (gcol < p.N && 8 * q + (lane & 7) < mrows)
+                                *reinterpret_cast<uint4*>(yb + static_cast<size_t>(8 * q) * p.N) = out;
                         }
                     } else if (live) {
                         if (p.y_dt == TFP8B_F16) {
