@@ -86,7 +86,9 @@ struct GemmHeader {
 static_assert(sizeof(GemmHeader) <= GM_HEADER, "header too large");
 
 // Build with -DTFP8B_GM_TRACE to record, for CTA 0, the SM clock at which each role passes each
-// k-block (a diagnostic for pipeline tuning; the array is read with cudaMemcpyFromSymbol).
+// k-block (a diagnostic for pipeline tuning; the array is read with cudaMemcpyFromSymbol). Row 0
+// also holds, at indices 250 - 255: kernel entry, end of set-up, first epilogue's start and end,
+// (unused), TMEM release.
 #ifdef TFP8B_GM_TRACE
 __device__ long long g_trace[8][256];
 #define GM_TRACE(ev, idx) do { if (blockIdx.x == 0 && (idx) < 256) g_trace[ev][idx] = clock64(); } while (0)
@@ -367,13 +369,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         const int group = td / GM_GROUP_THREADS;
         const int tg = td % GM_GROUP_THREADS;
         const int c = tg & 3;                        // 16-code chunk of the 64-wide K block
-        const int r0 = tg >> 2;                      // rows r0 + RSTEP * h
-        const uint32_t rpitch = p.rb == 2 ? 128u : 64u;
+        // Rows r0 + RSTEP * h. The 8 threads of a quarter-warp (one shared-memory wavefront of
+        // a 16-byte access) work on rows R and R ^ 5 of the warp's 8: the two rows differ in bit
+        // 0 and in bit 2 of the index, so that both the reads of the swizzled raw slot (chunks
+        // (4 half + c) ^ row: the halves differ through bit 2) and the stores into the swizzled
+        // decoded tile (chunks 2c ^ row: odd and even through bit 0) touch 8 different chunks.
+        const int rr = (tg >> 2) & 7;
+        const int r0 = (tg >> 5) * 8 + ((rr & 1) ? ((rr >> 1) ^ 5) : (rr >> 1));
         uint32_t roff[RPT], aoff0[RPT], aoff1[RPT];  // this thread's byte offsets inside a raw slot / a decoded tile
 #pragma unroll
         for (int h2 = 0; h2 < RPT; ++h2) {
             const uint32_t r = static_cast<uint32_t>(r0 + RSTEP * h2);
-            roff[h2] = r * rpitch + static_cast<uint32_t>(c) * 16u;
+            roff[h2] = p.rb == 2 ? r * 128u + ((static_cast<uint32_t>(c) ^ (r & 7u)) << 4) : r * 64u + static_cast<uint32_t>(c) * 16u;
             aoff0[h2] = r * 128u + (((2u * c) ^ (r & 7u)) << 4);
             aoff1[h2] = r * 128u + (((2u * c + 1u) ^ (r & 7u)) << 4);
         }
@@ -459,7 +466,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 #pragma unroll
                 for (int j = 0; j < PF; ++j) {
                     if (l0 + j >= nloc) break;
-                    const uint32_t st = stages_u32 + a_off, raw = raw_u32 + r_off + half_off;
+                    const uint32_t st = stages_u32 + a_off, raw = raw_u32 + r_off;
                     const uint32_t bar_full = full0 + a_bar, bar_empty = empty0 + a_bar;
                     const uint32_t bar_rfull = rfull0 + r_bar, bar_rempty = rempty0 + r_bar;
                     const uint32_t apar = a_par, rpar = r_par;
@@ -479,7 +486,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     {
                         uint4 q[RPT];
 #pragma unroll
-                        for (int h2 = 0; h2 < RPT; ++h2) q[h2] = gm_lds128(raw + roff[h2]);
+                        for (int h2 = 0; h2 < RPT; ++h2) q[h2] = gm_lds128(raw + (roff[h2] ^ half_off));   // the k-block's half: chunk bit 2
 #pragma unroll
                         for (int h2 = 0; h2 < RPT; ++h2) {
                             const uint32_t w[4] = {q[h2].x, q[h2].y, q[h2].z, q[h2].w};
@@ -954,7 +961,9 @@ static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, con
         const cuuint64_t wd[3] = {128, static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(K / 128)};
         const cuuint64_t ws[2] = {static_cast<cuuint64_t>(K), 128};
         const cuuint32_t wb[3] = {128, GM_BM, 1};
-        rc = encode_tensor_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, codes, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_NONE);
+        // 128-byte swizzle: the 16-byte chunk index of a row is XORed with (row & 7), which lets
+        // the decode warps read 8 rows' chunks without two of them sharing a bank
+        rc = encode_tensor_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, codes, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B);
     } else {
         rc = make_map_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, static_cast<uint64_t>(K), static_cast<uint64_t>(N),
                          GM_BK, GM_BM, CU_TENSOR_MAP_SWIZZLE_NONE);
