@@ -209,9 +209,9 @@ __global__ void __launch_bounds__(EW_THREADS) dequant_kernel(const uint8_t* __re
 
 // ------------------------------------------------------------------ one-pass weight quantizer
 // One CTA per weight row. Pass 1: per-group amax into shared memory (non-negative floats order
-// like their bit patterns, so an integer atomicMax does it). Pass 2 re-reads the row (now in
-// L1/L2 -- keeping it in shared memory instead measured slower), divides by the group scale and
-// encodes. 16 contiguous elements per thread per step.
+// like their bit patterns, so an integer atomicMax does it). Pass 2 divides by the group scale and
+// encodes; it takes the row from registers where it fits there, else re-reads it (from L1/L2 --
+// keeping it in shared memory instead measured slower). 16 contiguous elements per thread per step.
 __device__ __forceinline__ float scale_from_amax(float amax, float fmax, int pow2) {
     if (amax == 0.f) return 1.f;
     float s = fmaxf(__fdiv_rn(amax, fmax), FLT_MIN);
@@ -223,7 +223,10 @@ __device__ __forceinline__ float scale_from_amax(float amax, float fmax, int pow
     return s;
 }
 
-template <typename T, int FMT>
+// R > 0 (16-bit inputs, K <= R * 4096): the row stays in registers between the two passes -- all
+// of a thread's loads are issued before the first is used, and nothing is read twice. R == 0:
+// any K and fp32 inputs, pass 2 re-reads the row.
+template <typename T, int FMT, int R>
 __global__ void __launch_bounds__(EW_THREADS) quantize_kernel(const T* __restrict__ w, uint8_t* __restrict__ q,
                                                               void* __restrict__ scale, int scale_kind,
                                                               int K, int G, int pow2) {
@@ -232,15 +235,43 @@ __global__ void __launch_bounds__(EW_THREADS) quantize_kernel(const T* __restric
     const int ng = K / G;
     const float fmax = FMT == TFP8B_E4M3FN ? 448.f : 57344.f;
     const T* row = w + static_cast<size_t>(n) * K;
+    constexpr bool HOLD = R > 0 && sizeof(T) == 2;      // (an fp32 row is never held: twice the registers)
+    constexpr int RR = HOLD ? R : 1;
+    uint4 held[RR][2];
     for (int g = threadIdx.x; g < ng; g += blockDim.x) s_amax[g] = 0u;
-    __syncthreads();
-    for (int k = threadIdx.x * 16; k < K; k += blockDim.x * 16) {
-        float v[16];
-        load16<T>(row + k, v);
-        float m = 0.f;
+    if (HOLD) {
 #pragma unroll
-        for (int t = 0; t < 16; ++t) m = fmaxf(m, fabsf(v[t]));
-        atomicMax(&s_amax[k / G], __float_as_uint(m));
+        for (int i = 0; i < RR; ++i) {
+            const int k = (i * EW_THREADS + static_cast<int>(threadIdx.x)) * 16;
+            if (k < K) {
+                held[i][0] = __ldg(reinterpret_cast<const uint4*>(row + k));
+                held[i][1] = __ldg(reinterpret_cast<const uint4*>(row + k) + 1);
+            }
+        }
+    }
+    __syncthreads();
+    if (HOLD) {
+#pragma unroll
+        for (int i = 0; i < RR; ++i) {
+            const int k = (i * EW_THREADS + static_cast<int>(threadIdx.x)) * 16;
+            if (k < K) {
+                float v[16];
+                load16<T>(reinterpret_cast<const T*>(held[i]), v);
+                float m = 0.f;
+#pragma unroll
+                for (int t = 0; t < 16; ++t) m = fmaxf(m, fabsf(v[t]));
+                atomicMax(&s_amax[k / G], __float_as_uint(m));
+            }
+        }
+    } else {
+        for (int k = threadIdx.x * 16; k < K; k += blockDim.x * 16) {
+            float v[16];
+            load16<T>(row + k, v);
+            float m = 0.f;
+#pragma unroll
+            for (int t = 0; t < 16; ++t) m = fmaxf(m, fabsf(v[t]));
+            atomicMax(&s_amax[k / G], __float_as_uint(m));
+        }
     }
     __syncthreads();
     for (int g = threadIdx.x; g < ng; g += blockDim.x) {
@@ -251,12 +282,10 @@ __global__ void __launch_bounds__(EW_THREADS) quantize_kernel(const T* __restric
         else reinterpret_cast<float*>(scale)[si] = s;
     }
     __syncthreads();
-    for (int k = threadIdx.x * 16; k < K; k += blockDim.x * 16) {
+    // w / s, then clamp to +-fmax: the encoder's saturation is that clamp. Dividing by a power of
+    // two is multiplying by its reciprocal, exactly (the quotient's subnormal range included).
+    auto emit = [&](int k, float (&v)[16]) {
         const float s = __uint_as_float(s_amax[k / G]);
-        float v[16];
-        load16<T>(row + k, v);
-        // w / s, then clamp to +-fmax: the encoder's saturation is that clamp. Dividing by a power
-        // of two is multiplying by its reciprocal, exactly (the quotient's subnormal range included).
         const uint32_t sb = __float_as_uint(s);
         if ((sb & 0x007FFFFFu) == 0u && sb >= 0x00800000u && sb <= 0x7E800000u) {
             const float inv = __uint_as_float(0x7F000000u - sb);
@@ -267,6 +296,23 @@ __global__ void __launch_bounds__(EW_THREADS) quantize_kernel(const T* __restric
             for (int t = 0; t < 16; ++t) v[t] = __fdiv_rn(v[t], s);
         }
         *reinterpret_cast<uint4*>(q + static_cast<size_t>(n) * K + k) = encode16<FMT>(v, TFP8B_NAN_CAST);
+    };
+    if (HOLD) {
+#pragma unroll
+        for (int i = 0; i < RR; ++i) {
+            const int k = (i * EW_THREADS + static_cast<int>(threadIdx.x)) * 16;
+            if (k < K) {
+                float v[16];
+                load16<T>(reinterpret_cast<const T*>(held[i]), v);
+                emit(k, v);
+            }
+        }
+    } else {
+        for (int k = threadIdx.x * 16; k < K; k += blockDim.x * 16) {
+            float v[16];
+            load16<T>(row + k, v);
+            emit(k, v);
+        }
     }
 }
 
@@ -436,9 +482,20 @@ extern "C" int tfp8b_quantize(const void* w, int w_dtype, uint8_t* codes, void* 
     const size_t smem = static_cast<size_t>(K / G) * sizeof(uint32_t);
     TFP8B_REQUIRE(smem <= 48 * 1024, TFP8B_ERR_UNSUPPORTED, "tfp8b_quantize: more than 12288 groups per row");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define CALL(T, F) quantize_kernel<T, F><<<N, EW_THREADS, smem, st>>>(static_cast<const T*>(w), codes, scale, scale_kind, K, G, pow2)
+    // rows of 16-bit values up to 16384 long are held in registers between the passes
+    const int steps = (K + EW_THREADS * 16 - 1) / (EW_THREADS * 16);
+    const int held = (w_dtype != TFP8B_F32 && steps <= 4) ? (steps <= 1 ? 1 : steps <= 2 ? 2 : 4) : 0;
+#define CALL_R(T, F, R) quantize_kernel<T, F, R><<<N, EW_THREADS, smem, st>>>(static_cast<const T*>(w), codes, scale, scale_kind, K, G, pow2)
+#define CALL(T, F)                                                      \
+    do {                                                                \
+        if (held == 1) CALL_R(T, F, 1);                                 \
+        else if (held == 2) CALL_R(T, F, 2);                            \
+        else if (held == 4) CALL_R(T, F, 4);                            \
+        else CALL_R(T, F, 0);                                           \
+    } while (0)
     DISPATCH_DT_FMT(w_dtype, fmt, CALL);
 #undef CALL
+#undef CALL_R
     TFP8B_LAUNCH_CHECK("tfp8b_quantize");
     return TFP8B_OK;
 }
