@@ -212,6 +212,8 @@ __global__ void __launch_bounds__(EW_THREADS) dequant_kernel(const uint8_t* __re
 // like their bit patterns, so an integer atomicMax does it). Pass 2 divides by the group scale and
 // encodes; it takes the row from registers where it fits there, else re-reads it (from L1/L2 --
 // keeping it in shared memory instead measured slower). 16 contiguous elements per thread per step.
+// (Reducing the amax among the lanes of a group by shuffles before the atomic was measured too:
+// 12 - 20 % slower than letting all lanes hit the shared-memory word.)
 __device__ __forceinline__ float scale_from_amax(float amax, float fmax, int pow2) {
     if (amax == 0.f) return 1.f;
     float s = fmaxf(__fdiv_rn(amax, fmax), FLT_MIN);
