@@ -306,10 +306,18 @@ def run_ours(args, rank, world, local_rank):
         line["extra"] = extra_measurements(args, device, peaks, world) if world == 1 else {}
         del layers, launches, xs, outs, hx, hy, dx
         torch.cuda.empty_cache()
+        # the extras must never cost the headline line: an error that every rank meets alike
+        # (a shape the tensor-parallel size does not divide, no peer memory) is recorded instead
         if world > 1:
-            line["extra"]["tp_gemm"] = tp_gemm_measurements(device, peaks, world, rank)
+            try:
+                line["extra"]["tp_gemm"] = tp_gemm_measurements(device, peaks, world, rank)
+            except Exception as e:
+                line["extra"]["tp_gemm"] = {"error": f"{type(e).__name__}: {e}"[:300]}
         if not args.no_llama:
-            line["extra"]["llama_decode"] = llama_decode_measurements(device, peaks, world)
+            try:
+                line["extra"]["llama_decode"] = llama_decode_measurements(device, peaks, world)
+            except Exception as e:
+                line["extra"]["llama_decode"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     if rank == 0 and world == 1:
         line["cpu_baseline"] = cpu_baseline(args.cpu_seconds)
     return line
