@@ -73,8 +73,10 @@ extern "C" int tfp8b_device_status(unsigned int* out_status, tfp8b_stream_t stre
     if (rc != TFP8B_OK) return rc;
     if (out_status) *out_status = v;
     if (v) {
-        set_error("a kernel gave up on a bounded wait (status 0x%x: %s%s%s)", v, (v & STATUS_GEMV_WAIT) ? "gemv " : "",
-                  (v & STATUS_GEMM_WAIT) ? "gemm " : "", (v & STATUS_GLUE_WAIT) ? "all-reduce" : "");
+        set_error("a kernel reported a problem (status 0x%x:%s%s%s%s)", v, (v & STATUS_GEMV_WAIT) ? " gemv wait ran out;" : "",
+                  (v & STATUS_GEMM_WAIT) ? " gemm wait ran out;" : "",
+                  (v & STATUS_GLUE_WAIT) ? " all-reduce: a peer never answered, the rows were set to NaN;" : "",
+                  (v & STATUS_GLUE_POS) ? " rope_kv_store: a position outside the KV cache was skipped;" : "");
         return TFP8B_ERR_DEVICE;
     }
     return TFP8B_OK;

@@ -33,7 +33,7 @@ int cuda_fail(cudaError_t e, const char* what);
 // device code): kernels OR a bit in when a bounded wait runs out; each .cu file that has such
 // waits exports a reader that tfp8b_device_status() combines.
 static __device__ unsigned int g_status;
-constexpr unsigned STATUS_GEMV_WAIT = 1u, STATUS_GEMM_WAIT = 2u, STATUS_GLUE_WAIT = 4u;
+constexpr unsigned STATUS_GEMV_WAIT = 1u, STATUS_GEMM_WAIT = 2u, STATUS_GLUE_WAIT = 4u, STATUS_GLUE_POS = 8u;
 int read_and_clear_status(unsigned int* word_on_device, unsigned int* out, cudaStream_t st);
 
 // Host: fills a tiled tensor map (cuTensorMapEncodeTiled, fetched from the driver at first use).
@@ -303,6 +303,11 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
         "[%0], [%1, {%2, %3, %4}], [%5], %6;"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar), "l"(policy) : "memory");
+}
+// 3-D tiled prefetch of the same box into L2 only (no shared-memory destination, no barrier).
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 // Programmatic dependent launch: let the next kernel in the stream start its prologue now /
 // wait until everything the previous kernel wrote is visible.

@@ -48,6 +48,13 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const T* __restrict__ qkv,
         const int t = static_cast<int>((idx / (static_cast<long long>(pairs) * heads)) % Tn);
         const int b = static_cast<int>(idx / (static_cast<long long>(pairs) * heads * Tn));
         const long long p = pos[t];
+        // A position outside the cache would index the cos / sin tables and the caches out of
+        // bounds: such a token is skipped (nothing read at p, nothing stored) and reported in the
+        // device status word, since the position is a device value the host never sees.
+        if (p < 0 || p >= max_seq) {
+            if (ip == 0 && h == 0) atomicOr(&g_status, STATUS_GLUE_POS);
+            continue;
+        }
         const T* src = qkv + ((static_cast<size_t>(b) * Tn + t) * heads + h) * hd;
         const float2 x1 = unpack2(*reinterpret_cast<const P*>(src + 2 * ip));
         const float2 x2 = unpack2(*reinterpret_cast<const P*>(src + half + 2 * ip));
@@ -196,6 +203,7 @@ struct ArParams {
     unsigned int* flag[8];     // flag[r]: rank r's flags [2][world][max_rows]
     unsigned int* state;       // local: {sequence number of the last finished call, CTAs done in the running call}
     int rank, world, max_rows;
+    long long wait_cycles;     // SM clock cycles a CTA waits for a peer's flag before it gives up
 };
 constexpr int AR_THREADS = 256;
 template <typename T>
@@ -211,6 +219,8 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_add_rmsnorm_kernel(T* __
     const size_t buf_off = static_cast<size_t>(seq & 1u) * ar.world * slot_elems;
     const size_t flag_off = static_cast<size_t>(seq & 1u) * ar.world * ar.max_rows;
     const float* mine = part + static_cast<size_t>(row) * dim;
+    __shared__ int s_gave_up;
+    if (threadIdx.x == 0) s_gave_up = 0;
     // 1. push
     for (int v = threadIdx.x; v < nvec; v += AR_THREADS) {
         const float4 a = reinterpret_cast<const float4*>(mine)[v];
@@ -230,11 +240,16 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_add_rmsnorm_kernel(T* __
         for (;;) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(g) : "memory");
             if (got == seq) break;
-            if (clock64() - t0 > (1ll << 32)) { atomicOr(&g_status, STATUS_GLUE_WAIT); break; }   // about two seconds
+            if (clock64() - t0 > ar.wait_cycles) { atomicOr(&g_status, STATUS_GLUE_WAIT); s_gave_up = 1; break; }
             __nanosleep(100);
         }
     }
     __syncthreads();
+    // A peer that never answered: its slot holds stale data, so a sum would be silently wrong while
+    // the peer (which did receive this rank's partial) computes the right one. The row is poisoned
+    // instead -- NaN in the residual and in the output -- so the failure shows in every later token,
+    // and the status word says why.
+    const bool gave_up = s_gave_up != 0;
     // 3. sum in rank order, residual, norm (rows of up to 4 * AR_THREADS * AR_KEEP floats stay in registers)
     constexpr int AR_KEEP = 4;
     float4 keep[AR_KEEP];
@@ -251,6 +266,7 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_add_rmsnorm_kernel(T* __
                                               : __ldcg(reinterpret_cast<const float4*>(local + r * slot_elems) + v);
                 t.x += a.x; t.y += a.y; t.z += a.z; t.w += a.w;
             }
+            if (gave_up) t.x = t.y = t.z = t.w = __int_as_float(0x7FC00000);
             const uint2 xr = *reinterpret_cast<const uint2*>(x + xrow + v * 4);
             const P* xp = reinterpret_cast<const P*>(&xr);
             // the reduced projection output is rounded to the activation type, then added (as the
@@ -569,6 +585,9 @@ int glue_status(unsigned int* out, cudaStream_t st) {
     return read_and_clear_status(word, out, st);
 }
 
+// Wait limit of the fused all-reduce, in SM clock cycles (about two seconds by default).
+static long long g_ar_wait_cycles = 1ll << 32;
+
 static int grid_of(long long work) {
     long long blocks = (work + 255) / 256;
     return static_cast<int>(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
@@ -684,6 +703,7 @@ extern "C" int tfp8b_allreduce_add_rmsnorm(void* x, const float* partial, const 
         if (r < world) TFP8B_REQUIRE(ar.recv[r] && ar.flag[r], TFP8B_ERR_INVALID, "tfp8b_allreduce_add_rmsnorm: null peer pointer %d", r);
     }
     ar.state = state; ar.rank = rank; ar.world = world; ar.max_rows = max_rows;
+    ar.wait_cycles = __atomic_load_n(&g_ar_wait_cycles, __ATOMIC_RELAXED);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == TFP8B_F16)
         return launch_pdl("tfp8b_allreduce_add_rmsnorm", allreduce_add_rmsnorm_kernel<__half>, rows, AR_THREADS, st,
@@ -691,6 +711,12 @@ extern "C" int tfp8b_allreduce_add_rmsnorm(void* x, const float* partial, const 
     return launch_pdl("tfp8b_allreduce_add_rmsnorm", allreduce_add_rmsnorm_kernel<__nv_bfloat16>, rows, AR_THREADS, st,
                       static_cast<__nv_bfloat16*>(x), partial, static_cast<const __nv_bfloat16*>(weight),
                       static_cast<__nv_bfloat16*>(out), dim, eps, ar);
+}
+
+extern "C" long long tfp8b_allreduce_wait_limit(long long cycles) {
+    const long long old = __atomic_load_n(&g_ar_wait_cycles, __ATOMIC_RELAXED);
+    if (cycles > 0) __atomic_store_n(&g_ar_wait_cycles, cycles, __ATOMIC_RELAXED);
+    return old;
 }
 
 extern "C" int tfp8b_argmax(const void* logits, int dtype, long long* out, long long rows, long long n, long long row_pitch,

@@ -55,6 +55,7 @@ constexpr int GV_SMEM_TARGET = TFP8B_GV_SMEM_KB * 1024;       // per CTA: two CT
 constexpr int GV_SMEM_LARGE = 200 * 1024;        // ... unless the activations need the room (M > 1 with a long K)
 constexpr int GV_XRES_SMALL = 40 * 1024;         // resident activations up to this size keep the small footprint
 constexpr int GV_XRES_MAX = 96 * 1024;           // activations up to this size stay resident per CTA
+constexpr int GV_L2PF_DEFAULT = 6;               // stages prefetched into L2 ahead of the ring by a call that waits for its predecessor
 
 struct GemvParams {
     const void* x;
@@ -64,6 +65,7 @@ struct GemvParams {
     void* y;
     int M, N, K, G, scale_kind, y_dt;
     int nstages, wpitch, xpitch, wstage_bytes, stage_bytes, x_resident, xres_bytes, ntiles, pdl;
+    int l2pf;          // stages of the weight stream pulled into L2 ahead of the shared-memory ring (tensor-map layout)
     // Activations computed by the kernel itself instead of copied (16-bit types, resident rows):
     //   xmode 1  x = RMSNorm(xa + xb) * xw: the residual update (xb may be null) and the norm of a
     //            decoder block; the CTA with index 0 also stores the updated residual to xout
@@ -382,11 +384,31 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             }
         };
 
+        // L2 prefetch cursor: runs l2pf stages ahead of the stage being issued into the ring. The
+        // ring alone (what fits beside a second resident CTA) holds too few bytes to cover the HBM
+        // latency after a wait; the prefetched stages are already on their way, or in L2, when
+        // the ring asks for them. While the kernel sits at griddepcontrol.wait behind its
+        // predecessor this is what keeps its weight stream moving.
+        int tp = 0, cp = 0, ip = 0;
+        auto prefetch_to = [&](int upto) {               // prefetch stages [ip, min(upto, total))
+            if constexpr (TMA) {
+                if (p.l2pf <= 0) return;
+                for (; ip < upto && ip < total; ++ip) {
+                    const int n0 = (static_cast<int>(blockIdx.x) + tp * static_cast<int>(gridDim.x)) * GV_ROWS;
+                    if (lane == 0) tma_prefetch_l2_3d(&tm_w, 0, n0, (cp * GV_KS) >> 7);
+                    if (++cp == nchunks) { cp = 0; ++tp; }
+                }
+            }
+        };
         const int pre = min(S, total);
         int t = 0, c = 0;
         for (int i = 0; i < pre; ++i) {                  // weights first: they never depend on the predecessor
             issue_w(t, c, i);
             if (++c == nchunks) { c = 0; ++t; }
+        }
+        if (TMA && p.l2pf > 0) {                         // the ring's own stages need no prefetch
+            for (; ip < pre; ++ip) if (++cp == nchunks) { cp = 0; ++tp; }
+            prefetch_to(pre + p.l2pf);
         }
         if (p.pdl == 1) pdl_wait();                      // activations may be the predecessor's output
         if (p.x_resident && !XF) {
@@ -410,6 +432,7 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         for (int i = pre; i < total; ++i) {
             if (!mbar_wait(bar_empty + 8 * slot, phase, STATUS_GEMV_WAIT)) break;
             issue_w(t, c, slot);
+            prefetch_to(i + 1 + p.l2pf);
             if (!p.x_resident) issue_x(c, slot);
             if (++c == nchunks) { c = 0; ++t; }
             if (++slot == S) { slot = 0; phase ^= 1u; }
@@ -563,10 +586,15 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     }
 }
 
+// SM count of the current device, asked once per device (the query sits on the launch path of
+// kernels that take a few microseconds).
 static int sm_count_of_current_device() {
+    static int cached[64] = {};
     int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-        n = 148;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    if (dev >= 0 && dev < 64) cached[dev] = n;
     return n;
 }
 
@@ -673,76 +701,84 @@ extern "C" int tfp8b_gemv_gated(const void* gate_up, int x_dtype, const uint8_t*
                      nullptr, 0.f, stream);
 }
 
-static int gemv_impl(const void* x, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind, const float* bias,
-                     void* y, int y_dtype, int M, int N, int K, int G, int fmt, unsigned int flags, int xmode, const void* xa,
-                     const void* xb, const void* xw, void* xout, float xeps, tfp8b_stream_t stream) {
+// Everything of a launch that does not depend on the addresses of x and y: shape checks, the
+// shared-memory plan, the kernel variant, the tensor map of the weight stream.
+struct GemvSetup {
+    GemvParams p;
+    CUtensorMap tw;
+    size_t smem;
+    int fmt, smode, x_dtype;
+    bool tma;
+};
+
+static int gemv_weight_map(CUtensorMap* tw, const uint8_t* codes, int N, int K) {
+    // weights: [k-block][row][128 B]; dim 1 (rows) strides by K, dim 2 (k-blocks) by 128 bytes
+    const cuuint64_t wd[3] = {128, static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(K / 128)};
+    const cuuint64_t ws[2] = {static_cast<cuuint64_t>(K), 128};
+    const cuuint32_t wb[3] = {128, GV_ROWS, GV_KS / 128};
+    return encode_tensor_map(tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, codes, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+static int gemv_x_map(CUtensorMap* tx, const void* x, int x_dtype, int M, int K) {
+    const int xsz = dtype_size(x_dtype), epb = 128 / xsz;      // activations per 128-byte k-block
+    const cuuint64_t xd[3] = {static_cast<cuuint64_t>(epb), static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(K / epb)};
+    const cuuint64_t xs[2] = {static_cast<cuuint64_t>(K) * xsz, 128};
+    const cuuint32_t xb[3] = {static_cast<cuuint32_t>(epb), static_cast<cuuint32_t>(M), static_cast<cuuint32_t>(GV_KS / epb)};
+    const CUtensorMapDataType xt = x_dtype == TFP8B_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                 : x_dtype == TFP8B_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    return encode_tensor_map(tx, xt, 3, x, xd, xs, xb, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+static int gemv_setup(GemvSetup& g, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind, const float* bias,
+                      int y_dtype, int M, int N, int K, int G, int fmt, int xmode, bool with_weight_map) {
     TFP8B_REQUIRE(M >= 0 && N >= 0 && K > 0 && G > 0, TFP8B_ERR_INVALID, "tfp8b_gemv: bad size M=%d N=%d K=%d G=%d", M, N, K, G);
     TFP8B_REQUIRE(x_dtype >= 0 && x_dtype <= 2 && y_dtype >= 0 && y_dtype <= 2, TFP8B_ERR_INVALID, "tfp8b_gemv: bad dtype");
     TFP8B_REQUIRE(fmt == TFP8B_E4M3FN || fmt == TFP8B_E5M2, TFP8B_ERR_INVALID, "tfp8b_gemv: bad fmt %d", fmt);
     TFP8B_REQUIRE(scale_kind == TFP8B_SCALE_F32 || scale_kind == TFP8B_SCALE_UE8M0, TFP8B_ERR_INVALID,
                   "tfp8b_gemv: bad scale_kind %d", scale_kind);
     TFP8B_REQUIRE(M <= 8, TFP8B_ERR_UNSUPPORTED, "tfp8b_gemv: M=%d > 8, use tfp8b_gemm", M);
+    g.p = GemvParams{};
+    g.fmt = fmt; g.x_dtype = x_dtype; g.smem = 0; g.smode = 0; g.tma = false;
     if (M == 0 || N == 0) return TFP8B_OK;
-    TFP8B_REQUIRE(x && codes && scale && y, TFP8B_ERR_INVALID, "tfp8b_gemv: null pointer");
+    TFP8B_REQUIRE(codes && scale, TFP8B_ERR_INVALID, "tfp8b_gemv: null pointer");
     TFP8B_REQUIRE(K % 32 == 0 && G % 32 == 0 && K % G == 0, TFP8B_ERR_UNSUPPORTED,
                   "tfp8b_gemv: need K %% 32 == 0, G %% 32 == 0, K %% G == 0 (K=%d G=%d)", K, G);
-    TFP8B_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(codes)) & 15u) == 0, TFP8B_ERR_INVALID,
-                  "tfp8b_gemv: x and codes must be 16-byte aligned");
+    TFP8B_REQUIRE((reinterpret_cast<uintptr_t>(codes) & 15u) == 0, TFP8B_ERR_INVALID, "tfp8b_gemv: codes must be 16-byte aligned");
     const int smode = G == K ? 0 : (G % 64 == 0 ? 1 : 2);
     const int xsz = dtype_size(x_dtype);
-    GemvParams p = {};
-    p.x = x; p.w = codes; p.scale = scale; p.bias = bias; p.y = y;
+    GemvParams& p = g.p;
+    p.w = codes; p.scale = scale; p.bias = bias;
     p.M = M; p.N = N; p.K = K; p.G = G; p.scale_kind = scale_kind; p.y_dt = y_dtype;
     p.ntiles = (N + GV_ROWS - 1) / GV_ROWS;
-    p.xmode = xmode; p.xa = xa; p.xb = xb; p.xw = xw; p.xout = xout; p.xeps = xeps;
-    // TFP8B_NO_PDL=1 turns programmatic dependent launch off (profilers serialise kernels anyway);
+    p.xmode = xmode;
     // TFP8B_GEMV_BULK=1 forces the bulk-copy layout.
-    static const int no_pdl = [] { const char* v = getenv("TFP8B_NO_PDL"); return v && v[0] == '1'; }();
     static const int force_bulk = [] { const char* v = getenv("TFP8B_GEMV_BULK"); return v && v[0] == '1'; }();
-    // pdl: 0 = plain launch; 1 = early launch, wait for the predecessor before touching x / y;
-    //      2 = early launch, caller vouches that x / y are independent of the predecessor: the wait
-    //          moves to the very end (so that this grid never completes before its predecessor and
-    //          later work in the stream still sees both finished).
-    p.pdl = no_pdl ? 0 : ((flags & TFP8B_GEMV_INDEPENDENT_IO) ? 2 : 1);
     // The tensor map describes K in whole 128-byte k-blocks: a K that is not a multiple of 128
     // would make its last k-block read past the row (and, on the last row, past the buffer).
     const bool tma = K % 128 == 0 && !force_bulk;
     const int nchunks = (K + GV_KS - 1) / GV_KS;
-    CUtensorMap tw = {}, tx = {};
+    const int xpad = smode == 2 ? 64 : 16;
     if (tma) {
-        const int epb = 128 / xsz;                         // activations per 128-byte k-block
         p.wstage_bytes = GV_ROWS * GV_KS;
-        const int xpad = smode == 2 ? 64 : 16;
         p.x_resident = (M * (K * xsz + xpad) <= GV_XRES_MAX) ? 1 : 0;
         p.xpitch = K * xsz + xpad;                                      // resident rows only
         p.xres_bytes = p.x_resident ? ((M * p.xpitch + 1023) & ~1023) : 0;
-        const int nkb_x = K / epb;
         const int xstage = p.x_resident ? 0 : M * GV_KS * xsz;          // a multiple of 1024
         p.stage_bytes = p.wstage_bytes + xstage;
-        // weights: [k-block][row][128 B]; dim 1 (rows) strides by K, dim 2 (k-blocks) by 128 bytes
-        const cuuint64_t wd[3] = {128, static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(K / 128)};
-        const cuuint64_t ws[2] = {static_cast<cuuint64_t>(K), 128};
-        const cuuint32_t wb[3] = {128, GV_ROWS, GV_KS / 128};
-        int rc = encode_tensor_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, codes, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (rc != TFP8B_OK) return rc;
-        const cuuint64_t xd[3] = {static_cast<cuuint64_t>(epb), static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(nkb_x)};
-        const cuuint64_t xs[2] = {static_cast<cuuint64_t>(K) * xsz, 128};
-        const cuuint32_t xb[3] = {static_cast<cuuint32_t>(epb), static_cast<cuuint32_t>(M),
-                                  static_cast<cuuint32_t>(GV_KS / epb)};
-        const CUtensorMapDataType xt = x_dtype == TFP8B_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                                     : x_dtype == TFP8B_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-        rc = encode_tensor_map(&tx, xt, 3, x, xd, xs, xb, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (rc != TFP8B_OK) return rc;
+        if (with_weight_map) {
+            const int rc = gemv_weight_map(&g.tw, codes, N, K);
+            if (rc != TFP8B_OK) return rc;
+        }
     } else {
         // Row pitches that keep the 128-bit (64-code blocks) or 64-bit (32-code blocks) shared
         // loads of a quarter / half warp on distinct banks.
-        const int xpad = smode == 2 ? 64 : 16;
         p.wpitch = GV_KS + (smode == 2 ? 32 : 64);
         p.wstage_bytes = GV_ROWS * p.wpitch;
         p.x_resident = (M * (K * xsz + xpad) <= GV_XRES_MAX) ? 1 : 0;
         p.xpitch = (p.x_resident ? K : GV_KS) * xsz + xpad;
         p.xres_bytes = p.x_resident ? ((M * p.xpitch + 1023) & ~1023) : 0;
         p.stage_bytes = (p.wstage_bytes + (p.x_resident ? 0 : M * p.xpitch) + 127) & ~127;
+        if (with_weight_map) g.tw = CUtensorMap{};
     }
     TFP8B_REQUIRE(xmode == 0 || (p.x_resident && tma), TFP8B_ERR_UNSUPPORTED,
                   "tfp8b_gemv: computed activations need K %% 128 == 0 and M * K small enough to stay resident (M=%d K=%d)", M, K);
@@ -753,9 +789,86 @@ static int gemv_impl(const void* x, int x_dtype, const uint8_t* codes, const voi
     const int max_items = ((p.ntiles + sms - 1) / sms) * nchunks;     // stages the busiest CTA moves
     if (S > max_items) S = max_items;
     p.nstages = S;
-    const size_t smem = 1024 + GV_HEADER + p.xres_bytes + static_cast<size_t>(S) * p.stage_bytes;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (x_dtype == TFP8B_F16) return dispatch_gemv<__half>(tw, tx, p, fmt, smode, tma, smem, st);
-    if (x_dtype == TFP8B_BF16) return dispatch_gemv<__nv_bfloat16>(tw, tx, p, fmt, smode, tma, smem, st);
-    return dispatch_gemv<float>(tw, tx, p, fmt, smode, tma, smem, st);
+    g.smem = 1024 + GV_HEADER + p.xres_bytes + static_cast<size_t>(S) * p.stage_bytes;
+    g.smode = smode; g.tma = tma;
+    return TFP8B_OK;
 }
+
+// pdl: 0 = plain launch; 1 = early launch, wait for the predecessor before touching x / y;
+//      2 = early launch, caller vouches that x / y are independent of the predecessor: the wait
+//          moves to the very end (so that this grid never completes before its predecessor and
+//          later work in the stream still sees both finished).
+// TFP8B_NO_PDL=1 in the environment turns programmatic dependent launch off everywhere
+// (profilers serialise kernels anyway).
+static int pdl_mode_of(unsigned int flags) {
+    static const int no_pdl = [] { const char* v = getenv("TFP8B_NO_PDL"); return v && v[0] == '1'; }();
+    if (no_pdl || (flags & TFP8B_GEMV_NO_PDL)) return 0;
+    return (flags & TFP8B_GEMV_INDEPENDENT_IO) ? 2 : 1;
+}
+
+static int gemv_run(const GemvSetup& g, const void* x, void* y, unsigned int flags, const void* xa, const void* xb,
+                    const void* xw, void* xout, float xeps, tfp8b_stream_t stream) {
+    if (g.p.M == 0 || g.p.N == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(x && y, TFP8B_ERR_INVALID, "tfp8b_gemv: null pointer");
+    TFP8B_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15u) == 0, TFP8B_ERR_INVALID, "tfp8b_gemv: x must be 16-byte aligned");
+    GemvParams p = g.p;
+    p.x = x; p.y = y; p.xa = xa; p.xb = xb; p.xw = xw; p.xout = xout; p.xeps = xeps;
+    p.pdl = pdl_mode_of(flags);
+    // TFP8B_GEMV_L2PF=<stages> overrides how far the L2 prefetch runs ahead (0 = off). By default
+    // only calls that wait for their predecessor prefetch: an independent call streams at once.
+    static const int l2pf_env = [] { const char* v = getenv("TFP8B_GEMV_L2PF"); return v ? atoi(v) : -1; }();
+    p.l2pf = !g.tma ? 0 : (l2pf_env >= 0 ? l2pf_env : (p.pdl == 1 ? GV_L2PF_DEFAULT : 0));
+    CUtensorMap tx = {};
+    if (g.tma && !p.x_resident) {                 // activations that travel with the stages: their own tensor map
+        const int rc = gemv_x_map(&tx, x, g.x_dtype, p.M, p.K);
+        if (rc != TFP8B_OK) return rc;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (g.x_dtype == TFP8B_F16) return dispatch_gemv<__half>(g.tw, tx, p, g.fmt, g.smode, g.tma, g.smem, st);
+    if (g.x_dtype == TFP8B_BF16) return dispatch_gemv<__nv_bfloat16>(g.tw, tx, p, g.fmt, g.smode, g.tma, g.smem, st);
+    return dispatch_gemv<float>(g.tw, tx, p, g.fmt, g.smode, g.tma, g.smem, st);
+}
+
+static int gemv_impl(const void* x, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind, const float* bias,
+                     void* y, int y_dtype, int M, int N, int K, int G, int fmt, unsigned int flags, int xmode, const void* xa,
+                     const void* xb, const void* xw, void* xout, float xeps, tfp8b_stream_t stream) {
+    GemvSetup g;
+    const int rc = gemv_setup(g, x_dtype, codes, scale, scale_kind, bias, y_dtype, M, N, K, G, fmt, xmode, true);
+    if (rc != TFP8B_OK) return rc;
+    return gemv_run(g, x, y, flags, xa, xb, xw, xout, xeps, stream);
+}
+
+// ------------------------------------------------------------------ prepared launches
+struct tfp8b_gemv_plan {
+    int max_M, device;
+    GemvSetup by_m[9];          // by_m[M] for 1 <= M <= max_M (the weight tensor map is the same in all)
+};
+
+extern "C" int tfp8b_gemv_plan_create(tfp8b_gemv_plan** plan, int x_dtype, const uint8_t* codes, const void* scale,
+                                      int scale_kind, const float* bias, int y_dtype, int max_M, int N, int K, int G, int fmt) {
+    TFP8B_REQUIRE(plan, TFP8B_ERR_INVALID, "tfp8b_gemv_plan_create: null plan pointer");
+    *plan = nullptr;
+    TFP8B_REQUIRE(max_M >= 1 && max_M <= 8 && N >= 1, TFP8B_ERR_INVALID, "tfp8b_gemv_plan_create: 1 <= max_M <= 8 and N >= 1 (max_M=%d N=%d)",
+                  max_M, N);
+    tfp8b_gemv_plan* pl = static_cast<tfp8b_gemv_plan*>(calloc(1, sizeof(tfp8b_gemv_plan)));
+    TFP8B_REQUIRE(pl, TFP8B_ERR_INVALID, "tfp8b_gemv_plan_create: out of host memory");
+    pl->max_M = max_M;
+    for (int M = 1; M <= max_M; ++M) {
+        const int rc = gemv_setup(pl->by_m[M], x_dtype, codes, scale, scale_kind, bias, y_dtype, M, N, K, G, fmt, 0, true);
+        if (rc != TFP8B_OK) { free(pl); return rc; }
+    }
+    cudaError_t e = cudaGetDevice(&pl->device);
+    if (e != cudaSuccess) { free(pl); return cuda_fail(e, "cudaGetDevice"); }
+    *plan = pl;
+    return TFP8B_OK;
+}
+
+extern "C" int tfp8b_gemv_plan_run(const tfp8b_gemv_plan* plan, const void* x, void* y, int M, unsigned int flags,
+                                   tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(plan, TFP8B_ERR_INVALID, "tfp8b_gemv_plan_run: null plan");
+    if (M == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(M >= 1 && M <= plan->max_M, TFP8B_ERR_UNSUPPORTED, "tfp8b_gemv_plan_run: M=%d outside 1..%d", M, plan->max_M);
+    return gemv_run(plan->by_m[M], x, y, flags, nullptr, nullptr, nullptr, nullptr, 0.f, stream);
+}
+
+extern "C" void tfp8b_gemv_plan_destroy(tfp8b_gemv_plan* plan) { free(plan); }

@@ -39,6 +39,10 @@ _SIGNATURES = {
     "tfp8b_prep": ([_P, _I, _P, _P, _I, _I, _P], _I),
     "tfp8b_gemv": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_gemv_ex": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.c_uint, _P], _I),
+    "tfp8b_gemv_plan_create": ([ctypes.POINTER(_P), _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I], _I),
+    "tfp8b_gemv_plan_run": ([_P, _P, _P, _I, ctypes.c_uint, _P], _I),
+    "tfp8b_gemv_plan_destroy": ([_P], None),
+    "tfp8b_allreduce_wait_limit": ([ctypes.c_longlong], ctypes.c_longlong),
     "tfp8b_gemm": ([_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_gemv_normed": ([_P, _P, _P, _P, ctypes.c_float, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_gemv_gated": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
@@ -76,8 +80,7 @@ def load():
                 _error = e
                 raise RuntimeError(
                     f"tfp8: the CUDA kernel library could not be loaded from {_LIB_PATH} ({e}). "
-                    "Build it with `python -c 'import __graft_entry__ as g; g.build()'` or "
-                    "`make -C fp8-compatibility-layer_b200/csrc`.") from e
+                    f"Build it with `make -C {os.path.join(os.path.dirname(os.path.dirname(_LIB_PATH)), 'csrc')}`.") from e
     return _lib
 
 
@@ -226,11 +229,15 @@ def prepare_activations(x):
 class GemvLaunch:
     """A decode-GEMV call for one layer with everything but (x, y, M) bound once.
 
-    Per call: one `torch.empty`, three ctypes values, one C call. The bound tensors are referenced
-    here so their storage outlives the launch; FP8Linear rebuilds the object when a buffer object
-    is replaced. Same constructor and call signature as the reference's class of this name.
+    Construction makes a plan in the library (`tfp8b_gemv_plan_create`): shape checks, the
+    shared-memory layout, the kernel variant and the tensor map of the weight stream are worked
+    out there, once. Per call: one `torch.empty`, a few ctypes values, one C call that launches the
+    kernel. The bound tensors are referenced here so their storage outlives the launch; FP8Linear
+    rebuilds the object when a buffer object is replaced. Same constructor and call signature as
+    the reference's class of this name.
     """
-    __slots__ = ("fn", "dev", "device", "args", "q", "ws", "bias", "lut", "out_dtype", "N", "_stream")
+    __slots__ = ("fn", "dev", "device", "plan", "args", "q", "ws", "bias", "lut", "out_dtype", "N", "_stream", "_destroy",
+                 "__weakref__")
 
     def __init__(self, x_dtype, qweight, lut16, wscale, bias, out_dtype, group_size, fmt):
         lib = load()
@@ -238,12 +245,23 @@ class GemvLaunch:
         self.device = qweight.device
         N, K = qweight.shape
         self.N = N
-        self.fn = lib.tfp8b_gemv_ex
+        self.fn = lib.tfp8b_gemv_plan_run
+        self._destroy = lib.tfp8b_gemv_plan_destroy
         self._stream = torch._C._cuda_getCurrentRawStream
-        self.args = [_P(0), _I(_DT[x_dtype]), _P(qweight.data_ptr()), _P(wscale.data_ptr()), _I(_scale_kind(wscale)),
-                     _P(bias.data_ptr() if bias is not None else 0), _P(0), _I(_DT[out_dtype]), _I(0), _I(N), _I(K),
-                     _I(group_size), _I(FMT_ID[fmt]), ctypes.c_uint(0), _P(0)]
+        plan = _P(0)
+        with torch.cuda.device(self.dev):
+            rc = lib.tfp8b_gemv_plan_create(ctypes.byref(plan), _DT[x_dtype], qweight.data_ptr(), wscale.data_ptr(),
+                                            _scale_kind(wscale), bias.data_ptr() if bias is not None else None,
+                                            _DT[out_dtype], GEMV_MAXM, N, K, group_size, FMT_ID[fmt])
+        _check(rc, "tfp8b_gemv_plan_create")
+        self.plan = plan
+        self.args = [plan, _P(0), _P(0), _I(0), ctypes.c_uint(0), _P(0)]
         self.q, self.ws, self.bias, self.lut, self.out_dtype = qweight, wscale, bias, lut16, out_dtype
+
+    def __del__(self):
+        plan, self.plan = getattr(self, "plan", None), None
+        if plan is not None and plan.value:
+            self._destroy(plan)
 
     def __call__(self, x, M, out_shape=None, independent=False):
         """x: contiguous CUDA tensor of the bound dtype on this layer's device holding M rows of K
@@ -252,11 +270,11 @@ class GemvLaunch:
         precedes this call in the stream, so the two may run concurrently."""
         y = torch.empty(out_shape or (M, self.N), dtype=self.out_dtype, device=self.device)
         a = self.args
-        a[0].value = x.data_ptr()
-        a[6].value = y.data_ptr()
-        a[8].value = M
-        a[13].value = 1 if independent else 0
-        a[14].value = self._stream(self.dev)
+        a[1].value = x.data_ptr()
+        a[2].value = y.data_ptr()
+        a[3].value = M
+        a[4].value = 1 if independent else 0
+        a[5].value = self._stream(self.dev)
         rc = self.fn(*a)
         if rc != 0:
             _check(rc, "tfp8b_gemv")
@@ -408,6 +426,12 @@ def argmax_into(out, logits):
                                  logits.stride(0), _stream(dev))
     _check(rc, "tfp8b_argmax")
     return out
+
+
+def allreduce_wait_limit(cycles=0) -> int:
+    """Sets (cycles > 0) how many SM clock cycles the fused all-reduce waits for a peer before it
+    gives up and poisons the row; returns the previous limit. cycles <= 0 only queries."""
+    return int(load().tfp8b_allreduce_wait_limit(int(cycles)))
 
 
 def attn_scratch_floats(batch, n_heads, max_seq, head_dim=128):

@@ -57,7 +57,9 @@ def normalize_scale(scale, N, K, block=None):
 
 def linear_from_checkpoint(qweight, scale, bias=None, fmt="e4m3fn", block=None, **kw):
     """One FP8Linear from a checkpoint's code tensor (torch float8 or uint8, [N, K]) and scale
-    tensor in any of the layouts above. Codes and scale values are adopted bit for bit."""
+    tensor in any of the layouts above. Codes and scale values are adopted bit for bit.
+    `scale_format="ue8m0"` (in **kw) is accepted only for checkpoints whose scales are exact powers
+    of two; any other scale raises ValueError instead of being rounded."""
     if qweight.dim() != 2:
         raise ValueError("weight codes must be 2-D [out_features, in_features]")
     N, K = qweight.shape

@@ -318,11 +318,29 @@ class DecodeRunner:
             model.set_comm(comm if int(ok) else None)
         self.tok = torch.zeros(batch, 1, dtype=torch.int64, device=dev)
         self.pos = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.host_pos = 0            # host-side mirror of self.pos
         self.graph = None
+
+    def _room(self, more, what):
+        """The static KV cache holds cfg.max_seq positions; the position itself lives on the device
+        (it is bumped inside the captured graph), so the host keeps its own count and refuses a
+        call that would write past the cache instead of letting a kernel find out."""
+        if self.host_pos + more > self.model.cfg.max_seq:
+            raise ValueError(f"{what}: {self.host_pos} cached positions + {more} more exceed the KV cache "
+                             f"(max_seq={self.model.cfg.max_seq})")
+
+    def check_device(self):
+        """Raises if a kernel of the step gave up on a bounded wait (a tensor-parallel peer that
+        never answered) or skipped an out-of-range position. Synchronises."""
+        if self.tok.is_cuda:
+            _ext.device_status(self.tok.device)
 
     @torch.no_grad()
     def prefill(self, tokens):
         T = tokens.shape[1]
+        self.host_pos = 0
+        self._room(T, "prefill")
+        self.host_pos = T
         pos = torch.arange(T, device=tokens.device)
         logits = self.model(tokens, pos, prefill=True, last_only=True)
         self._pick(logits)
@@ -344,6 +362,7 @@ class DecodeRunner:
 
     @torch.no_grad()
     def capture(self, warmup=3):
+        self._room(max(warmup, 1), "capture (its warm-up steps write cache positions too)")
         keep_tok, keep_pos = self.tok.clone(), self.pos.clone()
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
@@ -358,7 +377,11 @@ class DecodeRunner:
         self.tok.copy_(keep_tok); self.pos.copy_(keep_pos)
 
     @torch.no_grad()
-    def decode(self, steps):
+    def decode(self, steps, check=True):
+        """`steps` greedy tokens per sequence, [B, steps]. With `check` the device status word is
+        read afterwards (one synchronisation per call, not per step)."""
+        self._room(steps, "decode")
+        self.host_pos += steps
         out = []
         for _ in range(steps):
             if self.graph is not None:
@@ -366,4 +389,6 @@ class DecodeRunner:
             else:
                 self._step()
             out.append(self.tok.clone())
+        if check:
+            self.check_device()
         return torch.cat(out, dim=1)

@@ -78,7 +78,9 @@ class FP8Linear(nn.Module):
     @classmethod
     def from_fp8_checkpoint(cls, qweight, weight_scale, bias=None, fmt="e4m3fn", **kw):
         """Adopt an existing FP8 checkpoint's codes and scales verbatim. `qweight` is uint8 or a
-        torch float8 tensor of the declared format; `weight_scale` is a scalar, [N] or [N, K/G]."""
+        torch float8 tensor of the declared format; `weight_scale` is a scalar, [N] or [N, K/G].
+        With scale_format="ue8m0" every scale must be an exact power of two (checked here: the
+        kernels would otherwise read other values than the float32 buffer holds)."""
         if qweight.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
             if qweight.dtype != get_format(fmt).torch_dtype:
                 raise ValueError(f"checkpoint dtype {qweight.dtype} does not match declared fmt {fmt}")
@@ -91,6 +93,8 @@ class FP8Linear(nn.Module):
         layer.weight_scale.copy_(ws)
         if bias is not None:
             layer.bias_f32.copy_(bias.float())
+        if layer.scale_format == "ue8m0":
+            scale_to_ue8m0(layer.weight_scale, what="from_fp8_checkpoint: weight_scale")     # raises unless exact
         return layer
 
     def extra_repr(self):
@@ -115,7 +119,8 @@ class FP8Linear(nn.Module):
             return ws
         c = self._e8
         if c is None or c[0] is not ws or c[1] != ws._version:
-            c = self._e8 = (ws, ws._version, scale_to_ue8m0(ws).contiguous())
+            c = self._e8 = (ws, ws._version,
+                            scale_to_ue8m0(ws, what=f"FP8Linear({self.in_features}->{self.out_features}).weight_scale").contiguous())
         return c[2]
 
     def _gemv_launch(self, x_dtype):

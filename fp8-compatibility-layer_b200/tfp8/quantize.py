@@ -53,12 +53,26 @@ def dequantize_weight(q: torch.Tensor, s: torch.Tensor, fmt, group_size) -> torc
     return (vals * s.float().unsqueeze(-1)).reshape(N, K)
 
 
-def scale_to_ue8m0(s: torch.Tensor) -> torch.Tensor:
-    """Power-of-two float32 scales -> UE8M0 bytes (value 2^(b-127)); a scale that is not a power
-    of two is rounded up to the next one first."""
-    m, e = torch.frexp(s.float())
+def scale_to_ue8m0(s: torch.Tensor, strict: bool = True, what: str = "weight scale") -> torch.Tensor:
+    """Power-of-two float32 scales -> UE8M0 bytes (value 2^(b-127)).
+
+    A UE8M0 byte can only hold a power of two in [2^-127, 2^127]. With `strict` (the default) any
+    other value -- not a power of two, zero, negative, non-finite -- raises ValueError: the bytes
+    would otherwise stand for a different number than the float32 scale that the CPU path and
+    `dequantized_weight()` keep using. With strict=False such a scale is rounded up to the next
+    power of two (and clamped into range)."""
+    s = s.float()
+    m, e = torch.frexp(s)
     e = torch.where(m == 0.5, e - 1, e)
-    return (e.clamp(-127, 127) + 127).to(torch.uint8)
+    b = (e.clamp(-127, 127) + 127).to(torch.uint8)
+    if strict:
+        bad = ~(ue8m0_to_scale(b) == s)
+        if bool(bad.any()):
+            v = s[bad].flatten()[0].item()
+            raise ValueError(f"{what}: {int(bad.sum())} of {s.numel()} values are not powers of two in [2^-127, 2^127] "
+                             f"(first: {v!r}); scale_format='ue8m0' needs power-of-two scales "
+                             "(quantize with pow2_scale=True, or keep scale_format='fp32')")
+    return b
 
 
 def ue8m0_to_scale(b: torch.Tensor) -> torch.Tensor:

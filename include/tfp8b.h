@@ -55,7 +55,15 @@ enum {
     TFP8B_ERR_INVALID = -1,     /* null pointer, bad enum, negative size, misaligned pointer */
     TFP8B_ERR_UNSUPPORTED = -2, /* shape outside what the kernels serve (K % 32, G % 32, ...) */
     TFP8B_ERR_CUDA = -3,        /* a CUDA runtime / driver call failed */
-    TFP8B_ERR_DEVICE = -4       /* a kernel gave up on a bounded wait (see tfp8b_device_status) */
+    TFP8B_ERR_DEVICE = -4       /* a kernel reported a problem in the device status word (see tfp8b_device_status) */
+};
+
+/* bits of the device status word */
+enum {
+    TFP8B_STATUS_GEMV_WAIT = 1, /* a decode-GEMV CTA gave up on a bounded wait: its outputs are incomplete */
+    TFP8B_STATUS_GEMM_WAIT = 2, /* the same for the tile GEMM */
+    TFP8B_STATUS_GLUE_WAIT = 4, /* tfp8b_allreduce_add_rmsnorm: a peer never raised its flag; the rows were set to NaN */
+    TFP8B_STATUS_GLUE_POS = 8   /* tfp8b_rope_kv_store: a position outside [0, max_seq) was skipped */
 };
 
 typedef void* tfp8b_stream_t; /* a cudaStream_t */
@@ -67,10 +75,10 @@ TFP8B_API int tfp8b_version(void);
  * from cuLaunchKernel's return code (tfp8/_ext.py:156-157, 215-216). */
 TFP8B_API const char* tfp8b_last_error_string(void);
 
-/* Reads and clears the device-side status word of the current device: 0 = no kernel has given up
- * on a bounded wait since the last call. SYNCHRONISES the stream. out_status may be NULL.
- * Returns TFP8B_ERR_DEVICE when the word was non-zero. No reference counterpart (its kernels
- * have no waits). */
+/* Reads and clears the device-side status word of the current device (TFP8B_STATUS_* bits): 0 = no
+ * kernel has given up on a bounded wait or skipped an out-of-range position since the last call.
+ * SYNCHRONISES the stream. out_status may be NULL. Returns TFP8B_ERR_DEVICE when the word was
+ * non-zero. No reference counterpart (its kernels have no waits). */
 TFP8B_API int tfp8b_device_status(unsigned int* out_status, tfp8b_stream_t stream);
 
 /* codes[i] = FP8(x[i]): round to nearest even, saturate to +-max finite, never inf.
@@ -111,17 +119,46 @@ TFP8B_API int tfp8b_gemv(const void* x, int x_dtype, const uint8_t* codes, const
                const float* bias, void* y, int y_dtype, int M, int N, int K, int G, int fmt,
                tfp8b_stream_t stream);
 
-/* tfp8b_gemv with flags. TFP8B_GEMV_INDEPENDENT_IO: the caller vouches that x and y (and scale,
- * bias) are neither written nor read by the kernel that precedes this call in the stream -- as
- * for the K and V projections that follow the Q projection of the same activations, or the layers
- * of a sweep. The call then runs concurrently with that kernel (programmatic dependent launch
- * without the wait in front of the activations); it still never completes before its
- * predecessor, so later work in the stream sees both finished. Without the flag the kernel
- * prefetches only its weights while the predecessor runs. No reference counterpart. */
+/* Ordering contract of the decode GEMVs (tfp8b_gemv, tfp8b_gemv_ex, tfp8b_gemv_normed,
+ * tfp8b_gemv_gated, tfp8b_gemv_plan_run). They are launched with programmatic dependent launch:
+ * the kernel may start while the kernel BEFORE it in the stream is still running, and reads
+ *   codes, scale, bias   at once, without waiting for that kernel;
+ *   x (and the inputs of the normed / gated forms), y   only after that kernel has completed.
+ * So the kernel that immediately precedes a GEMV in its stream must not WRITE that GEMV's codes,
+ * scale or bias (weights are normally written once, long before). A caller that does update
+ * weights in the kernel just before -- a requantize, a LoRA merge -- passes TFP8B_GEMV_NO_PDL,
+ * which makes the call an ordinary stream-ordered launch, or puts any other kernel in between.
+ *
+ * tfp8b_gemv with flags.
+ * TFP8B_GEMV_INDEPENDENT_IO: the caller vouches that x and y are neither written nor read by the
+ * kernel that precedes this call in the stream -- as for the K and V projections that follow the
+ * Q projection of the same activations, or the layers of a sweep. The call then runs
+ * concurrently with that kernel (no wait in front of the activations); it still never completes
+ * before its predecessor, so later work in the stream sees both finished.
+ * TFP8B_GEMV_NO_PDL: plain launch, nothing is read before the predecessor has completed.
+ * No reference counterpart. */
 #define TFP8B_GEMV_INDEPENDENT_IO 1u
+#define TFP8B_GEMV_NO_PDL 2u
 TFP8B_API int tfp8b_gemv_ex(const void* x, int x_dtype, const uint8_t* codes, const void* scale, int scale_kind,
                   const float* bias, void* y, int y_dtype, int M, int N, int K, int G, int fmt,
                   unsigned int flags, tfp8b_stream_t stream);
+
+/* A decode GEMV prepared once per layer: the tensor map of the weight stream, the shared-memory
+ * plan and the kernel choice are worked out when the plan is made, so a call costs one kernel
+ * launch and nothing else (tfp8b_gemv builds a tensor map per call). Replaces the reference's
+ * prepared launch, GemvLaunch (tfp8/_ext.py:163-217), which binds every argument but x, y and M.
+ *   create   binds codes / scale / bias / shape / types on the CURRENT device for 1 <= max_M <= 8
+ *            rows; *plan receives an opaque handle (host memory only, no device allocation).
+ *   run      y[0:M] = x[0:M] W^T (+ bias) for 1 <= M <= max_M; x, y as in tfp8b_gemv; flags as in
+ *            tfp8b_gemv_ex. The bound buffers must still be alive and unchanged in address.
+ *   destroy  frees the handle (NULL is allowed).
+ * A plan may be used from several threads and streams at once. */
+typedef struct tfp8b_gemv_plan tfp8b_gemv_plan;
+TFP8B_API int tfp8b_gemv_plan_create(tfp8b_gemv_plan** plan, int x_dtype, const uint8_t* codes, const void* scale,
+                  int scale_kind, const float* bias, int y_dtype, int max_M, int N, int K, int G, int fmt);
+TFP8B_API int tfp8b_gemv_plan_run(const tfp8b_gemv_plan* plan, const void* x, void* y, int M, unsigned int flags,
+                  tfp8b_stream_t stream);
+TFP8B_API void tfp8b_gemv_plan_destroy(tfp8b_gemv_plan* plan);
 
 /* Tile GEMM for any M >= 1 on prepared activations (tfp8b_prep):
  *   y[m,n] = xs[m] * sum_k x16[m,k] * dec(codes[n,k]) * scale[n,k/G] + bias[n]
@@ -166,7 +203,9 @@ TFP8B_API int tfp8b_epilogue(const float* acc, const float* xs, const float* bia
  * tfp8b_rope_kv_store: rotary embedding (rotate-half pairs i, i + hd/2) of the Q and K heads of a
  * fused projection output qkv [B, T, H + 2*KV, hd]; Q goes to q_out [B, H, T, hd], K and V into the
  * static caches [B, KV, max_seq, hd] at positions pos[t] (int64, on the device). cos / sin are
- * f32 [max_seq, hd/2]. dtype f16 or bf16. */
+ * f32 [max_seq, hd/2]. dtype f16 or bf16. A token whose position lies outside [0, max_seq) is
+ * skipped (no table read, no store, its q_out rows are left as they were) and
+ * TFP8B_STATUS_GLUE_POS is raised in the device status word. */
 TFP8B_API int tfp8b_rope_kv_store(const void* qkv, int dtype, const long long* pos, const float* cosv,
                   const float* sinv, void* q_out, void* k_cache, void* v_cache, int B, int T, int H,
                   int KV, int hd, int max_seq, tfp8b_stream_t stream);
@@ -238,6 +277,13 @@ TFP8B_API int tfp8b_add_rmsnorm(void* x, const void* delta, const void* weight, 
 TFP8B_API int tfp8b_allreduce_add_rmsnorm(void* x, const float* partial, const void* weight, void* out, int dtype,
                   int rows, int dim, float eps, float* const* recv, unsigned int* const* flags,
                   unsigned int* state, int rank, int world, int max_rows, tfp8b_stream_t stream);
+
+/* Sets how long (SM clock cycles, > 0) a CTA of tfp8b_allreduce_add_rmsnorm waits for a peer's flag
+ * before it gives up, for all later calls of this process; returns the previous limit (about two
+ * seconds by default; cycles <= 0 only queries). When the wait runs out the kernel does not sum
+ * stale data: it sets the row to NaN in x and out, raises TFP8B_STATUS_GLUE_WAIT and returns.
+ * No counterpart in the reference. */
+TFP8B_API long long tfp8b_allreduce_wait_limit(long long cycles);
 
 /* One-query attention over the static KV cache, grouped-query heads: for every sequence b and head h,
  * out[b, h, :] = softmax(q[b, h, :] . K[b, h / (H/KV), 0:pos+1, :]^T / sqrt(hd)) V[...]. q and out are

@@ -34,6 +34,27 @@ def test_rope_kv_store_matches_torch(dtype):
     assert not kc[:, :, untouched].any() and not vc[:, :, untouched].any()
 
 
+def test_rope_kv_store_leaves_guard_rows_untouched():
+    """The caches sit inside larger buffers whose neighbouring rows hold a pattern: storing at the
+    first and the last valid position must leave every guard row as it was (the store offset is
+    pos * hd, so an off-by-one at either end would land in a guard row)."""
+    from tfp8 import _ext
+    torch.manual_seed(3)
+    B, T, H, KV, hd, S = 1, 2, 4, 1, 128, 16
+    qkv = torch.randn(B, T, (H + 2 * KV) * hd, device="cuda").half()
+    pos = torch.tensor([0, S - 1], device="cuda")
+    ang = torch.arange(S, device="cuda").float()[:, None] * torch.ones(hd // 2, device="cuda")[None]
+    big_k = torch.full((S + 8, hd), 7.0, device="cuda", dtype=torch.float16)
+    big_v = torch.full((S + 8, hd), 9.0, device="cuda", dtype=torch.float16)
+    kc, vc = big_k[4:4 + S].view(B, KV, S, hd), big_v[4:4 + S].view(B, KV, S, hd)
+    _ext.rope_kv_store(qkv, pos, ang.cos().contiguous(), ang.sin().contiguous(), kc, vc, H, KV)
+    torch.cuda.synchronize()
+    assert (big_k[:4] == 7).all() and (big_k[4 + S:] == 7).all() and (big_v[:4] == 9).all() and (big_v[4 + S:] == 9).all()
+    assert (big_k[5:4 + S - 1] == 7).all() and (big_v[5:4 + S - 1] == 9).all()          # positions in between: untouched
+    assert not (big_v[4] == 9).all() and not (big_v[4 + S - 1] == 9).all()              # the two positions were written
+    assert _ext.device_status() == 0
+
+
 @pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16))
 def test_silu_mul_matches_torch(dtype):
     from tfp8 import _ext
@@ -101,6 +122,48 @@ def test_allreduce_add_rmsnorm_single_rank(dtype):
         g.replay(); g.replay()
     torch.cuda.synchronize()
     assert state.tolist() == [5, 0] and bool(torch.isfinite(out.float()).all())
+    assert _ext.device_status() == 0
+
+
+def test_allreduce_peer_that_never_answers_is_reported_not_summed():
+    """Failure detection without a fault: a group of two is described whose second "rank" is just
+    another local buffer that no kernel ever writes a flag into. With the wait limit set short the
+    kernel must return by itself, raise the status bit, and hand back NaN rows (not a sum that
+    silently misses the peer's part); the context stays usable and the next healthy call is right."""
+    from tfp8 import _ext
+    torch.manual_seed(6)
+    dim, rows, world = 1024, 2, 2
+    w = torch.ones(dim, device="cuda", dtype=torch.float16)
+    recv = [torch.zeros(2 * world * 8 * dim, dtype=torch.float32, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(2 * world * 8, dtype=torch.int32, device="cuda") for _ in range(world)]
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    x = torch.randn(rows, 1, dim, device="cuda").half()
+    x0 = x.clone()
+    part = torch.randn(rows, 1, dim, device="cuda")
+    old = _ext.allreduce_wait_limit(2_000_000)                       # about a millisecond of SM clock
+    try:
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        out = _ext.allreduce_add_rmsnorm(x, part, w, 1e-5, [r.data_ptr() for r in recv], [f.data_ptr() for f in flags],
+                                         state, 0, 8)
+        t1.record()
+        torch.cuda.synchronize()
+    finally:
+        _ext.allreduce_wait_limit(old)
+    assert t0.elapsed_time(t1) < 500.0                               # it gave up by itself, quickly
+    with pytest.raises(RuntimeError, match="peer never answered"):
+        _ext.device_status()
+    assert bool(torch.isnan(out.float()).all()) and bool(torch.isnan(x.float()).all())
+    # what it pushed to the "peer" before waiting is there, with the flag of call 1
+    assert torch.equal(recv[1].view(2, world, 8, dim)[1, 0, :rows], part.view(rows, dim))
+    assert flags[1].view(2, world, 8)[1, 0, :rows].tolist() == [1] * rows
+    assert _ext.device_status() == 0                                 # cleared by the read above
+    # a healthy single-rank call afterwards works on the same context
+    st1 = torch.zeros(2, dtype=torch.int32, device="cuda")
+    x.copy_(x0)
+    want = _ext.add_rmsnorm(x0.clone(), part.half(), w, 1e-5)
+    got = _ext.allreduce_add_rmsnorm(x, part, w, 1e-5, [recv[0].data_ptr()], [flags[0].data_ptr()], st1, 0, 8)
+    assert ((got.float() - want.float()).abs() <= 2.0 ** -9 * want.float().abs() + 1e-5).all()
     assert _ext.device_status() == 0
 
 

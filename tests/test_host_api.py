@@ -184,3 +184,37 @@ def test_operators_refuse_cpu_tensors():
         _ext.prepare_activations(torch.zeros(2, 64))
     with pytest.raises(ValueError):
         _ext.encode(torch.zeros(4))
+
+
+def test_ue8m0_needs_exact_powers_of_two():
+    """UE8M0 bytes can only stand for powers of two: anything else must be refused, not rounded,
+    or the kernels would use other scales than the float32 buffer (and the CPU path) holds."""
+    import pytest
+    from tfp8 import FP8Linear
+    from tfp8.quantize import scale_to_ue8m0, ue8m0_to_scale
+    s = torch.tensor([[2.0 ** -13, 1.0, 2.0 ** 20, 2.0 ** -127, 2.0 ** 127]])
+    assert torch.equal(ue8m0_to_scale(scale_to_ue8m0(s)), s)
+    for bad in (3.0, 0.0, -2.0, float("inf"), float("nan"), 2.0 ** -130):
+        with pytest.raises(ValueError, match="not powers of two"):
+            scale_to_ue8m0(torch.tensor([[1.0, bad]]))
+    assert scale_to_ue8m0(torch.tensor([3.0]), strict=False).item() == 129        # rounded up to 4 = 2^(129-127)
+    q = torch.zeros(64, 64, dtype=torch.uint8)
+    FP8Linear.from_fp8_checkpoint(q, torch.full((64, 2), 0.25), scale_format="ue8m0")
+    with pytest.raises(ValueError, match="from_fp8_checkpoint"):
+        FP8Linear.from_fp8_checkpoint(q, torch.full((64, 2), 0.3), scale_format="ue8m0")
+    layer = FP8Linear.from_fp8_checkpoint(q, torch.full((64, 2), 0.5), scale_format="ue8m0")
+    layer.weight_scale[3, 1] = 0.7                                   # a later in-place edit is caught when the bytes are re-derived
+    with pytest.raises(ValueError, match="weight_scale"):
+        layer._kernel_scale()
+
+
+def test_plan_argument_validation_needs_no_gpu():
+    lib = _ext.load()
+    plan = ctypes.c_void_p(0)
+    assert lib.tfp8b_gemv_plan_create(ctypes.byref(plan), 0, None, None, 0, None, 0, 9, 16, 64, 64, 0) == -1   # max_M > 8
+    assert plan.value is None
+    assert lib.tfp8b_gemv_plan_create(ctypes.byref(plan), 0, None, None, 0, None, 0, 8, 16, 64, 64, 0) == -1   # null codes
+    assert lib.tfp8b_gemv_plan_run(None, None, None, 1, 0, None) == -1
+    lib.tfp8b_gemv_plan_destroy(None)
+    old = lib.tfp8b_allreduce_wait_limit(0)
+    assert old > 0 and lib.tfp8b_allreduce_wait_limit(12345) == old and lib.tfp8b_allreduce_wait_limit(old) == 12345

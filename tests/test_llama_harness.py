@@ -23,3 +23,20 @@ def test_decode_step_matches_prefill():
     assert torch.allclose(logits[:, 0], full[:, 0], rtol=1e-3, atol=1e-3)          # fp16 projection outputs
     out = run.decode(3)
     assert out.shape == (2, 3) and int(run.pos) == 8 + 3
+
+
+def test_runner_refuses_to_run_past_the_kv_cache():
+    """The cache position lives on the device; the runner's host-side count must stop a prefill, a
+    capture or a decode that would write beyond max_seq before any kernel sees such a position."""
+    import pytest
+    torch.manual_seed(1)
+    model = build_fp8_llama(TINY, "cpu", dtype=torch.float32, fp8=FP8Config(min_features=64, nan_check=False))
+    run = DecodeRunner(model, 1)
+    with pytest.raises(ValueError, match="exceed the KV cache"):
+        run.prefill(torch.randint(0, TINY.vocab, (1, TINY.max_seq + 1)))
+    run.prefill(torch.randint(0, TINY.vocab, (1, TINY.max_seq - 2)))
+    run.decode(2)                                                   # fills the cache exactly
+    assert int(run.pos) == TINY.max_seq == run.host_pos
+    with pytest.raises(ValueError, match="exceed the KV cache"):
+        run.decode(1)
+    assert int(run.pos) == TINY.max_seq                             # nothing ran
