@@ -55,6 +55,7 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const 
 int gemv_status(unsigned int* out, cudaStream_t st);
 int gemm_status(unsigned int* out, cudaStream_t st);
 int glue_status(unsigned int* out, cudaStream_t st);
+int gemm_mx_status(unsigned int* out, cudaStream_t st);
 
 }  // namespace tfp8b
 
@@ -70,6 +71,7 @@ extern "C" int tfp8b_device_status(unsigned int* out_status, tfp8b_stream_t stre
     int rc = gemv_status(&v, st);
     if (rc == TFP8B_OK) rc = gemm_status(&v, st);
     if (rc == TFP8B_OK) rc = glue_status(&v, st);
+    if (rc == TFP8B_OK) rc = gemm_mx_status(&v, st);
     if (rc != TFP8B_OK) return rc;
     if (out_status) *out_status = v;
     if (v) {

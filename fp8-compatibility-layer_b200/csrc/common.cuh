@@ -304,11 +304,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         "[%0], [%1, {%2, %3, %4}], [%5], %6;"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar), "l"(policy) : "memory");
 }
-// 3-D tiled prefetch of the same box into L2 only (no shared-memory destination, no barrier).
-__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* map, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
-                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
 // Programmatic dependent launch: let the next kernel in the stream start its prologue now /
 // wait until everything the previous kernel wrote is visible.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -8,7 +8,10 @@
 //
 // Persistent CTAs (one per SM) walk the list of 128 x BN output tiles. K flows in 64-wide k-blocks
 // through three shared-memory rings that never drain between tiles -- raw FP8 codes (deep: it
-// hides HBM latency), activation tiles, decoded fp16 weight tiles -- and the FP32 accumulators are
+// hides HBM latency), activation tiles (their own ring with their own barriers, as deep as the
+// tile width allows: an activation tile is requested when its slot is released and arrives an L2
+// round trip later, so with only as many slots as decoded tiles that round trip, not the tensor
+// core, paced narrow tiles), decoded fp16 weight tiles -- and the FP32 accumulators are
 // double-buffered in tensor memory so the epilogue of a tile overlaps the main loop of the next.
 // Warp roles:
 //   warp 0       raw-code producer: one tiled TMA load per raw slot, 128 weight rows x 128
@@ -47,7 +50,9 @@ constexpr int GM_RPT = GM_NG;                          // rows per decode thread
 constexpr int GM_DEC_WARP0 = 4;                        // warps 0..3: raw producer, MMA, activation producer, second MMA
 constexpr int GM_EPI_WARP0 = GM_DEC_WARP0 + GM_DEC_WARPS;
 constexpr int GM_THREADS = (GM_EPI_WARP0 + 4) * 32;
-constexpr int GM_MAX_SLOTS = 8;     // per ring
+constexpr int GM_MAX_SLOTS = 8;     // per ring (decoded tiles, raw codes)
+constexpr int GM_MAX_XSLOTS = 8;    // activation ring
+constexpr int GM_NA = 4;            // decoded-tile slots: the groups' tiles in decode, the one in the MMA, one spare
 constexpr int GM_MAX_DST = 8;       // output destinations of one launch (one per GPU of a tensor-parallel group)
 constexpr int GM_HEADER = 2048;     // barriers, TMEM base, per-row scale reciprocals
 constexpr int GM_A_BYTES = GM_BM * GM_BK * 2;    // decoded fp16 tile
@@ -56,6 +61,7 @@ constexpr int GM_SMEM_MAX = 232448;              // 227 KB opt-in limit per CTA
 static_assert(GM_NG == 2 || GM_NG == 4, "two or four decode groups");
 
 struct GemmParams {
+    int sc_row;               // bytes of one row's K-group scales kept in shared memory per tile, 0 = read from global
     const float* xs;
     const void* scale;
     const float* bias;
@@ -65,10 +71,9 @@ struct GemmParams {
     int push;                 // peers are served by the push warp (16-byte copies of whole tile rows), not by the epilogue
     int M, N, K, G, scale_kind, y_dt;
     int BN, tmem_cols, m_tiles, ntiles;
-    int ns, sr;          // stages (decoded weight tile + activation tile), slots of the raw-code ring
+    int ns, sr, nx;      // slots of the decoded-tile ring, of the raw-code ring, of the activation ring
     int rb;              // k-blocks per raw slot: 2 (128 bytes per weight row and copy) or 1
     int x_bytes;         // one activation tile: BN x 64 fp16
-    int stage_bytes;
     int nmma;            // MMA-issuing threads; thread t takes k-blocks t, t + nmma, ... into its own accumulator
     int ks, nkbu;        // split-K: every tile is cut into ks units of nkbu k-blocks; ntiles counts units
     float* ws;           // ks > 1: FP32 [M, N] workspace the units add their partial tiles into
@@ -77,6 +82,7 @@ struct GemmParams {
 struct GemmHeader {
     uint64_t full[GM_MAX_SLOTS], empty[GM_MAX_SLOTS];
     uint64_t raw_full[GM_MAX_SLOTS], raw_empty[GM_MAX_SLOTS];
+    uint64_t x_full[GM_MAX_XSLOTS], x_empty[GM_MAX_XSLOTS];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint32_t tmem_base;
@@ -207,8 +213,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     GemmHeader* hd = reinterpret_cast<GemmHeader*>(smem);
     if (threadIdx.x == 0) GM_TRACE(0, 250);
-    uint8_t* stages = smem + GM_HEADER;                                   // [decoded tile 16 KB][activation tile]
-    uint8_t* raw_ring = stages + static_cast<size_t>(p.ns) * p.stage_bytes;
+    uint8_t* stages = smem + GM_HEADER;                                   // decoded tiles, 16 KB each
+    uint8_t* x_ring = stages + static_cast<size_t>(p.ns) * GM_A_BYTES;    // activation tiles
+    uint8_t* raw_ring = x_ring + static_cast<size_t>(p.nx) * p.x_bytes;
+    uint8_t* sc_cache = raw_ring + static_cast<size_t>(p.sr) * p.rb * GM_RAW_BYTES;   // [2][128 rows][sc_row bytes]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nkb = p.nkbu;                               // k-blocks of one unit of work (the whole K unless split)
@@ -227,8 +235,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.ns; ++s) {
-            mbar_init(smem_u32(&hd->full[s]), GM_GROUP_WARPS + 1);      // a group's warps + the activation copy
+            mbar_init(smem_u32(&hd->full[s]), GM_GROUP_WARPS);          // the warps of the group that decoded it
             mbar_init(smem_u32(&hd->empty[s]), 1);
+        }
+        for (int s = 0; s < p.nx; ++s) {
+            mbar_init(smem_u32(&hd->x_full[s]), 1);                     // the activation copy (bytes counted)
+            mbar_init(smem_u32(&hd->x_empty[s]), 1);
         }
         for (int s = 0; s < p.sr; ++s) {
             mbar_init(smem_u32(&hd->raw_full[s]), 1);
@@ -288,11 +300,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             for (int i = 0; i < my_tiles && ok; ++i) {
                 const int m0 = tile_m0(i), kb0 = unit_kb0(i);
                 for (int kb = 0; kb < nkb; ++kb) {
-                    if (!first_pass && !mbar_wait(smem_u32(&hd->empty[slot]), phase, STATUS_GEMM_WAIT)) { ok = false; break; }
-                    const uint32_t bar = smem_u32(&hd->full[slot]);
+                    if (!first_pass && !mbar_wait(smem_u32(&hd->x_empty[slot]), phase, STATUS_GEMM_WAIT)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&hd->x_full[slot]);
                     mbar_expect_tx(bar, static_cast<uint32_t>(p.x_bytes));
-                    tma_load_2d(smem_u32(stages + static_cast<size_t>(slot) * p.stage_bytes + GM_A_BYTES), &tm_x, (kb0 + kb) * GM_BK, m0, bar, pol_x);
-                    if (++slot == p.ns) { slot = 0; phase ^= 1u; first_pass = false; }
+                    tma_load_2d(smem_u32(x_ring + static_cast<size_t>(slot) * p.x_bytes), &tm_x, (kb0 + kb) * GM_BK, m0, bar, pol_x);
+                    if (++slot == p.nx) { slot = 0; phase ^= 1u; first_pass = false; }
                 }
             }
         }
@@ -310,16 +322,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             // D fp32, A/B fp16, both K-major, N = BN, M = 128
             const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(p.BN >> 3) << 17) | (static_cast<uint32_t>(GM_BM >> 4) << 24);
             const int t = warp == 1 ? 0 : 1;
-            const uint32_t stage_step = static_cast<uint32_t>(p.nmma * p.stage_bytes);
-            const uint32_t ring_bytes = static_cast<uint32_t>(p.ns * p.stage_bytes);
-            const uint32_t stages_u32 = smem_u32(stages);
-            uint32_t st = stages_u32 + static_cast<uint32_t>(t * p.stage_bytes);     // this thread's next stage
-            uint32_t bar_off = static_cast<uint32_t>(t * 8);                          // its barriers' offset in full[] / empty[]
+            // this thread's cursors in the decoded-tile ring and in the activation ring: byte
+            // offset of the slot, offset of its barriers, parity to wait for
+            const uint32_t a_step = static_cast<uint32_t>(p.nmma * GM_A_BYTES), a_ring = static_cast<uint32_t>(p.ns * GM_A_BYTES);
+            const uint32_t x_step = static_cast<uint32_t>(p.nmma * p.x_bytes), x_ringb = static_cast<uint32_t>(p.nx * p.x_bytes);
+            const uint32_t stages_u32 = smem_u32(stages), xring_u32 = smem_u32(x_ring);
+            uint32_t a_off = static_cast<uint32_t>(t * GM_A_BYTES), a_bar = static_cast<uint32_t>(t * 8), a_par = 0;
+            uint32_t x_off = static_cast<uint32_t>(t * p.x_bytes), x_bar = static_cast<uint32_t>(t * 8), x_par = 0;
             const uint32_t full0 = smem_u32(&hd->full[0]), empty0 = smem_u32(&hd->empty[0]);
+            const uint32_t xfull0 = smem_u32(&hd->x_full[0]), xempty0 = smem_u32(&hd->x_empty[0]);
             int next = t;                     // CTA-wide number of this thread's next k-block
-            uint32_t par = 0;
-            bool ok = true, ready = false;    // ready: the next k-block's barrier was already seen complete
-            uint64_t da = umma_desc_sw128(st), db = umma_desc_sw128(st + GM_A_BYTES);
+            bool ok = true, ready = false;    // ready: the next k-block's barriers were already seen complete
+            uint64_t da = umma_desc_sw128(stages_u32 + a_off), db = umma_desc_sw128(xring_u32 + x_off);
             for (int i = 0; i < my_tiles && ok; ++i) {
                 const int buf = i & 1;
                 // the accumulator buffer must have been drained by the epilogue of tile i - 2
@@ -330,24 +344,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 int kb = next - i * nkb;
                 for (; kb < nkb; kb += p.nmma) {
                     GM_TRACE(5, i * nkb + kb);
-                    if (!ready) ok = mbar_wait(full0 + bar_off, par, STATUS_GEMM_WAIT);
+                    if (!ready) ok = mbar_wait(full0 + a_bar, a_par, STATUS_GEMM_WAIT) && mbar_wait(xfull0 + x_bar, x_par, STATUS_GEMM_WAIT);
                     if (!ok) break;
                     GM_TRACE(3, i * nkb + kb);
                     tc_fence_after();
                     tc_mma_f16(tmem_acc, da, db, idesc, accumulate);
                     tc_mma_f16(tmem_acc, da + 2, db + 2, idesc, 1u);
                     // while those two are queued: move on to this thread's next k-block, look at its
-                    // barrier once and build its descriptors
-                    const uint32_t cur_empty = empty0 + bar_off;
+                    // barriers once and build its descriptors
+                    const uint32_t cur_empty = empty0 + a_bar, cur_xempty = xempty0 + x_bar;
                     const uint64_t da_cur = da, db_cur = db;
-                    st += stage_step; bar_off += static_cast<uint32_t>(p.nmma * 8);
-                    if (st >= stages_u32 + ring_bytes) { st -= ring_bytes; bar_off -= static_cast<uint32_t>(p.ns * 8); par ^= 1u; }
-                    ready = mbar_try_wait(full0 + bar_off, par);
-                    da = umma_desc_sw128(st); db = umma_desc_sw128(st + GM_A_BYTES);
+                    a_off += a_step; a_bar += static_cast<uint32_t>(p.nmma * 8);
+                    if (a_off >= a_ring) { a_off -= a_ring; a_bar -= static_cast<uint32_t>(p.ns * 8); a_par ^= 1u; }
+                    x_off += x_step; x_bar += static_cast<uint32_t>(p.nmma * 8);
+                    if (x_off >= x_ringb) { x_off -= x_ringb; x_bar -= static_cast<uint32_t>(p.nx * 8); x_par ^= 1u; }
+                    ready = mbar_try_wait(full0 + a_bar, a_par) && mbar_try_wait(xfull0 + x_bar, x_par);
+                    da = umma_desc_sw128(stages_u32 + a_off); db = umma_desc_sw128(xring_u32 + x_off);
                     tc_mma_f16(tmem_acc, da_cur + 4, db_cur + 4, idesc, 1u);
                     tc_mma_f16(tmem_acc, da_cur + 6, db_cur + 6, idesc, 1u);
                     GM_TRACE(6, i * nkb + kb);
-                    tc_commit(cur_empty);
+                    tc_commit(cur_empty);             // both slots are free once these MMAs have read them
+                    tc_commit(cur_xempty);
                     GM_TRACE(4, i * nkb + kb);
                     accumulate = 1u;
                 }
@@ -389,10 +406,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         const uint32_t rfull0 = smem_u32(&hd->raw_full[0]), rempty0 = smem_u32(&hd->raw_empty[0]);
         // ring cursors of the group's next k-block: byte offset of its stage / raw slot, the offset
         // of their barriers, the parity to wait for
-        const uint32_t a_step = static_cast<uint32_t>(GM_NG * p.stage_bytes), a_ring = static_cast<uint32_t>(p.ns * p.stage_bytes);
+        const uint32_t a_step = static_cast<uint32_t>(GM_NG * GM_A_BYTES), a_ring = static_cast<uint32_t>(p.ns * GM_A_BYTES);
         const uint32_t r_slots = static_cast<uint32_t>(GM_NG / p.rb);           // raw slots between the group's k-blocks
         const uint32_t r_step = r_slots * raw_slot_bytes, r_ring = static_cast<uint32_t>(p.sr) * raw_slot_bytes;
-        uint32_t a_off = static_cast<uint32_t>(group * p.stage_bytes), a_bar = static_cast<uint32_t>(group * 8), a_par = 0;
+        uint32_t a_off = static_cast<uint32_t>(group * GM_A_BYTES), a_bar = static_cast<uint32_t>(group * 8), a_par = 0;
         uint32_t r_off = static_cast<uint32_t>(group / p.rb) * raw_slot_bytes, r_bar = static_cast<uint32_t>(group / p.rb) * 8u, r_par = 0;
         int done = group;                            // CTA-wide number of the group's next k-block
         bool ok = true;
@@ -413,7 +430,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 bmax[h2] = 0;
                 srow[h2] = static_cast<size_t>(min(n0 + r0 + RSTEP * h2, p.N - 1)) * ng;
             }
-            if (ng > 1) {
+            // K-group scales of the tile. A scale read from global memory in the k-loop is a demand
+            // miss that queues behind the megabytes of weight tiles this very kernel keeps in flight:
+            // measured, it comes back about 2.4 us later, and with the ratios fetched eight k-blocks
+            // ahead that latency -- not HBM bandwidth, not the tensor core -- set the pace of narrow
+            // tiles (0.3 us per k-block whatever the width). So where a row's scales are short
+            // enough, the decode warps copy the tile's scales into shared memory once, at the start
+            // of the tile (double-buffered by tile parity: a group may already be in the next tile
+            // while the other finishes this one), and the k-loop reads them from there.
+            const uint8_t* sc = sc_cache + static_cast<size_t>(i & 1) * GM_BM * p.sc_row;
+            if (ng > 1 && p.sc_row > 0) {
+                const int vpr = p.sc_row >> 4;                                      // 16-byte vectors per row
+                for (int v = td; v < GM_BM * vpr; v += GM_DEC_THREADS) {
+                    const int row = v / vpr, j = v - row * vpr;
+                    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.scale) + static_cast<size_t>(min(n0 + row, p.N - 1)) * p.sc_row + j * 16;
+                    *reinterpret_cast<uint4*>(const_cast<uint8_t*>(sc) + row * p.sc_row + j * 16) = __ldg(reinterpret_cast<const uint4*>(src));
+                }
+                named_barrier_sync(1, GM_DEC_THREADS);
+#pragma unroll
+                for (int h2 = 0; h2 < RPT; ++h2) {
+                    const uint8_t* rowp = sc + (r0 + RSTEP * h2) * p.sc_row;
+                    float mx = 0.f;
+                    uint32_t bm = 0u;
+                    for (int j = 0; j < vpr; ++j) {
+                        const uint4 t = *reinterpret_cast<const uint4*>(rowp + j * 16);
+                        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            if (e8) {
+                                const uint32_t m4 = __vmaxu4(w[e], __byte_perm(w[e], 0u, 0x4321));
+                                bm = max(bm, max(m4 & 0xFFu, (m4 >> 16) & 0xFFu));
+                            } else {
+                                mx = fmaxf(mx, __uint_as_float(w[e]));
+                            }
+                        }
+                    }
+                    binv[h2] = e8 ? __uint_as_float(bm) : (mx > 0.f ? 1.f / mx : 0.f);
+                    bmax[h2] = static_cast<int>(bm);
+                }
+            } else if (ng > 1) {
                 // row maxima of the K-group scales: GM_DEC_THREADS / 128 threads share a row
                 constexpr int TPR = GM_DEC_THREADS / GM_BM;
                 const int row = td / TPR, part = td % TPR;
@@ -451,10 +506,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     if (ng > 1 && l0 + j < nloc) {
                         const int u32 = (kabs + (l0 + j) * GM_NG) * 2 + (c >> 1);
                         const int gi = min(g_shift >= 0 ? (u32 >> g_shift) : (u32 / g32), ng - 1);
+                        if (p.sc_row > 0) {
 #pragma unroll
-                        for (int h2 = 0; h2 < RPT; ++h2) {
-                            if (e8) dst[j][h2] = static_cast<uint32_t>(static_cast<int>(reinterpret_cast<const uint8_t*>(p.scale)[srow[h2] + gi]) - bmax[h2]);
-                            else dst[j][h2] = __float_as_uint(reinterpret_cast<const float*>(p.scale)[srow[h2] + gi] * binv[h2]);
+                            for (int h2 = 0; h2 < RPT; ++h2) {
+                                const uint8_t* rowp = sc + (r0 + RSTEP * h2) * p.sc_row;
+                                if (e8) dst[j][h2] = static_cast<uint32_t>(static_cast<int>(rowp[gi]) - bmax[h2]);
+                                else dst[j][h2] = __float_as_uint(reinterpret_cast<const float*>(rowp)[gi] * binv[h2]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int h2 = 0; h2 < RPT; ++h2) {
+                                if (e8) dst[j][h2] = static_cast<uint32_t>(static_cast<int>(reinterpret_cast<const uint8_t*>(p.scale)[srow[h2] + gi]) - bmax[h2]);
+                                else dst[j][h2] = __float_as_uint(reinterpret_cast<const float*>(p.scale)[srow[h2] + gi] * binv[h2]);
+                            }
                         }
                     }
                 }
@@ -935,24 +999,35 @@ static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, con
     p.nmma = (bn <= 128 && p.nkbu >= 4) ? 2 : 1;
     p.tmem_cols = 2 * p.nmma * bn < 32 ? 32 : 2 * p.nmma * bn;
     if (p.nmma != 1) p.push = 0;                             // warp 3 issues MMAs there
-    // Shared memory: four stages (the groups' tiles in decode, the one in the MMA, one spare), the
-    // rest raw codes -- the ring whose depth hides HBM latency. (At BN = 256 that rest is two slots,
-    // four k-blocks: there the CTAs of the other activation tiles pull the same stripe through L2.)
-    // Every ring's length is a multiple of the stride its users walk it with (decode groups,
-    // issuing threads), so a slot is always revisited by the same user, in order: a parity wait
-    // can then never be answered by a phase two completions away.
+    // Shared memory: four decoded tiles (the groups' tiles in decode, the one in the MMA, one
+    // spare); an activation ring as deep as pays (narrow tiles are paced by the L2 round trip of
+    // their activation tile unless enough of them are in flight; at BN = 256 the MMA of a k-block
+    // outlasts it); the rest raw codes -- the ring whose depth hides HBM latency. (At BN = 256 that
+    // rest is two slots, four k-blocks: there the CTAs of the other activation tiles pull the
+    // same stripe through L2.) Every ring's length is a multiple of the stride its users walk it
+    // with (decode groups, issuing threads), so a slot is always revisited by the same user, in
+    // order: a parity wait can then never be answered by a phase two completions away.
     p.x_bytes = bn * GM_BK * 2;
-    p.stage_bytes = GM_A_BYTES + p.x_bytes;
     const int budget = GM_SMEM_MAX - 1024 - GM_HEADER;
-    p.ns = 4;
-    static_assert(4 % GM_NG == 0, "stage ring must be a multiple of the decode groups");
+    p.ns = GM_NA;
+    static_assert(GM_NA % GM_NG == 0 && GM_NA % 2 == 0, "decoded-tile ring: a multiple of the decode groups and of the issuing threads");
+    p.nx = bn >= 256 ? 4 : (bn == 128 ? 6 : GM_MAX_XSLOTS);          // even: two issuing threads walk it with stride 2
     const int raw_slot = p.rb * GM_RAW_BYTES;
     const int raw_stride = GM_NG / p.rb;                      // slots between a group's consecutive k-blocks
-    p.sr = (budget - p.ns * p.stage_bytes) / raw_slot;
+    // K-group scales of a tile in shared memory (two tiles' worth), where a row's scales are whole
+    // 16-byte pieces of at most 128 bytes: see the decode warps. TFP8B_GEMM_SCALE_CACHE=0 turns it off.
+    {
+        static const int use_cache = [] { const char* v = getenv("TFP8B_GEMM_SCALE_CACHE"); return !(v && v[0] == '0'); }();
+        const int row_bytes = (K / G) * (scale_kind == TFP8B_SCALE_UE8M0 ? 1 : 4);
+        p.sc_row = (use_cache && G != K && row_bytes % 16 == 0 && row_bytes <= 128 && (reinterpret_cast<uintptr_t>(scale) & 15u) == 0) ? row_bytes : 0;
+    }
+    const int sc_bytes = 2 * GM_BM * p.sc_row;
+    p.sr = (budget - p.ns * GM_A_BYTES - p.nx * p.x_bytes - sc_bytes) / raw_slot;
     if (p.sr > GM_MAX_SLOTS) p.sr = GM_MAX_SLOTS;
     p.sr -= p.sr % raw_stride;
-    TFP8B_REQUIRE(p.sr >= GM_NG, TFP8B_ERR_INVALID, "tfp8b_gemm: ring sizes ns=%d sr=%d do not fit", p.ns, p.sr);
-    const size_t smem = 1024 + GM_HEADER + static_cast<size_t>(p.ns) * p.stage_bytes + static_cast<size_t>(p.sr) * raw_slot;
+    TFP8B_REQUIRE(p.sr >= GM_NG / p.rb && p.sr >= 2, TFP8B_ERR_INVALID, "tfp8b_gemm: ring sizes ns=%d nx=%d sr=%d do not fit", p.ns, p.nx, p.sr);
+    const size_t smem = 1024 + GM_HEADER + static_cast<size_t>(p.ns) * GM_A_BYTES + static_cast<size_t>(p.nx) * p.x_bytes +
+                        static_cast<size_t>(p.sr) * raw_slot + sc_bytes;
 
     CUtensorMap tw, tx;
     int rc;

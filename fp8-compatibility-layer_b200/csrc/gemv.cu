@@ -55,7 +55,6 @@ constexpr int GV_SMEM_TARGET = TFP8B_GV_SMEM_KB * 1024;       // per CTA: two CT
 constexpr int GV_SMEM_LARGE = 200 * 1024;        // ... unless the activations need the room (M > 1 with a long K)
 constexpr int GV_XRES_SMALL = 40 * 1024;         // resident activations up to this size keep the small footprint
 constexpr int GV_XRES_MAX = 96 * 1024;           // activations up to this size stay resident per CTA
-constexpr int GV_L2PF_DEFAULT = 6;               // stages prefetched into L2 ahead of the ring by a call that waits for its predecessor
 
 struct GemvParams {
     const void* x;
@@ -65,7 +64,6 @@ struct GemvParams {
     void* y;
     int M, N, K, G, scale_kind, y_dt;
     int nstages, wpitch, xpitch, wstage_bytes, stage_bytes, x_resident, xres_bytes, ntiles, pdl;
-    int l2pf;          // stages of the weight stream pulled into L2 ahead of the shared-memory ring (tensor-map layout)
     // Activations computed by the kernel itself instead of copied (16-bit types, resident rows):
     //   xmode 1  x = RMSNorm(xa + xb) * xw: the residual update (xb may be null) and the norm of a
     //            decoder block; the CTA with index 0 also stores the updated residual to xout
@@ -384,31 +382,11 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             }
         };
 
-        // L2 prefetch cursor: runs l2pf stages ahead of the stage being issued into the ring. The
-        // ring alone (what fits beside a second resident CTA) holds too few bytes to cover the HBM
-        // latency after a wait; the prefetched stages are already on their way, or in L2, when
-        // the ring asks for them. While the kernel sits at griddepcontrol.wait behind its
-        // predecessor this is what keeps its weight stream moving.
-        int tp = 0, cp = 0, ip = 0;
-        auto prefetch_to = [&](int upto) {               // prefetch stages [ip, min(upto, total))
-            if constexpr (TMA) {
-                if (p.l2pf <= 0) return;
-                for (; ip < upto && ip < total; ++ip) {
-                    const int n0 = (static_cast<int>(blockIdx.x) + tp * static_cast<int>(gridDim.x)) * GV_ROWS;
-                    if (lane == 0) tma_prefetch_l2_3d(&tm_w, 0, n0, (cp * GV_KS) >> 7);
-                    if (++cp == nchunks) { cp = 0; ++tp; }
-                }
-            }
-        };
         const int pre = min(S, total);
         int t = 0, c = 0;
         for (int i = 0; i < pre; ++i) {                  // weights first: they never depend on the predecessor
             issue_w(t, c, i);
             if (++c == nchunks) { c = 0; ++t; }
-        }
-        if (TMA && p.l2pf > 0) {                         // the ring's own stages need no prefetch
-            for (; ip < pre; ++ip) if (++cp == nchunks) { cp = 0; ++tp; }
-            prefetch_to(pre + p.l2pf);
         }
         if (p.pdl == 1) pdl_wait();                      // activations may be the predecessor's output
         if (p.x_resident && !XF) {
@@ -432,7 +410,6 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         for (int i = pre; i < total; ++i) {
             if (!mbar_wait(bar_empty + 8 * slot, phase, STATUS_GEMV_WAIT)) break;
             issue_w(t, c, slot);
-            prefetch_to(i + 1 + p.l2pf);
             if (!p.x_resident) issue_x(c, slot);
             if (++c == nchunks) { c = 0; ++t; }
             if (++slot == S) { slot = 0; phase ^= 1u; }
@@ -814,10 +791,6 @@ static int gemv_run(const GemvSetup& g, const void* x, void* y, unsigned int fla
     GemvParams p = g.p;
     p.x = x; p.y = y; p.xa = xa; p.xb = xb; p.xw = xw; p.xout = xout; p.xeps = xeps;
     p.pdl = pdl_mode_of(flags);
-    // TFP8B_GEMV_L2PF=<stages> overrides how far the L2 prefetch runs ahead (0 = off). By default
-    // only calls that wait for their predecessor prefetch: an independent call streams at once.
-    static const int l2pf_env = [] { const char* v = getenv("TFP8B_GEMV_L2PF"); return v ? atoi(v) : -1; }();
-    p.l2pf = !g.tma ? 0 : (l2pf_env >= 0 ? l2pf_env : (p.pdl == 1 ? GV_L2PF_DEFAULT : 0));
     CUtensorMap tx = {};
     if (g.tma && !p.x_resident) {                 // activations that travel with the stages: their own tensor map
         const int rc = gemv_x_map(&tx, x, g.x_dtype, p.M, p.K);

@@ -46,6 +46,10 @@ _SIGNATURES = {
     "tfp8b_gemm": ([_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_gemv_normed": ([_P, _P, _P, _P, ctypes.c_float, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_gemv_gated": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
+    "tfp8b_gemm_w8a8": ([_P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _P], _I),
+    "tfp8b_mx_packed_scale_bytes": ([_I, _I], ctypes.c_longlong),
+    "tfp8b_mx_pack_scales": ([_P, _P, _I, _I, _P], _I),
+    "tfp8b_quantize_k": ([_P, _I, _P, _P, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_gemm_splitk": ([_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P], _I),
     "tfp8b_gemm_scatter": ([_P, _P, _P, _P, _I, _P, _P, _I, ctypes.c_longlong, ctypes.c_longlong, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_linear_static": ([_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P], _I),
@@ -372,6 +376,75 @@ def epilogue_into(y, acc, xs, bias, n0=0):
         rc = load().tfp8b_epilogue(acc.data_ptr(), xs.data_ptr(), bview.data_ptr() if bview is not None else 0,
                                    yv.data_ptr(), _DT[y.dtype], M, n, y.shape[1], _stream(dev))
     _check(rc, "tfp8b_epilogue")
+    return y
+
+
+# ------------------------------------------------------------------ W8A8 (FP8 activations x FP8 weights)
+W8A8_BLOCK32, W8A8_ROWCOL = 0, 1
+
+
+def mx_packed_scale_bytes(rows, K) -> int:
+    """Size of the packed UE8M0 scale buffer of a [rows, K] code tensor (512 bytes per 128 rows x 128 K)."""
+    return int(load().tfp8b_mx_packed_scale_bytes(rows, K))
+
+
+def mx_pack_scales(scale_u8):
+    """Row-major UE8M0 bytes [rows, K/32] -> the packed chunk layout the MX GEMM reads (uint8, 1-D)."""
+    dev = _need_cuda(scale_u8)
+    if scale_u8.dtype != torch.uint8 or scale_u8.dim() != 2:
+        raise ValueError("mx_pack_scales takes a 2-D uint8 tensor [rows, K/32]")
+    rows, kb = scale_u8.shape
+    out = torch.empty(mx_packed_scale_bytes(rows, kb * 32), dtype=torch.uint8, device=scale_u8.device)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_mx_pack_scales(scale_u8.contiguous().data_ptr(), out.data_ptr(), rows, kb * 32, _stream(dev))
+    _check(rc, "tfp8b_mx_pack_scales")
+    return out
+
+
+def quantize_k(x, fmt="e4m3fn", ue8m0=False, packed=False):
+    """x [R, K] -> (codes u8 [R, K], scales): one scale per row and 32-wide block of K, amax / fmax
+    clamped below at 1e-12; with ue8m0 rounded up to a power of two and stored as its exponent byte.
+    scales: float32 [R, K/32]; uint8 [R, K/32] (ue8m0); or the packed 1-D uint8 buffer (packed)."""
+    dev = _need_cuda(x)
+    R, K = x.shape
+    if K % 32:
+        raise ValueError(f"quantize_k: K={K} must be a multiple of 32")
+    x = x.contiguous()
+    if x.dtype not in _DT:
+        x = x.float()
+    q = torch.empty(R, K, dtype=torch.uint8, device=x.device)
+    if packed:
+        s = torch.empty(mx_packed_scale_bytes(R, K), dtype=torch.uint8, device=x.device)
+    else:
+        s = torch.empty(R, K // 32, dtype=torch.uint8 if ue8m0 else torch.float32, device=x.device)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_quantize_k(x.data_ptr(), _DT[x.dtype], q.data_ptr(), s.data_ptr(), R, K, FMT_ID[fmt], int(ue8m0 or packed),
+                                     int(packed), _stream(dev))
+    _check(rc, "tfp8b_quantize_k")
+    return q, s
+
+
+def gemm_w8a8(a_codes, a_scale, a_fmt, w_codes, w_scale, w_fmt, bias=None, out_dtype=torch.float32, mode=W8A8_BLOCK32):
+    """y [M, N] = dec(a_codes [M, K]) @ dec(w_codes [N, K]).T with the scales applied, + bias.
+    mode W8A8_BLOCK32: per row and 32-wide block of K -- uint8 scales are UE8M0 in the PACKED
+    layout (mx_pack_scales / quantize_k(packed=True)) and run on the block-scaled tensor-core
+    path; float32 scales are [rows, K/32] row-major. mode W8A8_ROWCOL: a_scale [M], w_scale [N]."""
+    dev = _need_cuda(a_codes, a_scale, w_codes, w_scale, bias)
+    M, K = a_codes.shape
+    N = w_codes.shape[0]
+    if w_codes.shape[1] != K:
+        raise ValueError(f"gemm_w8a8: K mismatch ({K} vs {w_codes.shape[1]})")
+    if a_scale.dtype != w_scale.dtype:
+        raise ValueError("gemm_w8a8: both scale tensors must have the same type")
+    y = torch.empty(M, N, dtype=out_dtype, device=a_codes.device)
+    if M == 0 or N == 0:
+        return y
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_gemm_w8a8(a_codes.contiguous().data_ptr(), a_scale.contiguous().data_ptr(), FMT_ID[a_fmt],
+                                    w_codes.contiguous().data_ptr(), w_scale.contiguous().data_ptr(), FMT_ID[w_fmt], mode,
+                                    _scale_kind(a_scale), bias.data_ptr() if bias is not None else None, y.data_ptr(),
+                                    _DT[out_dtype], M, N, K, _stream(dev))
+    _check(rc, "tfp8b_gemm_w8a8")
     return y
 
 

@@ -12,7 +12,11 @@ class FP8Config:
     fmt: str = "e4m3fn"
     profile: str = "llm_safe"
     weight_group: int | None = None      # None: one scale per output channel; 32 / 128: per K-group
-    activation: str = "fp16"             # W8A16 only
+    # "fp16": W8A16, the reference's only implemented mode. "fp8": W8A8 -- activations are quantized
+    # per row and 32-wide block of K on the fly and the product runs on the block-scaled FP8 tensor
+    # cores; needs weight_group=32 and scale_format="ue8m0" (the MX layout). The reference reserves
+    # the field and raises for anything but "fp16" (tfp8/config.py:25-26 there).
+    activation: str = "fp16"
     kv_cache: str = "fp16"
     fallback: str = "tbf16"              # owner recorded for modules that are left alone
     min_features: int | None = None      # None: 1024 (llm_safe) / 256 (image_safe)
@@ -32,8 +36,10 @@ class FP8Config:
     def __post_init__(self):
         if self.profile not in PROFILES:
             raise ValueError(f"profile {self.profile!r} not supported; use one of {PROFILES}")
-        if self.activation != "fp16":
-            raise NotImplementedError("only W8A16 (activation='fp16') is implemented")
+        if self.activation not in ("fp16", "fp8"):
+            raise NotImplementedError("activation must be 'fp16' (W8A16) or 'fp8' (W8A8 with 32-wide block scales)")
+        if self.activation == "fp8" and (self.weight_group != 32 or self.scale_format != "ue8m0"):
+            raise NotImplementedError("activation='fp8' is the MX layout: weight_group=32 and scale_format='ue8m0'")
         if self.kv_cache != "fp16":
             raise NotImplementedError("an FP8 KV cache is not implemented")
         if self.large_m_backend not in ("fused", "chunked"):

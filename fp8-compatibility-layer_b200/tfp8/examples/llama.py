@@ -250,12 +250,17 @@ class Llama(nn.Module):
 
 
 def build_fp8_llama(cfg: LlamaConfig, device, dtype=torch.float16, fp8: FP8Config | None = None, group=None, seed=0,
-                    sigma=0.02):
+                    sigma=0.02, tp=None):
     """Random-init (N(0, sigma^2)) decoder with every projection quantized to FP8Linear, built one
     layer at a time so the full-precision model never exists. With a process group the layers are
-    quantized first and then sharded Megatron-style (every rank draws the same full weights)."""
+    quantized first and then sharded Megatron-style (every rank draws the same full weights);
+    tp=1 builds the unsharded model even when a process group exists."""
     fp8 = fp8 or FP8Config(profile="llm_safe", nan_check=False)
     world = dist.get_world_size(group) if (group is not None or (dist.is_available() and dist.is_initialized())) else 1
+    if tp is not None:
+        if tp not in (1, world):
+            raise ValueError(f"tp={tp}: either 1 (unsharded) or the size of the process group ({world})")
+        world = tp
     if cfg.n_heads % world or (cfg.n_kv_heads % world and world % cfg.n_kv_heads) or cfg.ffn % world:
         raise ValueError(f"tensor-parallel size {world} does not divide the model")
     with torch.device("meta"):
@@ -320,6 +325,7 @@ class DecodeRunner:
         self.pos = torch.zeros(1, dtype=torch.int64, device=dev)
         self.host_pos = 0            # host-side mirror of self.pos
         self.graph = None
+        self.last_logits = None      # logits [B, 1, vocab] of the latest decode step
 
     def _room(self, more, what):
         """The static KV cache holds cfg.max_seq positions; the position itself lives on the device
@@ -357,6 +363,7 @@ class DecodeRunner:
     @torch.no_grad()
     def _step(self):
         logits = self.model(self.tok, self.pos, prefill=False)
+        self.last_logits = logits            # inside a captured graph: the static tensor every replay rewrites
         self._pick(logits)
         self.pos.add_(1)
 
@@ -377,9 +384,10 @@ class DecodeRunner:
         self.tok.copy_(keep_tok); self.pos.copy_(keep_pos)
 
     @torch.no_grad()
-    def decode(self, steps, check=True):
+    def decode(self, steps, check=True, keep_logits=None):
         """`steps` greedy tokens per sequence, [B, steps]. With `check` the device status word is
-        read afterwards (one synchronisation per call, not per step)."""
+        read afterwards (one synchronisation per call, not per step). `keep_logits`: a list that
+        receives a copy of every step's logits [B, 1, vocab]."""
         self._room(steps, "decode")
         self.host_pos += steps
         out = []
@@ -389,6 +397,8 @@ class DecodeRunner:
             else:
                 self._step()
             out.append(self.tok.clone())
+            if keep_logits is not None:
+                keep_logits.append(self.last_logits.clone())
         if check:
             self.check_device()
         return torch.cat(out, dim=1)

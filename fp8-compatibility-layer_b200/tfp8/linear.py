@@ -10,6 +10,12 @@ fallback behaviour as the reference's tfp8/linear.py. Routing per call, by M = a
                   FP16 weight workspace exists any more)
   CPU tensors     dequantize + float32 matmul in torch -- the definition of the result
 
+With activation="fp8" (W8A8: 32-wide UE8M0 K-groups, K a multiple of 128) every M takes one other
+route: the activation rows are quantized on the fly to FP8 with one power-of-two scale per 32-wide
+block (the reference's quantize_k, fp8_cuda.py:74-91 there) and the product runs on the
+block-scaled FP8 tensor cores (tcgen05.mma.kind::mxf8f6f4); booked as "w8a8". On CPU tensors the
+same arithmetic is spelled out in torch (quantize, dequantize both operands, float32 matmul).
+
 On CUDA tensors nothing falls back silently: without the kernel library the call raises.
 """
 import torch
@@ -28,7 +34,7 @@ class FP8Linear(nn.Module):
 
     def __init__(self, in_features, out_features, bias=True, fmt="e4m3fn", group_size=None,
                  out_dtype=torch.bfloat16, large_m=256, large_m_backend="chunked",
-                 workspace_mb=32, nan_check=True, device=None, scale_format="fp32"):
+                 workspace_mb=32, nan_check=True, device=None, scale_format="fp32", activation="fp16"):
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
         self.fmt = get_format(fmt).name
@@ -41,6 +47,11 @@ class FP8Linear(nn.Module):
         self.large_m, self.large_m_backend = large_m, large_m_backend
         self.workspace_mb, self.nan_check = workspace_mb, nan_check
         self.scale_format = scale_format
+        if activation not in ("fp16", "fp8"):
+            raise ValueError("activation must be 'fp16' or 'fp8'")
+        if activation == "fp8" and (self.group_size != 32 or scale_format != "ue8m0" or in_features % 128):
+            raise ValueError("activation='fp8' needs group_size=32, scale_format='ue8m0' and in_features % 128 == 0")
+        self.activation = activation
         groups = in_features // self.group_size
         self.register_buffer("qweight", torch.zeros(out_features, in_features, dtype=torch.uint8, device=device))
         self.register_buffer("weight_scale", torch.ones(out_features, groups, dtype=torch.float32, device=device))
@@ -48,7 +59,7 @@ class FP8Linear(nn.Module):
         self._nan_checks = 0
         self.fallback = None
         self.fallback_reason = None
-        self.stats = {"gemv": 0, "gemm": 0, "chunked": 0, "torch": 0, "fallback": 0}
+        self.stats = {"gemv": 0, "gemm": 0, "chunked": 0, "torch": 0, "fallback": 0, "w8a8": 0}
         self._shape_ok = in_features % 32 == 0 and self.group_size % 32 == 0
         self._kernels_ok = self._shape_ok and _ext.available()
         self._lut = lut(self.fmt, device) if device is not None else None
@@ -58,6 +69,7 @@ class FP8Linear(nn.Module):
         self.independent_input = False
         self._gemv = {}            # (x dtype, out dtype) -> _ext.GemvLaunch
         self._e8 = None            # (weight_scale object, its version, uint8 tensor) for scale_format="ue8m0"
+        self._e8_packed = None     # (the uint8 tensor above, its packed copy) for activation="fp8"
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -97,6 +109,13 @@ class FP8Linear(nn.Module):
             scale_to_ue8m0(layer.weight_scale, what="from_fp8_checkpoint: weight_scale")     # raises unless exact
         return layer
 
+    def __getstate__(self):
+        # prepared launches hold handles of the kernel library and device pointers: a copy of the
+        # layer (copy.deepcopy, pickle) starts without them and builds its own on first use
+        d = self.__dict__.copy()
+        d["_gemv"], d["_e8"], d["_e8_packed"] = {}, None, None
+        return d
+
     def extra_repr(self):
         return (f"in={self.in_features}, out={self.out_features}, fmt={self.fmt}, "
                 f"group={self.group_size}, out_dtype={self.out_dtype}, scales={self.scale_format}")
@@ -123,6 +142,32 @@ class FP8Linear(nn.Module):
                             scale_to_ue8m0(ws, what=f"FP8Linear({self.in_features}->{self.out_features}).weight_scale").contiguous())
         return c[2]
 
+    def _packed_scale(self):
+        """The weight's UE8M0 bytes in the packed order the block-scaled tensor-core path reads."""
+        e8 = self._kernel_scale()
+        c = self._e8_packed
+        if c is None or c[0] is not e8:
+            c = self._e8_packed = (e8, _ext.mx_pack_scales(e8))
+        return c[1]
+
+    def _forward_w8a8(self, x2):
+        """W8A8: quantize the activation rows per 32-wide block, multiply codes by codes."""
+        fmt = self.fmt
+        if x2.is_cuda:
+            self._require_kernels()
+            if x2.dtype not in _ext._TAG:
+                x2 = x2.float()
+            aq, sa = _ext.quantize_k(x2, fmt, True, packed=True)
+            return _ext.gemm_w8a8(aq, sa, fmt, self.qweight, self._packed_scale(), fmt, self.bias_f32, self.out_dtype)
+        # CPU tensors: the same arithmetic in torch (the definition)
+        f = get_format(fmt)
+        M, K = x2.shape
+        xb = x2.float().reshape(M, K // 32, 32)
+        s = (xb.abs().amax(-1) / f.max_finite).clamp_min(1e-12)
+        s = torch.exp2(torch.ceil(torch.log2(s)).clamp(-127, 127))
+        xq = (xb / s[..., None]).clamp(-f.max_finite, f.max_finite).to(f.torch_dtype).float() * s[..., None]
+        return F.linear(xq.reshape(M, K), self.dequantized_weight(), self.bias_f32).to(self.out_dtype)
+
     def _gemv_launch(self, x_dtype):
         """Prepared GEMV call for (input dtype, current out_dtype), rebuilt when a buffer object was
         replaced; in-place updates keep the storage and therefore the bound pointers."""
@@ -146,6 +191,12 @@ class FP8Linear(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def forward(self, x):
+        if self.activation == "fp8" and self.fallback is None:
+            lead = x.shape[:-1]
+            x2 = x.reshape(-1, x.shape[-1])
+            self.stats["w8a8" if x2.is_cuda else "torch"] += 1
+            y = self._forward_w8a8(x2.contiguous())
+            return y if x.dim() == 2 else y.reshape(*lead, self.out_features)
         # Decode fast path: contiguous CUDA input of at most 8 rows, after the NaN-checked calls.
         # Only x's data pointer and M are needed, so [B, T, K] is neither reshaped in nor out.
         if ((self._nan_checks >= _NAN_CHECKED_CALLS or not self.nan_check) and self.fallback is None

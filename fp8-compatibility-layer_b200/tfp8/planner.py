@@ -109,7 +109,7 @@ def prepare_model(model: nn.Module, domain: str = "llm", config: FP8Config | Non
         new = FP8Linear.from_linear(mod, config.fmt, config.weight_group, config.pow2_scale,
                                     large_m=config.large_m, large_m_backend=config.large_m_backend,
                                     workspace_mb=config.workspace_mb, nan_check=config.nan_check,
-                                    scale_format=config.scale_format)
+                                    scale_format=config.scale_format, activation=config.activation)
         _replace_module(model, d.name, new)
         del mod, modules[d.name]
         if torch.cuda.is_available():

@@ -171,6 +171,39 @@ TFP8B_API int tfp8b_gemm(const void* x16, const float* xs, const uint8_t* codes,
                int scale_kind, const float* bias, void* y, int y_dtype, int M, int N, int K, int G,
                int fmt, tfp8b_stream_t stream);
 
+/* ---- W8A8: FP8 activations x FP8 weights (the reference project's second native kernel,
+ * fp8_gemm_kernel.cu, and its binding fp8_cuda.py) ----
+ *
+ * tfp8b_gemm_w8a8:  y[m,n] = sum_k dec(a[m,k]) * dec(w[n,k]) * (scales) + bias[n], FP32 accumulation.
+ *   a_codes u8 [M, K], w_codes u8 [N, K] (both row-major, K contiguous), E4M3FN or E5M2 each.
+ *   scale_mode TFP8B_W8A8_BLOCK32: one scale per row and 32-wide block of K, applied to each block's
+ *       partial product (fp8_gemm_kernel.cu:86-103, SCALE_BLOCK_K). With scale_kind UE8M0 the scales
+ *       are exponent bytes in the PACKED layout below and the tensor cores apply them
+ *       (tcgen05.mma.kind::mxf8f6f4.block_scale); with scale_kind F32 they are float32 [rows, K/32]
+ *       row-major and every block goes through an FP32 register accumulation (correct, slow).
+ *   scale_mode TFP8B_W8A8_ROWCOL: a_scale [M], w_scale [N] (float32 or UE8M0 bytes), applied once
+ *       in the epilogue (fp8_gemm_kernel.cu:113-120, SCALE_ROW_COL).
+ *   Replaces the four kernels gemm_{block,rowcol}_{fp32,ue8m0} (fp8_gemm_kernel.cu:123-126) and
+ *   their launch (fp8_cuda.py:94-138). The reference stores the weight as [K, N] with scales
+ *   [K/32, N]; here both operands are K-major, the layout FP8Linear keeps (transpose once at load).
+ *   K % 128 == 0; codes and scales 16-byte aligned. y f32 (the reference's output type), f16 or bf16.
+ * PACKED scale layout: for every 128 rows x 128 K one 512-byte chunk, the byte of (row r, block b) at
+ *   (r % 32) * 16 + ((r % 128) / 32) * 4 + (b % 4), chunks ordered [r / 128][b / 4]; rows and blocks
+ *   beyond the tensor hold 127 (= 1.0). tfp8b_mx_packed_scale_bytes gives the buffer size,
+ *   tfp8b_mx_pack_scales converts row-major UE8M0 bytes [rows, K/32] (weights: once at load).
+ * tfp8b_quantize_k: rows -> FP8 codes + one scale per 32-wide block of K, the reference's dynamic
+ *   activation quantizer quantize_k (fp8_cuda.py:74-91): s = max(amax / fmax, 1e-12); with ue8m0
+ *   e = clamp(ceil(log2 s), -127, 127), s = 2^e, byte e + 127; codes = FP8(clamp(x / s)). scale:
+ *   float32 [rows, K/32], or UE8M0 bytes row-major (packed == 0) or in the packed layout. */
+enum { TFP8B_W8A8_BLOCK32 = 0, TFP8B_W8A8_ROWCOL = 1 };
+TFP8B_API int tfp8b_gemm_w8a8(const uint8_t* a_codes, const void* a_scale, int a_fmt, const uint8_t* w_codes, const void* w_scale,
+                  int w_fmt, int scale_mode, int scale_kind, const float* bias, void* y, int y_dtype, int M, int N, int K,
+                  tfp8b_stream_t stream);
+TFP8B_API long long tfp8b_mx_packed_scale_bytes(int rows, int K);
+TFP8B_API int tfp8b_mx_pack_scales(const uint8_t* scale_rowmajor, uint8_t* packed, int rows, int K, tfp8b_stream_t stream);
+TFP8B_API int tfp8b_quantize_k(const void* x, int x_dtype, uint8_t* codes, void* scale, int rows, int K, int fmt, int ue8m0,
+                  int packed, tfp8b_stream_t stream);
+
 /* The whole linear layer for any M >= 1 in one call that allocates nothing:
  *   y = x @ dequant(codes).T + bias   (activation prep, then the tile GEMM)
  * This entry point has no counterpart in the reference. It exists for callers that cannot obtain

@@ -1,4 +1,4 @@
-"""The BASELINE configurations at their FULL sizes. The oracle cannot multiply a 28672 x 8192 weight
+"""The benchmark configurations at their FULL sizes. The oracle cannot multiply a 28672 x 8192 weight
 in seconds, so these tests check (i) a random sample of output channels against the numpy oracle
 with the reference's gate, and (ii) properties that hold at any size: a one-hot activation reads
 a column of the dequantized weight back exactly, doubling the activations doubles the output
@@ -47,10 +47,10 @@ def test_decode_sweep_full_shapes(fmt):
         assert torch.equal(col, want.t().contiguous())
 
 
-@pytest.mark.parametrize("G,Ms,xdt", ((128, (16, 64, 256, 1024), torch.float16), (32, (2048, 4096), torch.bfloat16)))
+@pytest.mark.parametrize("G,Ms,xdt", ((128, (16, 64, 256, 1024), torch.float16), (32, (2048, 4096, 8192), torch.bfloat16)))
 def test_group_scaled_gemm_full_shape(G, Ms, xdt):
-    """Configs 3 and 4: 28672 x 8192 E4M3FN, UE8M0 K-group scales of 128 / 32, every M of the
-    configuration (8192 rows are the same code path as 4096)."""
+    """The group-scaled layer 28672 x 8192 E4M3FN with UE8M0 K-group scales of 128 (fp16
+    activations, 16 .. 1024 rows) and of 32 (bf16 activations, 2048 .. 8192 rows), every M."""
     from tfp8 import _ext, synth
     N, K = synth.GROUP_GEMM_SHAPE
     w = synth.group_outlier_weight(N, K, group=G, seed=G).cuda()

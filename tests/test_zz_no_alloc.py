@@ -54,3 +54,35 @@ def test_linear_static_refuses_what_does_not_fit():
     assert _call_static(lib, x, q, ws, None, y, 8192) == -2
     assert b"exceeds the built-in scratch" in lib.tfp8b_last_error_string()
     assert _call_static(lib, x[:0], q, ws, None, y[:0], 8192) == 0          # nothing to do
+
+
+def test_linear_static_allocates_nothing_and_serves_its_limit():
+    """What the entry point is named for: free device memory is the same before and after calls
+    (torch's caching allocator is not involved either: inputs and outputs exist beforehand), and a
+    call of exactly the documented maximum -- 8192 rows x 512 = 4 Mi activation values -- is served,
+    here on a layer with UE8M0 scale bytes. Checked against prep + gemm bit for bit."""
+    from tfp8 import FP8Linear, _ext
+    lib = _ext.load()
+    torch.manual_seed(22)
+    M, K, N, G = 8192, 512, 256, 128
+    layer = FP8Linear.from_linear(torch.nn.Linear(K, N, device="cuda", dtype=torch.bfloat16), group_size=G, scale_format="ue8m0")
+    q, e8, bias = layer.qweight, layer._kernel_scale(), layer.bias_f32
+    assert e8.dtype == torch.uint8
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    want = _ext.w8a16(x, q, None, e8, bias, torch.bfloat16, G, "e4m3fn")
+    got = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    assert _call_static(lib, x[:8], q, e8, bias, got[:8], G) == 0      # first call on the device: the address lookup
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    reserved0 = torch.cuda.memory_reserved()
+    for _ in range(3):
+        got.fill_(float("nan"))
+        rc = _call_static(lib, x, q, e8, bias, got, G)
+        assert rc == 0, lib.tfp8b_last_error_string()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0 and torch.cuda.memory_reserved() == reserved0, (free0, free1)
+    assert torch.equal(got, want)
+    one_more = torch.empty(M + 1, K, device="cuda", dtype=torch.bfloat16)   # one row beyond the limit
+    assert _call_static(lib, one_more, q, e8, bias, torch.empty(M + 1, N, device="cuda", dtype=torch.bfloat16), G) == -2
+    assert _ext.device_status() == 0
