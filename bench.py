@@ -310,14 +310,34 @@ def run_ours(args, rank, world, local_rank):
     hx_all = torch.cat([x.reshape(-1).cpu() for x in xs]).pin_memory()
     dx_all = torch.empty_like(hx_all, device=device)
     dx = [dx_all[offs[i]:offs[i + 1]].view(1, -1) for i in range(len(layers))]
-    hy = [torch.empty(1, l.out_features, dtype=torch.float16).pin_memory() for l in layers]
+    youts = np.cumsum([0] + [l.out_features for l in layers])
+    hy_all = torch.empty(int(youts[-1]), dtype=torch.float16).pin_memory()
+    hy = [hy_all[youts[i]:youts[i + 1]].view(1, -1) for i in range(len(layers))]
+
+    def enqueue_e2e():
+        # one copy in, the layers back to back (a copy between two layers would end the overlap of
+        # consecutive kernels), their results gathered on the device, one copy out
+        dx_all.copy_(hx_all, non_blocking=True)
+        ys = [l(d).view(-1) for l, d in zip(layers, dx)]
+        hy_all.copy_(torch.cat(ys), non_blocking=True)
+
+    # the step is captured once (copies and layer calls alike, as the decode runner captures its
+    # step) and replayed: per step one graph launch and one synchronisation on the host side
+    e2e_stream = torch.cuda.Stream()
+    e2e_stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(e2e_stream):
+        for _ in range(4):
+            enqueue_e2e()                                   # past the layers' checked first calls
+        torch.cuda.synchronize()
+        e2e_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(e2e_graph, stream=e2e_stream):
+            enqueue_e2e()
 
     def step_e2e():
-        dx_all.copy_(hx_all, non_blocking=True)
-        for l, d, o in zip(layers, dx, hy):
-            o.copy_(l(d), non_blocking=True)
+        e2e_graph.replay()                                  # on the current stream
         torch.cuda.current_stream().synchronize()
 
+    hy_all.zero_()
     step_e2e()
     for l, x, o in zip(layers, xs, hy):                     # the host rows hold the layers' results
         assert torch.equal(o, l(x).cpu()), "e2e path does not reproduce the layer's output"
@@ -325,10 +345,11 @@ def run_ours(args, rank, world, local_rank):
     with ClockSampler(local_rank) as clk_e2e:
         e2e_sec = max_over_ranks(time_eager(step_e2e, args.steps, args.warmup), world, device)
     e2e = {"value": world * step_bytes / e2e_sec / 1e9, "unit": UNIT,
-           "h2d_bytes_per_step": hx_all.numel() * 2, "d2h_bytes_per_step": sum(h.numel() * 2 for h in hy),
+           "h2d_bytes_per_step": hx_all.numel() * 2, "d2h_bytes_per_step": hy_all.numel() * 2,
            "ms_per_step": e2e_sec * 1e3, "clocks": clk_e2e.summary(),
-           "how": "FP8Linear.forward per layer (prepared GEMV plan); one pinned H2D copy of the step's activations, "
-                  "one D2H copy per layer result, one stream synchronisation per step"}
+           "how": "FP8Linear.forward per layer (prepared GEMV plan), captured once in a CUDA graph together with the pinned "
+                  "H2D copy of the step's activations, a device-side gather of the layers' results and one D2H copy "
+                  "into pinned host memory; per step one replay and one stream synchronisation"}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -365,7 +386,7 @@ def run_ours(args, rank, world, local_rank):
     if not args.quick:
         line["extra"] = extra_measurements(args, device, peaks, world, clocks, local_rank) if world == 1 else {}
         line["extra"]["clocks"] = clocks
-        del layers, launches, xs, outs, hx_all, hy, dx, dx_all
+        del layers, launches, xs, outs, hx_all, hy, hy_all, dx, dx_all
         torch.cuda.empty_cache()
         # the extras must never cost the headline line: an error that every rank meets alike
         # (a shape the tensor-parallel size does not divide, no peer memory) is recorded instead
@@ -383,6 +404,21 @@ def run_ours(args, rank, world, local_rank):
                 clocks["llama_decode"] = c.summary()
             except Exception as e:
                 line["extra"]["llama_decode"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+    if world > 1 and "extra" in line:
+        # the sharded configurations in named keys: whole-job numbers on `world` GPUs, the one-GPU
+        # figures measured by the same processes, and the efficiency = speed-up / world
+        sh = {"tp": world}
+        tg = line["extra"].get("tp_gemm")
+        if isinstance(tg, list):
+            sh["prefill_gemm_28672x8192_g32"] = [
+                {"M": r["M"], "tflops_fused_gather": r.get("tflops_fused_gather"), "tflops_nccl_gather": r["tflops_with_gather"],
+                 "tflops_one_gpu": r["tflops_one_gpu_same_process"], "efficiency_fused_gather": r.get("efficiency_fused_gather"),
+                 "efficiency_nccl_gather": r["efficiency_nccl_gather"], "fused_equals_nccl": r.get("fused_equals_nccl")} for r in tg]
+        ld = line["extra"].get("llama_decode")
+        if isinstance(ld, dict) and "scaling" in ld:
+            sh["llama3_8b_decode"] = ld["scaling"]
+            sh["llama3_8b_decode_parity"] = ld.get("parity")
+        line["sharded"] = sh
     if rank == 0 and world == 1:
         line["cpu_baseline"] = cpu_baseline(args.cpu_seconds)
     return line
@@ -780,6 +816,21 @@ def run_probe(args):
     if kind == "w8a8":
         print(json.dumps({"probe": args.probe, **w8a8_row(device, M, N, K, args.steps, args.warmup)}))
         return
+    if kind == "decode":
+        # decode:B,layers,prompt -- a Llama-3-8B-shaped decoder cut to `layers` blocks: prefill, capture,
+        # then `steps` graph-replayed decode steps (a launch list of one step under a profiler)
+        from tfp8.examples.llama import LlamaConfig, DecodeRunner, build_fp8_llama
+        B, layers, prompt = M, N, K
+        cfg = LlamaConfig(n_layers=layers, max_seq=prompt + 64)
+        model = build_fp8_llama(cfg, device, torch.float16)
+        run = DecodeRunner(model, B)
+        run.prefill(torch.randint(0, cfg.vocab, (B, prompt), device=device))
+        run.capture()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); run.decode(args.steps); e1.record(); torch.cuda.synchronize()
+        print(json.dumps({"probe": args.probe, "batch": B, "layers": layers, "ms_per_step": e0.elapsed_time(e1) / args.steps}))
+        return
     copies = max(1, min(8, int(2.2 * 126e6 / (N * K)) + 1))
     qs = [synth.random_codes(N, K, torch.float8_e4m3fn, seed=c).to(device) for c in range(copies)]
     ng = K // G
@@ -820,9 +871,78 @@ def run_reference(args, rank, world):
     return {"metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "impl": "reference",
-            "config": {"workload": "decode GEMV sweep (BASELINE configs[1]), bounded sample on the host cores"},
+            "config": {"workload": "decode GEMV sweep (M=1, the four Llama-7B layer shapes), bounded sample on the host cores"},
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def run_reference_gpu(args):
+    """The reference's OWN GPU kernels on this GPU, beside this build's: its Python package is
+    imported unmodified from oracle/_ref/tfp8_reference (staged by `make -C oracle` where the
+    reference checkout exists) and compiles its sm_75-era kernels with NVRTC for the device it
+    finds, exactly as it does on the authors' machine. Same inputs, same rotation over distinct
+    weight buffers (> 2x L2), CUDA-event loops, interleaved A/B as the reference's own benches do
+    (tests/perf_decode.py:32-48 there). Prints one JSON line; not part of the default run."""
+    ref = reference_package()
+    if ref is None:
+        print(json.dumps({"impl": "reference-gpu", "unavailable": "oracle/_ref/tfp8_reference is not staged (build where the reference checkout exists)"}))
+        return
+    import tfp8
+    from tfp8 import synth
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    if not ref._ext.available():
+        print(json.dumps({"impl": "reference-gpu", "unavailable": f"the reference's NVRTC kernels did not load: {ref._ext.last_error()}"[:300]}))
+        return
+    peaks = measured_peaks()
+    rows = []
+
+    def ab(make_ref, make_ours, x, copies, rounds=7, inner=20):
+        """Median over rounds of the per-call time of each side, the sides alternating."""
+        ref_layers, our_layers = [make_ref(c) for c in range(copies)], [make_ours(c) for c in range(copies)]
+        for l in ref_layers + our_layers:
+            for _ in range(4):                       # past the NaN-checked calls, kernels compiled
+                l(x)
+        tr, to = [], []
+        for _ in range(rounds):
+            for side, layers, acc in (("ref", ref_layers, tr), ("ours", our_layers, to)):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                for _ in range(inner):
+                    for l in layers:
+                        l(x)
+                e1.record()
+                torch.cuda.synchronize()
+                acc.append(e0.elapsed_time(e1) / 1e3 / (inner * copies))
+        return float(np.median(tr)), float(np.median(to))
+
+    for (N, K) in synth.DECODE_SHAPES:
+        copies = max(2, int(np.ceil(2.2 * 126e6 / (N * K))))
+        qs = [synth.random_codes(N, K, torch.float8_e4m3fn, seed=c).to(device) for c in range(copies)]
+        sc = torch.full((N, 1), 2.0 ** -13, device=device)
+        for M in (1, 8):
+            x = synth.activations(M, K).to(device)
+            t_ref, t_ours = ab(lambda c: ref.FP8Linear.from_fp8_checkpoint(qs[c], sc, None, "e4m3fn", out_dtype=torch.float16),
+                               lambda c: tfp8.FP8Linear.from_fp8_checkpoint(qs[c], sc, None, "e4m3fn", out_dtype=torch.float16), x, copies)
+            b = gemv_bytes(M, N, K, K)
+            rows.append({"op": "FP8Linear.forward", "M": M, "N": N, "K": K, "reference_us": t_ref * 1e6, "ours_us": t_ours * 1e6,
+                         "reference_gbs": b / t_ref / 1e9, "ours_gbs": b / t_ours / 1e9, "speedup": t_ref / t_ours,
+                         "note": "eager calls through each package's own FP8Linear (Python launch overhead included on both sides)"})
+        del qs
+    # prefill-size GEMM: the reference's fused WMMA kernel and its chunked dequant + cuBLAS path
+    N, K, M = 4096, 4096, 2048
+    q = synth.random_codes(N, K, torch.float8_e4m3fn, seed=1).to(device)
+    sc = torch.full((N, 1), 2.0 ** -13, device=device)
+    x = synth.activations(M, K).to(device)
+    for backend in ("fused", "chunked"):
+        t_ref, t_ours = ab(lambda c: ref.FP8Linear.from_fp8_checkpoint(q, sc, None, "e4m3fn", out_dtype=torch.float16, large_m_backend=backend),
+                           lambda c: tfp8.FP8Linear.from_fp8_checkpoint(q, sc, None, "e4m3fn", out_dtype=torch.float16), x, 1, rounds=5, inner=10)
+        fl = 2.0 * M * N * K
+        rows.append({"op": f"FP8Linear.forward (reference large_m_backend={backend})", "M": M, "N": N, "K": K,
+                     "reference_ms": t_ref * 1e3, "ours_ms": t_ours * 1e3, "reference_tflops": fl / t_ref / 1e12,
+                     "ours_tflops": fl / t_ours / 1e12, "speedup": t_ref / t_ours})
+    print(json.dumps({"impl": "reference-gpu", "device": torch.cuda.get_device_name(0), "peaks": peaks, "rows": rows}))
 
 
 def main():
@@ -830,7 +950,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference", "reference-gpu"))
     ap.add_argument("--quick", action="store_true", help="headline only: skip the per-shape / GEMM / codec tables")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-llama", action="store_true", help="skip the Llama-3-8B decode measurement")
@@ -842,6 +962,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.probe:
         run_probe(args)
+        return
+    if args.impl == "reference-gpu":
+        run_reference_gpu(args)
         return
     # The result is ONE line on stdout. Libraries write there too (NCCL prints a version banner
     # when NCCL_DEBUG asks for it), so during the run file descriptor 1 points at stderr and the

@@ -238,17 +238,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: polls (each poll may itself block for a short, hardware-chosen time) and gives
-// up after about two seconds of SM clock, records `status_bit` in the device status word and
-// returns false. No wait in this library is unbounded, so a protocol error ends the kernel
-// instead of hanging the GPU.
+// The same test, but the thread may be suspended by the hardware until the phase completes or
+// `ns` nanoseconds have passed, instead of coming straight back: a waiting warp then costs no
+// issue slots, which on an SM whose other warps are doing the work is the difference between
+// polling and waiting (the tile GEMM at 16 rows spent more than two thirds of its issued
+// instructions in polls).
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
+// Bounded wait: tests once, then waits in suspended polls of up to 20 us each and gives up after
+// about two seconds of SM clock, records `status_bit` in the device status word and returns
+// false. No wait in this library is unbounded, so a protocol error ends the kernel instead of
+// hanging the GPU.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned status_bit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 256; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
         if (clock64() - t0 > (1ll << 32)) break;
     }
     atomicOr(&g_status, status_bit);

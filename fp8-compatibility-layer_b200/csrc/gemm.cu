@@ -1009,9 +1009,12 @@ static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, con
     // order: a parity wait can then never be answered by a phase two completions away.
     p.x_bytes = bn * GM_BK * 2;
     const int budget = GM_SMEM_MAX - 1024 - GM_HEADER;
-    p.ns = GM_NA;
-    static_assert(GM_NA % GM_NG == 0 && GM_NA % 2 == 0, "decoded-tile ring: a multiple of the decode groups and of the issuing threads");
+    // TFP8B_GEMM_NS=<4|6|8> overrides the number of decoded-tile slots (tuning).
+    static const int ns_env = [] { const char* v = getenv("TFP8B_GEMM_NS"); return v ? atoi(v) : 0; }();
+    p.ns = (ns_env == 4 || ns_env == 6 || ns_env == 8) ? ns_env : GM_NA;
+    static_assert(GM_NA % GM_NG == 0 && GM_NA % 2 == 0 && GM_NG == 2, "decoded-tile ring: a multiple of the decode groups and of the issuing threads");
     p.nx = bn >= 256 ? 4 : (bn == 128 ? 6 : GM_MAX_XSLOTS);          // even: two issuing threads walk it with stride 2
+    if (p.ns > 4 && bn >= 64) p.nx = 4;
     const int raw_slot = p.rb * GM_RAW_BYTES;
     const int raw_stride = GM_NG / p.rb;                      // slots between a group's consecutive k-blocks
     // K-group scales of a tile in shared memory (two tiles' worth), where a row's scales are whole
@@ -1021,6 +1024,8 @@ static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, con
         const int row_bytes = (K / G) * (scale_kind == TFP8B_SCALE_UE8M0 ? 1 : 4);
         p.sc_row = (use_cache && G != K && row_bytes % 16 == 0 && row_bytes <= 128 && (reinterpret_cast<uintptr_t>(scale) & 15u) == 0) ? row_bytes : 0;
     }
+    const int min_raw = raw_stride > 2 ? raw_stride : 2;
+    if ((budget - p.ns * GM_A_BYTES - p.nx * p.x_bytes - 2 * GM_BM * p.sc_row) / raw_slot < min_raw) p.sc_row = 0;   // no room at this tile width
     const int sc_bytes = 2 * GM_BM * p.sc_row;
     p.sr = (budget - p.ns * GM_A_BYTES - p.nx * p.x_bytes - sc_bytes) / raw_slot;
     if (p.sr > GM_MAX_SLOTS) p.sr = GM_MAX_SLOTS;

@@ -4,15 +4,17 @@
 //
 // The weight stream is the whole cost (N*K bytes against M*(K+N) activation elements), so the
 // kernel is built around keeping HBM busy from its first to its last microsecond:
-//   * persistent CTAs, one per SM, each walking a list of 16-row weight tiles; K is cut into
-//     stages of 1024 codes that flow through one ring of shared-memory stages which does not
-//     drain between tiles;
-//   * a producer warp moves each stage with 1-D bulk async copies (cp.async.bulk: 16 row pieces of
-//     1 KB, evict-first in L2), completion counted in bytes on an mbarrier -- no registers are
-//     held for data in flight and about 90 KB per SM is always on its way;
+//   * persistent CTAs, one per SM (two resident: this kernel's and its successor's), each walking
+//     a list of 16-row weight tiles; K is cut into stages of 1024 codes that flow through one ring
+//     of shared-memory stages which does not drain between tiles;
+//   * a producer warp moves each stage with ONE 3-D tensor-map load (16 rows x 8 k-blocks of 128
+//     bytes, 128-byte swizzle, evict-first in L2), completion counted in bytes on an mbarrier -- no
+//     registers are held for data in flight. A K that is not a multiple of 128 takes the other
+//     layout: 16 row pieces per stage by 1-D bulk copies into padded rows;
 //   * the activations are copied into shared memory once per CTA when they fit (always for
-//     M = 1), otherwise piecewise with each stage;
-//   * eight consumer warps each take a 128-code slice of a stage: 128-bit shared loads, two
+//     M = 1), otherwise they travel with each stage through a tensor map of their own; two
+//     further instantiations compute them in the kernel instead (residual + RMSNorm, SwiGLU);
+//   * sixteen consumer warps each take a 64-code slice of a stage: 128-bit shared loads, two
 //     codes per conversion instruction (see dec2_f16), products on the tensor cores with
 //     mma.sync.m16n8k16 (16 weight rows x 8 activation rows, FP32 accumulate): at M = 8 the
 //     FP32 FMA pipe could not keep up with HBM3e's byte rate, the MMA makes M irrelevant;
@@ -20,12 +22,13 @@
 //     to bf16 (every FP8 value is exact in both); f32 -> three bf16 terms (24 mantissa bits) and
 //     three MMAs. Nothing is rounded before the FP32 accumulation;
 //   * per-K-group scales multiply each group's partial sum in FP32 (exact for any scale value),
-//     per-channel scales once at the end; the eight partial sums of a tile are added in a fixed
-//     order, so results are deterministic;
+//     per-channel scales once at the end; the sixteen partial sums of a tile are handed to an
+//     epilogue warp through one of two buffers and added in a fixed order, so results are
+//     deterministic and the consumers never wait for the stores;
 //   * programmatic dependent launch: the kernel releases its successor at once and only waits
 //     for its predecessor before it touches activations or outputs, so in a chain of layers the
-//     next layer's weights are already streaming while this one finishes. Weights are never
-//     written by a kernel that releases its successor early, so prefetching them is safe.
+//     next layer's weights are already streaming while this one finishes. (The kernel before a
+//     GEMV in its stream must therefore not write that GEMV's weights: see include/tfp8b.h.)
 // All mbarrier waits are bounded; a wait that runs out sets a status bit and ends the CTA.
 #include <stdlib.h>
 

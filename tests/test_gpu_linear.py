@@ -257,7 +257,7 @@ def test_unsupported_shapes_are_reported():
 
 
 def test_config1_golden(golden_c1):
-    """BASELINE config 1 at full size: 4096x4096 outlier weight, per-channel power-of-two scales,
+    """The CPU-runnable reference configuration at full size: 4096x4096 outlier weight, per-channel power-of-two scales,
     x 1x4096 fp16: codes and scales bit-exact with the reference, output within fp16 rounding."""
     import hashlib
     from tfp8 import FP8Linear, synth

@@ -195,10 +195,15 @@ def test_fp8linear_activation_fp8_switch():
     import torch.nn as nn
     from tfp8 import FP8Config, FP8Linear, _ext, prepare_model
     torch.manual_seed(4)
-    model = nn.Sequential(nn.Linear(1024, 1536), nn.Linear(1536, 1024, bias=False)).half().cuda()
+    class Mlp(nn.Module):                                    # names the planner's LLM rule converts
+        def __init__(self):
+            super().__init__()
+            self.up_proj, self.down_proj = nn.Linear(1024, 1536), nn.Linear(1536, 1024, bias=False)
+
+    model = Mlp().half().cuda()
     prepare_model(model, "llm", FP8Config(profile="llm_safe", weight_group=32, scale_format="ue8m0", activation="fp8", nan_check=False))
-    layer = model[0]
-    assert isinstance(layer, FP8Linear) and layer.activation == "fp8" and isinstance(model[1], FP8Linear)
+    layer = model.up_proj
+    assert isinstance(layer, FP8Linear) and layer.activation == "fp8" and isinstance(model.down_proj, FP8Linear)
     for M in (1, 8, 40, 300):
         x = torch.randn(M, 1024, device="cuda", dtype=torch.float16)
         y = layer(x)
