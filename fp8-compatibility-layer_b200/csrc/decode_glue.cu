@@ -585,8 +585,11 @@ int glue_status(unsigned int* out, cudaStream_t st) {
     return read_and_clear_status(word, out, st);
 }
 
-// Wait limit of the fused all-reduce, in SM clock cycles (about two seconds by default).
-static long long g_ar_wait_cycles = 1ll << 32;
+// Wait limit of the fused all-reduce, in SM clock cycles. The default, about 17 seconds, is far
+// beyond any skew between healthy ranks (a rank's first call can be seconds late: lazy module
+// loading, graph instantiation, a garbage-collection pause on its host thread) and still ends the
+// kernel if a peer is gone.
+static long long g_ar_wait_cycles = 1ll << 35;
 
 static int grid_of(long long work) {
     long long blocks = (work + 255) / 256;

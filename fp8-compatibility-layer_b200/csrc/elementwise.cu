@@ -346,6 +346,27 @@ __global__ void __launch_bounds__(EW_THREADS) quantize_kernel(const T* __restric
     }
 }
 
+// |max| over the 16 values of two 16-byte vectors of 16-bit floats, taken on the packed pairs
+// (the maximum of halves is a half: exact) and widened once. NaNs are ignored, as fmaxf does.
+template <typename T>
+__device__ __forceinline__ float amax16_packed(const uint4 (&v)[2]);
+template <>
+__device__ __forceinline__ float amax16_packed<__half>(const uint4 (&v)[2]) {
+    const __half2* h = reinterpret_cast<const __half2*>(v);
+    __half2 m = __habs2(h[0]);
+#pragma unroll
+    for (int i = 1; i < 8; ++i) m = __hmax2(m, __habs2(h[i]));
+    return fmaxf(__half2float(__low2half(m)), __half2float(__high2half(m)));
+}
+template <>
+__device__ __forceinline__ float amax16_packed<__nv_bfloat16>(const uint4 (&v)[2]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(v);
+    __nv_bfloat162 m = __habs2(h[0]);
+#pragma unroll
+    for (int i = 1; i < 8; ++i) m = __hmax2(m, __habs2(h[i]));
+    return fmaxf(__bfloat162float(__low2bfloat16(m)), __bfloat162float(__high2bfloat16(m)));
+}
+
 // The same quantizer for rows of 16-bit values that fit the registers twice over (K <= 8192):
 // persistent CTAs, each walking rows blockIdx.x, blockIdx.x + gridDim.x, ..., and the loads of a
 // CTA's NEXT row are issued before the current row's three barrier-separated phases (amax, scale,
@@ -373,27 +394,25 @@ __global__ void __launch_bounds__(EW_THREADS) quantize_rows_kernel(const T* __re
     };
     int n = blockIdx.x;
     if (n < N) load_row(n, cur);
-    for (; n < N; n += gridDim.x) {
+    // Two amax / scale buffers, alternating per row: the next row's buffer is cleared during this
+    // row's scale phase, which leaves two CTA barriers per row instead of four.
+    for (int g = threadIdx.x; g < ng; g += blockDim.x) s_amax[g] = 0u;
+    __syncthreads();
+    int buf = 0;
+    for (; n < N; n += gridDim.x, buf ^= 1) {
+        uint32_t* sa = s_amax + buf * ng;
         const int n_next = n + static_cast<int>(gridDim.x);
         if (n_next < N) load_row(n_next, nxt);
-        for (int g = threadIdx.x; g < ng; g += blockDim.x) s_amax[g] = 0u;
-        __syncthreads();
 #pragma unroll
         for (int i = 0; i < R; ++i) {
             const int k = (i * EW_THREADS + static_cast<int>(threadIdx.x)) * 16;
-            if (k < K) {
-                float v[16];
-                load16<T>(reinterpret_cast<const T*>(cur[i]), v);
-                float m = 0.f;
-#pragma unroll
-                for (int t = 0; t < 16; ++t) m = fmaxf(m, fabsf(v[t]));
-                atomicMax(&s_amax[k / G], __float_as_uint(m));
-            }
+            if (k < K) atomicMax(&sa[k / G], __float_as_uint(amax16_packed<T>(cur[i])));
         }
         __syncthreads();
         for (int g = threadIdx.x; g < ng; g += blockDim.x) {
-            const float sc = scale_from_amax(__uint_as_float(s_amax[g]), fmax, pow2);
-            s_amax[g] = __float_as_uint(sc);
+            const float sc = scale_from_amax(__uint_as_float(sa[g]), fmax, pow2);
+            sa[g] = __float_as_uint(sc);
+            s_amax[(buf ^ 1) * ng + g] = 0u;
             const size_t si = static_cast<size_t>(n) * ng + g;
             if (scale_kind == TFP8B_SCALE_UE8M0) reinterpret_cast<uint8_t*>(scale)[si] = static_cast<uint8_t>(__float_as_uint(sc) >> 23);
             else reinterpret_cast<float*>(scale)[si] = sc;
@@ -405,7 +424,7 @@ __global__ void __launch_bounds__(EW_THREADS) quantize_rows_kernel(const T* __re
             if (k < K) {
                 float v[16];
                 load16<T>(reinterpret_cast<const T*>(cur[i]), v);
-                const float sc = __uint_as_float(s_amax[k / G]);
+                const float sc = __uint_as_float(sa[k / G]);
                 const uint32_t sb = __float_as_uint(sc);
                 if ((sb & 0x007FFFFFu) == 0u && sb >= 0x00800000u && sb <= 0x7E800000u) {
                     const float inv = __uint_as_float(0x7F000000u - sb);      // dividing by a power of two, exactly
@@ -418,7 +437,6 @@ __global__ void __launch_bounds__(EW_THREADS) quantize_rows_kernel(const T* __re
                 __stcs(reinterpret_cast<uint4*>(q + static_cast<size_t>(n) * K + k), encode16<FMT>(v, TFP8B_NAN_CAST));
             }
         }
-        __syncthreads();                               // s_amax is rewritten by the next row
 #pragma unroll
         for (int i = 0; i < R; ++i) { cur[i][0] = nxt[i][0]; cur[i][1] = nxt[i][1]; }
     }
@@ -604,7 +622,7 @@ extern "C" int tfp8b_quantize(const void* w, int w_dtype, uint8_t* codes, void* 
     if (held == 1 || held == 2) {
         // 16-bit rows of up to 8192 values: persistent CTAs that keep their next row in flight
         const int grid = N < sm_count() * 4 ? N : sm_count() * 4;      // four resident CTAs per SM at 62 registers
-#define CALL_P(T, F, R) quantize_rows_kernel<T, F, R><<<grid, EW_THREADS, smem, st>>>(static_cast<const T*>(w), codes, scale, scale_kind, N, K, G, pow2)
+#define CALL_P(T, F, R) quantize_rows_kernel<T, F, R><<<grid, EW_THREADS, 2 * smem, st>>>(static_cast<const T*>(w), codes, scale, scale_kind, N, K, G, pow2)
 #define CALL_PF(T, R)                                                   \
         do {                                                            \
             if (fmt == TFP8B_E4M3FN) CALL_P(T, TFP8B_E4M3FN, R); else CALL_P(T, TFP8B_E5M2, R); \

@@ -205,7 +205,13 @@ __device__ __forceinline__ float row_scale_max(const void* scale, size_t row_off
 //   GM_OUT_PUSH    the same, peers served by the push warp from the local copy
 constexpr int GM_OUT_PLAIN = 0, GM_OUT_SPLITK = 1, GM_OUT_WINDOW = 2, GM_OUT_PUSH = 3;
 
-template <int FMT, int OUT>
+// SC: the tile's K-group scales are kept in shared memory (see the decode warps). A template
+// parameter because the two ways of fetching scale ratios want different loop shapes: from global
+// memory they are fetched four of the group's k-blocks ahead and the loop is unrolled by four;
+// from shared memory one k-block ahead is enough, and the four-times smaller loop body matters:
+// the roles of this kernel together are ~7000 instructions, far more than an instruction cache
+// level close to the schedulers holds.
+template <int FMT, int OUT, int SC>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -417,7 +423,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         // K-group of a k-block: (kb * 2 + c / 2) 32-code units / (G / 32); a shift when that is a power of two
         const int g32 = p.G / 32;
         const int g_shift = (g32 & (g32 - 1)) == 0 ? __ffs(g32) - 1 : -1;
-        constexpr int PF = 4;                        // the group's k-blocks whose scale ratios are fetched ahead
+        constexpr int PF = SC ? 1 : 4;               // the group's k-blocks whose scale ratios are fetched ahead
         for (int i = 0; i < my_tiles; ++i) {
             const int n0 = tile_n0(i);
             // per row: 1 / max_g scale (float scales) or the largest exponent byte (UE8M0)
@@ -439,7 +445,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             // of the tile (double-buffered by tile parity: a group may already be in the next tile
             // while the other finishes this one), and the k-loop reads them from there.
             const uint8_t* sc = sc_cache + static_cast<size_t>(i & 1) * GM_BM * p.sc_row;
-            if (ng > 1 && p.sc_row > 0) {
+            if (ng > 1 && SC) {
                 const int vpr = p.sc_row >> 4;                                      // 16-byte vectors per row
                 for (int v = td; v < GM_BM * vpr; v += GM_DEC_THREADS) {
                     const int row = v / vpr, j = v - row * vpr;
@@ -506,7 +512,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     if (ng > 1 && l0 + j < nloc) {
                         const int u32 = (kabs + (l0 + j) * GM_NG) * 2 + (c >> 1);
                         const int gi = min(g_shift >= 0 ? (u32 >> g_shift) : (u32 / g32), ng - 1);
-                        if (p.sc_row > 0) {
+                        if (SC) {
 #pragma unroll
                             for (int h2 = 0; h2 < RPT; ++h2) {
                                 const uint8_t* rowp = sc + (r0 + RSTEP * h2) * p.sc_row;
@@ -840,27 +846,29 @@ static int device_sms(int dev) {
     return sms;
 }
 
-template <int FMT, int OUT>
+template <int FMT, int OUT, int SC>
 static int launch_gemm_as(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, size_t smem, int dev, cudaStream_t st) {
     static unsigned long long configured = 0ull;             // one per instantiation: bit d = device d is set up
     if (dev >= 64 || !((configured >> dev) & 1ull)) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<FMT, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM_MAX);
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<FMT, OUT, SC>, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM_MAX);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm)");
         if (dev < 64) __atomic_fetch_or(&configured, 1ull << dev, __ATOMIC_RELAXED);
     }
     const int sms = device_sms(dev);
     const int grid = p.ntiles < sms ? p.ntiles : sms;
-    gemm_kernel<FMT, OUT><<<grid, GM_THREADS, smem, st>>>(tw, tx, p);
+    gemm_kernel<FMT, OUT, SC><<<grid, GM_THREADS, smem, st>>>(tw, tx, p);
     TFP8B_LAUNCH_CHECK("tfp8b_gemm");
     return TFP8B_OK;
 }
 
 template <int FMT>
 static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, size_t smem, int dev, cudaStream_t st) {
-    if (p.ks > 1) return launch_gemm_as<FMT, GM_OUT_SPLITK>(tw, tx, p, smem, dev, st);
-    if (p.push) return launch_gemm_as<FMT, GM_OUT_PUSH>(tw, tx, p, smem, dev, st);
-    if (p.ndst > 1 || p.ldy != p.N || p.col0 != 0) return launch_gemm_as<FMT, GM_OUT_WINDOW>(tw, tx, p, smem, dev, st);
-    return launch_gemm_as<FMT, GM_OUT_PLAIN>(tw, tx, p, smem, dev, st);
+    if (p.ks > 1) return p.sc_row > 0 ? launch_gemm_as<FMT, GM_OUT_SPLITK, 1>(tw, tx, p, smem, dev, st)
+                                      : launch_gemm_as<FMT, GM_OUT_SPLITK, 0>(tw, tx, p, smem, dev, st);
+    if (p.push) return launch_gemm_as<FMT, GM_OUT_PUSH, 0>(tw, tx, p, smem, dev, st);
+    if (p.ndst > 1 || p.ldy != p.N || p.col0 != 0) return launch_gemm_as<FMT, GM_OUT_WINDOW, 0>(tw, tx, p, smem, dev, st);
+    return p.sc_row > 0 ? launch_gemm_as<FMT, GM_OUT_PLAIN, 1>(tw, tx, p, smem, dev, st)
+                        : launch_gemm_as<FMT, GM_OUT_PLAIN, 0>(tw, tx, p, smem, dev, st);
 }
 
 // ------------------------------------------------------------------ scratch for tfp8b_linear_static
@@ -1022,7 +1030,9 @@ static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, con
     {
         static const int use_cache = [] { const char* v = getenv("TFP8B_GEMM_SCALE_CACHE"); return !(v && v[0] == '0'); }();
         const int row_bytes = (K / G) * (scale_kind == TFP8B_SCALE_UE8M0 ? 1 : 4);
-        p.sc_row = (use_cache && G != K && row_bytes % 16 == 0 && row_bytes <= 128 && (reinterpret_cast<uintptr_t>(scale) & 15u) == 0) ? row_bytes : 0;
+        const bool plain_form = n_dst == 1 && ldy == N && col0 == 0;           // the other output forms keep the global path
+        p.sc_row = (use_cache && plain_form && G != K && row_bytes % 16 == 0 && row_bytes <= 128 &&
+                    (reinterpret_cast<uintptr_t>(scale) & 15u) == 0) ? row_bytes : 0;
     }
     const int min_raw = raw_stride > 2 ? raw_stride : 2;
     if ((budget - p.ns * GM_A_BYTES - p.nx * p.x_bytes - 2 * GM_BM * p.sc_row) / raw_slot < min_raw) p.sc_row = 0;   // no room at this tile width

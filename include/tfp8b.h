@@ -312,8 +312,8 @@ TFP8B_API int tfp8b_allreduce_add_rmsnorm(void* x, const float* partial, const v
                   unsigned int* state, int rank, int world, int max_rows, tfp8b_stream_t stream);
 
 /* Sets how long (SM clock cycles, > 0) a CTA of tfp8b_allreduce_add_rmsnorm waits for a peer's flag
- * before it gives up, for all later calls of this process; returns the previous limit (about two
- * seconds by default; cycles <= 0 only queries). When the wait runs out the kernel does not sum
+ * before it gives up, for all later calls of this process; returns the previous limit (2^35 cycles,
+ * about 17 seconds, by default; cycles <= 0 only queries). When the wait runs out the kernel does not sum
  * stale data: it sets the row to NaN in x and out, raises TFP8B_STATUS_GLUE_WAIT and returns.
  * No counterpart in the reference. */
 TFP8B_API long long tfp8b_allreduce_wait_limit(long long cycles);
