@@ -36,16 +36,31 @@
 
 namespace tfp8b {
 
-constexpr int MX_BM = 128, MX_BN = 128, MX_BK = 128;
-constexpr int MX_STAGES = 6;
+constexpr int MX_BM = 128, MX_BK = 128;
+constexpr int MX_MAX_STAGES = 6;
 constexpr int MX_THREADS = 256;                         // warp 0 producer, warp 1 MMA, warps 4..7 epilogue
-constexpr int MX_TILE_BYTES = MX_BM * MX_BK;            // 16 KB of codes
-constexpr int MX_SF_BYTES = 512;
-constexpr int MX_STAGE_BYTES = 2 * MX_TILE_BYTES + 2 * MX_SF_BYTES;      // 33 KB (a multiple of 1024)
+constexpr int MX_A_BYTES = MX_BM * MX_BK;               // 16 KB of activation codes per stage
+constexpr int MX_SF_BYTES = 512;                        // one scale chunk: 128 rows x 4 blocks
 constexpr int MX_HEADER = 1024;
-constexpr int MX_SMEM = 1024 + MX_HEADER + MX_STAGES * MX_STAGE_BYTES;
-constexpr int MX_TMEM_COLS = 512;                        // 2 x 128 accumulator columns + 8 scale columns per stage
-constexpr int MX_SF_COL0 = 2 * MX_BN;
+constexpr int MX_TMEM_COLS = 512;
+// Per tile width BN (weight rows per tile = accumulator columns). 192 is the widest that leaves
+// room in tensor memory for two accumulators AND the scale columns (2 x 192 + 5 x 12 = 444 of 512
+// columns; with 256 the two accumulators alone take all 512): the wider the tile, the fewer bytes
+// cross from L2 per FLOP, and that crossing is what bounds this kernel. A 192-row tile starts at a
+// multiple of 64 rows, so it reads two 128-row scale chunks and its scale columns begin at column
+// 0 or 2 of the first chunk.
+template <int BN>
+struct MxCfg {
+    static constexpr int B_BYTES = BN * MX_BK;
+    static constexpr int SFB_CHUNKS = BN > 128 ? 2 : 1;
+    static constexpr int STAGE_BYTES = (MX_A_BYTES + B_BYTES + MX_SF_BYTES * (1 + SFB_CHUNKS) + 1023) / 1024 * 1024;
+    static constexpr int STAGES = BN > 128 ? 5 : 6;
+    static constexpr int SMEM = 1024 + MX_HEADER + STAGES * STAGE_BYTES;
+    static constexpr int SF_COLS = 4 + 4 * SFB_CHUNKS;       // tensor-memory columns of one stage's scales
+    static constexpr int SF_COL0 = 2 * BN;
+    static_assert(SF_COL0 + SF_COLS * STAGES <= MX_TMEM_COLS, "tensor memory: accumulators + scale columns");
+    static_assert(SMEM <= 232448 && STAGES <= MX_MAX_STAGES, "shared memory");
+};
 
 constexpr int MXM_BLOCK_E8 = 0, MXM_ROWCOL = 1, MXM_BLOCK_F32 = 2;
 
@@ -55,16 +70,15 @@ struct MxParams {
     const float* bias;
     void* y;
     int M, N, K, y_dt, a_fmt, w_fmt, scale_kind;
-    int m_tiles, ntiles, nkt;
+    int m_tiles, ntiles, nkt, n_chunks;     // n_chunks: 128-row scale chunks of the weight
 };
 
 struct MxHeader {
-    uint64_t full[MX_STAGES], empty[MX_STAGES];
+    uint64_t full[MX_MAX_STAGES], empty[MX_MAX_STAGES];
     uint64_t acc_full[2], acc_empty[2];
     uint32_t tmem_base;
 };
 static_assert(sizeof(MxHeader) <= MX_HEADER, "header too large");
-static_assert(MX_SF_COL0 + 8 * MX_STAGES <= MX_TMEM_COLS, "tensor memory: accumulators + scale columns");
 
 // ------------------------------------------------------------------ tcgen05 wrappers (this file's own)
 __device__ __forceinline__ void mx_tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
@@ -123,13 +137,16 @@ __device__ __forceinline__ uint64_t mx_desc_sf(uint32_t smem_addr) {
 __device__ __forceinline__ float mx_scale(const void* s, size_t i, int kind) { return load_scale(s, i, kind); }
 
 // ------------------------------------------------------------------ the kernel
-template <int MODE>
+template <int MODE, int BN>
 __global__ void __launch_bounds__(MX_THREADS, 1)
 gemm_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w, const MxParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     MxHeader* hd = reinterpret_cast<MxHeader*>(smem);
     uint8_t* stages = smem + MX_HEADER;
+    using C = MxCfg<BN>;
+    constexpr int MX_BN = BN, MX_STAGES = C::STAGES, MX_STAGE_BYTES = C::STAGE_BYTES;
+    constexpr int OFF_B = MX_A_BYTES, OFF_SFA = MX_A_BYTES + C::B_BYTES, OFF_SFB = OFF_SFA + MX_SF_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int my_tiles = (p.ntiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
     auto tile_of = [&](int i) { return static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x); };
@@ -169,21 +186,27 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             int slot = 0;
             uint32_t phase = 1;
             bool ok = true, first_pass = true;
-            const uint32_t tx = 2 * MX_TILE_BYTES + (MODE == MXM_BLOCK_E8 ? 2 * MX_SF_BYTES : 0);
             for (int i = 0; i < my_tiles && ok; ++i) {
                 const int m0 = tile_m0(i), n0 = tile_n0(i);
+                // the weight tile's scale chunks: one, or two for a 192-row tile (the second may lie
+                // beyond the last chunk of the weight: then it is not fetched, its columns are unused)
+                const int c0 = n0 / 128;
+                const bool two = C::SFB_CHUNKS == 2 && c0 + 1 < p.n_chunks;
+                const uint32_t tx = MX_A_BYTES + C::B_BYTES + (MODE == MXM_BLOCK_E8 ? MX_SF_BYTES * (two ? 3u : 2u) : 0u);
                 for (int kt = 0; kt < p.nkt; ++kt) {
                     if (!first_pass && !mbar_wait(smem_u32(&hd->empty[slot]), phase, STATUS_GEMM_WAIT)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&hd->full[slot]);
                     uint8_t* st = stages + static_cast<size_t>(slot) * MX_STAGE_BYTES;
                     mbar_expect_tx(bar, tx);
                     tma_load_2d(smem_u32(st), &tm_a, kt * MX_BK, m0, bar, pol_a);
-                    tma_load_2d(smem_u32(st + MX_TILE_BYTES), &tm_w, kt * MX_BK, n0, bar, pol_w);
+                    tma_load_2d(smem_u32(st + OFF_B), &tm_w, kt * MX_BK, n0, bar, pol_w);
                     if (MODE == MXM_BLOCK_E8) {
-                        bulk_g2s(smem_u32(st + 2 * MX_TILE_BYTES), p.sfa + (static_cast<size_t>(m0 / MX_BM) * p.nkt + kt) * MX_SF_BYTES,
+                        bulk_g2s(smem_u32(st + OFF_SFA), p.sfa + (static_cast<size_t>(m0 / MX_BM) * p.nkt + kt) * MX_SF_BYTES,
                                  MX_SF_BYTES, bar, pol_a);
-                        bulk_g2s(smem_u32(st + 2 * MX_TILE_BYTES + MX_SF_BYTES),
-                                 p.sfw + (static_cast<size_t>(n0 / MX_BN) * p.nkt + kt) * MX_SF_BYTES, MX_SF_BYTES, bar, pol_w);
+                        bulk_g2s(smem_u32(st + OFF_SFB), p.sfw + (static_cast<size_t>(c0) * p.nkt + kt) * MX_SF_BYTES, MX_SF_BYTES, bar, pol_w);
+                        if (two)
+                            bulk_g2s(smem_u32(st + OFF_SFB + MX_SF_BYTES), p.sfw + (static_cast<size_t>(c0 + 1) * p.nkt + kt) * MX_SF_BYTES,
+                                     MX_SF_BYTES, bar, pol_w);
                     }
                     if (++slot == MX_STAGES) { slot = 0; phase ^= 1u; first_pass = false; }
                 }
@@ -221,11 +244,14 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     if (!ok) break;
                     mx_fence_after();
                     const uint32_t st = smem_u32(stages + static_cast<size_t>(slot) * MX_STAGE_BYTES);
-                    const uint64_t da = mx_desc_sw128(st), db = mx_desc_sw128(st + MX_TILE_BYTES);
+                    const uint64_t da = mx_desc_sw128(st), db = mx_desc_sw128(st + OFF_B);
                     if (MODE == MXM_BLOCK_E8) {
-                        const uint32_t tsfa = tmem_base + static_cast<uint32_t>(MX_SF_COL0 + slot * 8), tsfb = tsfa + 4u;
-                        mx_cp_sf(tsfa, mx_desc_sf(st + 2 * MX_TILE_BYTES));
-                        mx_cp_sf(tsfb, mx_desc_sf(st + 2 * MX_TILE_BYTES + MX_SF_BYTES));
+                        const uint32_t tsfa = tmem_base + static_cast<uint32_t>(C::SF_COL0 + slot * C::SF_COLS);
+                        mx_cp_sf(tsfa, mx_desc_sf(st + OFF_SFA));
+                        mx_cp_sf(tsfa + 4u, mx_desc_sf(st + OFF_SFB));
+                        if (C::SFB_CHUNKS == 2) mx_cp_sf(tsfa + 8u, mx_desc_sf(st + OFF_SFB + MX_SF_BYTES));
+                        // the tile's first weight row inside its first chunk: 32 rows per scale column
+                        const uint32_t tsfb = tsfa + 4u + static_cast<uint32_t>((tile_n0(i) & 127) >> 5);
 #pragma unroll
                         for (uint32_t kb = 0; kb < 4; ++kb) {
                             // block kb of the k-tile: byte kb of the scale columns, for both operands
@@ -416,19 +442,34 @@ static int mx_device_sms() {
     return n;
 }
 
-template <int MODE>
-static int launch_mx(const CUtensorMap& ta, const CUtensorMap& tw, const MxParams& p, cudaStream_t st) {
+template <int MODE, int BN>
+static int launch_mx(const void* a_codes, const void* w_codes, MxParams p, cudaStream_t st) {
+    using C = MxCfg<BN>;
     static unsigned long long configured = 0ull;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (dev >= 64 || !((configured >> dev) & 1ull)) {
-        e = cudaFuncSetAttribute(gemm_mx_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, MX_SMEM);
+        e = cudaFuncSetAttribute(gemm_mx_kernel<MODE, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm_mx)");
         if (dev < 64) __atomic_fetch_or(&configured, 1ull << dev, __ATOMIC_RELAXED);
     }
+    p.m_tiles = (p.M + MX_BM - 1) / MX_BM;
+    p.ntiles = p.m_tiles * ((p.N + BN - 1) / BN);
+    p.n_chunks = (p.N + 127) / 128;
+    CUtensorMap ta, tw;
+    {
+        const cuuint64_t da[2] = {static_cast<cuuint64_t>(p.K), static_cast<cuuint64_t>(p.M)};
+        const cuuint64_t dw[2] = {static_cast<cuuint64_t>(p.K), static_cast<cuuint64_t>(p.N)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.K)};
+        const cuuint32_t box_a[2] = {MX_BK, MX_BM}, box_w[2] = {MX_BK, BN};
+        int rc = encode_tensor_map(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a_codes, da, strides, box_a, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != TFP8B_OK) return rc;
+        rc = encode_tensor_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w_codes, dw, strides, box_w, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != TFP8B_OK) return rc;
+    }
     const int sms = mx_device_sms();
-    gemm_mx_kernel<MODE><<<p.ntiles < sms ? p.ntiles : sms, MX_THREADS, MX_SMEM, st>>>(ta, tw, p);
+    gemm_mx_kernel<MODE, BN><<<p.ntiles < sms ? p.ntiles : sms, MX_THREADS, C::SMEM, st>>>(ta, tw, p);
     TFP8B_LAUNCH_CHECK("tfp8b_gemm_w8a8");
     return TFP8B_OK;
 }
@@ -511,22 +552,14 @@ extern "C" int tfp8b_gemm_w8a8(const uint8_t* a_codes, const void* a_scale, int 
     p.sfa = static_cast<const uint8_t*>(a_scale); p.sfw = static_cast<const uint8_t*>(w_scale);
     p.bias = bias; p.y = y;
     p.M = M; p.N = N; p.K = K; p.y_dt = y_dtype; p.a_fmt = a_fmt; p.w_fmt = w_fmt; p.scale_kind = scale_kind;
-    p.m_tiles = (M + MX_BM - 1) / MX_BM;
-    p.ntiles = p.m_tiles * ((N + MX_BN - 1) / MX_BN);
     p.nkt = K / MX_BK;
-    CUtensorMap ta, tw;
-    {
-        const cuuint64_t da[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
-        const cuuint64_t dw[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(N)};
-        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K)};
-        const cuuint32_t box[2] = {MX_BK, MX_BM};
-        int rc = encode_tensor_map(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a_codes, da, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (rc != TFP8B_OK) return rc;
-        rc = encode_tensor_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w_codes, dw, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (rc != TFP8B_OK) return rc;
-    }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (scale_mode == TFP8B_W8A8_ROWCOL) return launch_mx<MXM_ROWCOL>(ta, tw, p, st);
-    if (scale_kind == TFP8B_SCALE_UE8M0) return launch_mx<MXM_BLOCK_E8>(ta, tw, p, st);
-    return launch_mx<MXM_BLOCK_F32>(ta, tw, p, st);
+    // TFP8B_W8A8_BN=128 selects the narrower tile for the tensor-core forms (tuning / comparison).
+    static const int bn_env = [] { const char* v = getenv("TFP8B_W8A8_BN"); return v ? atoi(v) : 0; }();
+    const bool wide = bn_env != 128;
+    if (scale_mode == TFP8B_W8A8_ROWCOL)
+        return wide ? launch_mx<MXM_ROWCOL, 192>(a_codes, w_codes, p, st) : launch_mx<MXM_ROWCOL, 128>(a_codes, w_codes, p, st);
+    if (scale_kind == TFP8B_SCALE_UE8M0)
+        return wide ? launch_mx<MXM_BLOCK_E8, 192>(a_codes, w_codes, p, st) : launch_mx<MXM_BLOCK_E8, 128>(a_codes, w_codes, p, st);
+    return launch_mx<MXM_BLOCK_F32, 128>(a_codes, w_codes, p, st);      // accumulates a tile's columns in registers: 128 of them
 }

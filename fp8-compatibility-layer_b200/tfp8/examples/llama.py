@@ -302,6 +302,43 @@ def build_fp8_llama(cfg: LlamaConfig, device, dtype=torch.float16, fp8: FP8Confi
     return model
 
 
+def reorder_fused_rows_like_tp(model: Llama, tp: int):
+    """Re-orders, in place, the rows of the fused QKV and gate/up projections of an UNSHARDED model
+    so that it computes what a `tp`-way tensor-parallel build of the same seed computes.
+
+    The fused projections keep their rows rank by rank ([q_r | k_r | v_r], [gate_r | up_r]), so the
+    same random matrix means a different model for every tensor-parallel size: rank r's block of a
+    tp-way build holds heads that an unsharded build would read as something else. Gathering the
+    q parts of all ranks, then the k parts, then the v parts (and gate parts, then up parts) gives
+    the one-GPU model that is mathematically the same as the sharded one -- what a parity check
+    between the two needs."""
+    cfg = model.cfg
+    if model.tp != 1 or cfg.n_heads % tp or cfg.n_kv_heads % tp or cfg.ffn % tp:
+        raise ValueError("needs an unsharded model and a tensor-parallel size that divides heads, KV heads and FFN")
+    hd = cfg.head_dim
+    hq, hk, f = cfg.n_heads // tp * hd, cfg.n_kv_heads // tp * hd, cfg.ffn // tp
+
+    def perm_of(parts, per, dev):
+        idx, off = [], 0
+        offs = []
+        for n in parts:
+            offs.append(off)
+            off += n
+        for o, n in zip(offs, parts):
+            for r in range(tp):
+                idx.append(torch.arange(r * per + o, r * per + o + n, device=dev))
+        return torch.cat(idx)
+
+    for blk in model.layers:
+        for lin, parts in ((blk.qkv_proj, (hq, hk, hk)), (blk.gate_up_proj, (f, f))):
+            perm = perm_of(parts, sum(parts), lin.qweight.device)
+            lin.qweight.copy_(lin.qweight[perm])
+            lin.weight_scale.copy_(lin.weight_scale[perm])
+            if lin.bias_f32 is not None:
+                lin.bias_f32.copy_(lin.bias_f32[perm])
+    return model
+
+
 class DecodeRunner:
     """Prefill, then greedy decode with the whole step (all layers, lm_head, argmax, position bump)
     captured in one CUDA graph."""

@@ -3,11 +3,14 @@ library's own kernels for the exchanges. Skipped unless the machine shows at lea
 
   * tfp8b_allreduce_add_rmsnorm (peer stores + per-row flags, slots double-buffered by call
     parity) against NCCL all_reduce -> cast -> tfp8b_add_rmsnorm: many calls in a row with changing
-    row counts, eagerly and replayed from a CUDA graph -- equal bits (two ranks: one float32 add);
+    row counts, eagerly and replayed from a CUDA graph -- the updated residual equal bit for bit
+    (two ranks: one float32 add, one rounding), the normed output within one rounding of the
+    activation type (the two kernels group the sum of squares differently);
   * the gather fused into the tile GEMM's epilogue against NCCL all_gather_into_tensor: equal bits;
   * the tensor-parallel decoder: greedy tokens with the fused all-reduce equal those with NCCL
-    all-reduces, and the logits agree with the unsharded model on one GPU within the tolerance of a
-    different float32 summation order.
+    all-reduces, logits within a rounding; and both agree with the mathematically identical
+    unsharded model on one GPU (same seed, fused rows re-ordered as the sharded build reads them)
+    within the tolerance of a different float32 summation order.
 No rank fails or leaves in these tests; every wait in the kernels is bounded, the process group
 has a two-minute timeout, and the parent gives the two children four minutes in all.
 
@@ -40,7 +43,7 @@ def _worker(rank, world, port, results):
     import torch.distributed as dist
     import torch.nn as nn
     from tfp8 import FP8Config, FP8Linear, _ext
-    from tfp8.examples.llama import TINY_HD128, DecodeRunner, build_fp8_llama
+    from tfp8.examples.llama import TINY_HD128, DecodeRunner, build_fp8_llama, reorder_fused_rows_like_tp
     from tfp8.parallel import ColumnParallelFP8Linear, FusedAllReduceNorm
     import datetime
     import gc
@@ -55,6 +58,10 @@ def _worker(rank, world, port, results):
         g = torch.Generator(device=dev).manual_seed(100 + rank)        # different partials per rank
         gs = torch.Generator(device=dev).manual_seed(7)                # same residual / weight on every rank
         w = (1 + 0.1 * torch.randn(dim, device=dev, generator=gs)).half()
+        def close(a, b):                # one rounding of fp16 apart at most (plus a floor for values near zero)
+            a, b = a.float(), b.float()
+            return bool(((a - b).abs() <= 2.0 ** -9 * b.abs() + 1e-5).all())
+
         ok = True
         for call, rows in enumerate((1, 8, 3, 8, 2, 5, 1, 8, 8)):
             x = torch.randn(rows, 1, dim, device=dev, generator=gs).half()
@@ -63,7 +70,7 @@ def _worker(rank, world, port, results):
             dist.all_reduce(red)
             want = _ext.add_rmsnorm(x_ref, red.half(), w, 1e-5)
             got = comm.add_rmsnorm(x, part, w, 1e-5)
-            ok &= torch.equal(x, x_ref) and torch.equal(got, want)
+            ok &= torch.equal(x, x_ref) and close(got, want)
         out["allreduce_eager"] = bool(ok)
         # replayed from a graph, several times: the sequence number advances on the device
         x = torch.randn(4, 1, dim, device=dev, generator=gs).half()
@@ -83,7 +90,7 @@ def _worker(rank, world, port, results):
                 gr.replay()
                 x_ref = x0.clone()
                 want = _ext.add_rmsnorm(x_ref, red.half(), w, 1e-5)
-                ok &= torch.equal(x, x_ref) and torch.equal(got, want)
+                ok &= torch.equal(x, x_ref) and close(got, want)
         torch.cuda.current_stream().wait_stream(s)
         out["allreduce_graph"] = bool(ok)
 
@@ -103,7 +110,8 @@ def _worker(rank, world, port, results):
         cfg = TINY_HD128
         fp8 = FP8Config(min_features=64, nan_check=False)
         tp_model = build_fp8_llama(cfg, dev, torch.float16, fp8=fp8, seed=11)
-        one = build_fp8_llama(cfg, dev, torch.float16, fp8=fp8, seed=11, tp=1)      # the unsharded model, same weights
+        # the unsharded model with the same weights, its fused rows in the order the sharded build reads them
+        one = reorder_fused_rows_like_tp(build_fp8_llama(cfg, dev, torch.float16, fp8=fp8, seed=11, tp=1), world)
         toks = torch.randint(0, cfg.vocab, (2, 12), device=dev, generator=gs)
         runs = {}
         for name, fused in (("fused", True), ("nccl", False)):
@@ -117,14 +125,15 @@ def _worker(rank, world, port, results):
         r1 = DecodeRunner(one, 2)
         pre1 = r1.prefill(toks).float()
         out["tp_tokens_equal"] = bool(torch.equal(runs["fused"][1], runs["nccl"][1]))
-        out["tp_logits_equal"] = bool(torch.equal(runs["fused"][2], runs["nccl"][2]))
+        out["tp_logits_close"] = float((runs["fused"][2] - runs["nccl"][2]).abs().max() / runs["nccl"][2].abs().max())
         scale = float(pre1.abs().max())
         out["tp_vs_one_gpu"] = float((runs["fused"][0] - pre1).abs().max() / scale)
         # teacher-forced: the one-GPU model on the tokens the tensor-parallel run produced
         first = runs["fused"][0].argmax(-1)
         seq = torch.cat([toks, first, runs["fused"][1][:, :-1]], 1)
         r1b = DecodeRunner(one, 2)
-        ref = one(seq, torch.arange(seq.shape[1], device=dev), prefill=True)[:, 12:].float()
+        with torch.no_grad():
+            ref = one(seq, torch.arange(seq.shape[1], device=dev), prefill=True)[:, 12:].float()
         out["tp_decode_vs_one_gpu"] = float((runs["fused"][2] - ref).abs().max() / float(ref.abs().max()))
         out["status"] = _ext.device_status()
         results[rank] = out                     # the verdict is with the parent before anything is torn down
@@ -168,6 +177,6 @@ def test_two_ranks_fused_exchanges_match_nccl():
         print(rank, r)
         assert r["allreduce_eager"] and r["allreduce_graph"], (rank, r)
         assert r["fused_gather"], (rank, r)
-        assert r["tp_tokens_equal"] and r["tp_logits_equal"], (rank, r)
+        assert r["tp_tokens_equal"] and r["tp_logits_close"] <= 1e-2, (rank, r)
         assert r["tp_vs_one_gpu"] <= 2e-2 and r["tp_decode_vs_one_gpu"] <= 2e-2, (rank, r)
         assert r["status"] == 0
