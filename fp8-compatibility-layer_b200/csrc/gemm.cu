@@ -445,6 +445,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             // of the tile (double-buffered by tile parity: a group may already be in the next tile
             // while the other finishes this one), and the k-loop reads them from there.
             const uint8_t* sc = sc_cache + static_cast<size_t>(i & 1) * GM_BM * p.sc_row;
+            // UE8M0 scales cached for the tile: whether EVERY ratio of the warp's rows is a normal
+            // fp16 power of two (exponent bytes within 14 of the row maximum) is known once per
+            // tile, and the k-loop needs neither the range test nor a vote per k-block.
+            bool tile_fast = true;
             if (ng > 1 && SC) {
                 const int vpr = p.sc_row >> 4;                                      // 16-byte vectors per row
                 for (int v = td; v < GM_BM * vpr; v += GM_DEC_THREADS) {
@@ -473,7 +477,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     }
                     binv[h2] = e8 ? __uint_as_float(bm) : (mx > 0.f ? 1.f / mx : 0.f);
                     bmax[h2] = static_cast<int>(bm);
+                    if (e8) {                                 // smallest exponent byte of the row: decides the fold form for the tile
+                        uint32_t bn = 255u;
+                        for (int j = 0; j < vpr; ++j) {
+                            const uint4 t = *reinterpret_cast<const uint4*>(rowp + j * 16);
+                            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const uint32_t m4 = __vminu4(w[e], __byte_perm(w[e], 0u, 0x4321));
+                                bn = min(bn, min(m4 & 0xFFu, (m4 >> 16) & 0xFFu));
+                            }
+                        }
+                        tile_fast = tile_fast && static_cast<int>(bm) - static_cast<int>(bn) <= 14;
+                    }
                 }
+                tile_fast = e8 && __all_sync(0xffffffffu, tile_fast);
             } else if (ng > 1) {
                 // row maxima of the K-group scales: GM_DEC_THREADS / 128 threads share a row
                 constexpr int TPR = GM_DEC_THREADS / GM_BM;
@@ -570,14 +588,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         // multiply and one fp16 rounding); the choice is made for the whole warp.
                         // UE8M0 factors are powers of two by construction: 2^e, e <= 0, whose fp16
                         // bit pattern is (e + 15) << 10 while e >= -14.
-                        bool pow2 = true;
+                        bool fast;
+                        if (SC && e8) {
+                            fast = tile_fast;
+                        } else {
+                            bool pow2 = true;
 #pragma unroll
-                        for (int h2 = 0; h2 < RPT; ++h2) {
-                            const uint32_t rb = rcur[j][h2];
-                            pow2 = pow2 && (e8 ? static_cast<int>(rb) >= -14
-                                               : ((rb & 0x007FFFFFu) == 0u && rb >= 0x38800000u && rb <= 0x47000000u));
+                            for (int h2 = 0; h2 < RPT; ++h2) {
+                                const uint32_t rb = rcur[j][h2];
+                                pow2 = pow2 && (e8 ? static_cast<int>(rb) >= -14
+                                                   : ((rb & 0x007FFFFFu) == 0u && rb >= 0x38800000u && rb <= 0x47000000u));
+                            }
+                            fast = __all_sync(0xffffffffu, pow2);
                         }
-                        if (__all_sync(0xffffffffu, pow2)) {
+                        if (fast) {
 #pragma unroll
                             for (int h2 = 0; h2 < RPT; ++h2) {
                                 const uint32_t rb = rcur[j][h2];

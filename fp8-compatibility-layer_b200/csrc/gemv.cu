@@ -738,9 +738,14 @@ static int gemv_setup(GemvSetup& g, int x_dtype, const uint8_t* codes, const voi
     const bool tma = K % 128 == 0 && !force_bulk;
     const int nchunks = (K + GV_KS - 1) / GV_KS;
     const int xpad = smode == 2 ? 64 : 16;
+    // Tuning knobs: TFP8B_GEMV_XRES_MAX=<bytes> lowers the size up to which activations stay resident
+    // (larger ones then travel with the stages); TFP8B_GEMV_STREAM_SMALL=1 gives that streaming
+    // form the small footprint (two CTAs per SM) instead of the large one.
+    static const int xres_max = [] { const char* v = getenv("TFP8B_GEMV_XRES_MAX"); const int n = v ? atoi(v) : 0; return n > 0 && n < GV_XRES_MAX ? n : GV_XRES_MAX; }();
+    static const int stream_small = [] { const char* v = getenv("TFP8B_GEMV_STREAM_SMALL"); return v && v[0] == '1'; }();
     if (tma) {
         p.wstage_bytes = GV_ROWS * GV_KS;
-        p.x_resident = (M * (K * xsz + xpad) <= GV_XRES_MAX) ? 1 : 0;
+        p.x_resident = (M * (K * xsz + xpad) <= xres_max) ? 1 : 0;
         p.xpitch = K * xsz + xpad;                                      // resident rows only
         p.xres_bytes = p.x_resident ? ((M * p.xpitch + 1023) & ~1023) : 0;
         const int xstage = p.x_resident ? 0 : M * GV_KS * xsz;          // a multiple of 1024
@@ -762,7 +767,7 @@ static int gemv_setup(GemvSetup& g, int x_dtype, const uint8_t* codes, const voi
     }
     TFP8B_REQUIRE(xmode == 0 || (p.x_resident && tma), TFP8B_ERR_UNSUPPORTED,
                   "tfp8b_gemv: computed activations need K %% 128 == 0 and M * K small enough to stay resident (M=%d K=%d)", M, K);
-    const int target = (p.x_resident && p.xres_bytes <= GV_XRES_SMALL) ? GV_SMEM_TARGET : GV_SMEM_LARGE;
+    const int target = ((p.x_resident && p.xres_bytes <= GV_XRES_SMALL) || (!p.x_resident && tma && stream_small)) ? GV_SMEM_TARGET : GV_SMEM_LARGE;
     int S = (target - 1024 - GV_HEADER - p.xres_bytes) / p.stage_bytes;
     S = S < 2 ? 2 : (S > GV_MAX_STAGES ? GV_MAX_STAGES : S);
     const int sms = sm_count_of_current_device();
