@@ -76,7 +76,9 @@ struct GemmParams {
     int x_bytes;         // one activation tile: BN x 64 fp16
     int nmma;            // MMA-issuing threads; thread t takes k-blocks t, t + nmma, ... into its own accumulator
     int ks, nkbu;        // split-K: every tile is cut into ks units of nkbu k-blocks; ntiles counts units
-    float* ws;           // ks > 1: FP32 [M, N] workspace the units add their partial tiles into
+    int span, span_total, nkbt;   // split-K by spans (span > 0): CTA b owns k-blocks [b * span, (b + 1) * span) of the
+                         // tile-major sequence of all span_total k-blocks; a tile has nkbt of them
+    float* ws;           // split-K: FP32 [M, N] workspace the units add their partial tiles into
 };
 
 struct GemmHeader {
@@ -225,19 +227,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     uint8_t* sc_cache = raw_ring + static_cast<size_t>(p.sr) * p.rb * GM_RAW_BYTES;   // [2][128 rows][sc_row bytes]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nkb = p.nkbu;                               // k-blocks of one unit of work (the whole K unless split)
     const int raw_slot_bytes = p.rb * GM_RAW_BYTES;
     const int ng = p.K / p.G;
-    const int my_tiles = (p.ntiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
     // Unit i of this CTA is global unit blockIdx.x + i * gridDim.x = (tile, K part), the part the
     // fast index; within the tiles the activation-row tile is the fast index, so CTAs that run
     // together share one weight stripe through L2.
-    auto unit_of = [&](int i) { return static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x); };
+    // Split-K by spans: the k-blocks of all tiles form one tile-major sequence, and CTA b owns
+    // [b * span, (b + 1) * span) of it, so every SM works equally long whatever the number of
+    // tiles. The span is cut at tile boundaries into this CTA's units (at most three while
+    // span >= a tile's k-blocks): the end of one tile, whole tiles, the start of another.
     constexpr bool SPLIT = OUT == GM_OUT_SPLITK;
-    auto tile_of = [&](int i) { return SPLIT ? unit_of(i) / p.ks : unit_of(i); };
+    const bool spans = SPLIT && p.span > 0;
+    const int sp_lo = spans ? static_cast<int>(blockIdx.x) * p.span : 0;
+    const int sp_hi = spans ? min(sp_lo + p.span, p.span_total) : 0;
+    const int sp_t0 = spans ? sp_lo / p.nkbt : 0;
+    const int my_tiles = spans ? (sp_hi > sp_lo ? (sp_hi - 1) / p.nkbt - sp_t0 + 1 : 0)
+                               : (p.ntiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+    auto unit_of = [&](int i) { return static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x); };
+    auto tile_of = [&](int i) { return spans ? sp_t0 + i : (SPLIT ? unit_of(i) / p.ks : unit_of(i)); };
     auto tile_m0 = [&](int i) { return (tile_of(i) % p.m_tiles) * p.BN; };
     auto tile_n0 = [&](int i) { return (tile_of(i) / p.m_tiles) * GM_BM; };
-    auto unit_kb0 = [&](int i) { return SPLIT ? (unit_of(i) % p.ks) * nkb : 0; };  // first k-block of the unit
+    // first k-block of the unit inside its tile, its number of k-blocks, and the k-blocks of the
+    // CTA's earlier units
+    auto unit_kb0 = [&](int i) { return spans ? max(sp_lo - (sp_t0 + i) * p.nkbt, 0) : (SPLIT ? (unit_of(i) % p.ks) * p.nkbu : 0); };
+    auto unit_len = [&](int i) { return spans ? min(sp_hi, (sp_t0 + i + 1) * p.nkbt) - max(sp_lo, (sp_t0 + i) * p.nkbt) : p.nkbu; };
+    auto unit_base = [&](int i) { return spans ? max((sp_t0 + i) * p.nkbt - sp_lo, 0) : i * p.nkbu; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.ns; ++s) {
@@ -282,10 +296,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             uint32_t phase = 1;               // ring position (no divisions): the first pass over the ring does not wait
             bool ok = true, first_pass = true;
             for (int i = 0; i < my_tiles && ok; ++i) {
-                const int n0 = tile_n0(i), kb0 = unit_kb0(i);
+                const int n0 = tile_n0(i), kb0 = unit_kb0(i), nkb = unit_len(i);
                 for (int kb = 0; kb < nkb; kb += p.rb) {
                     if (!first_pass && !mbar_wait(smem_u32(&hd->raw_empty[slot]), phase, STATUS_GEMM_WAIT)) { ok = false; break; }
-                    GM_TRACE(0, i * nkb + kb);
+                    GM_TRACE(0, unit_base(i) + kb);
                     const uint32_t bar = smem_u32(&hd->raw_full[slot]);
                     const uint32_t dst = smem_u32(raw_ring + static_cast<size_t>(slot) * raw_slot_bytes);
                     mbar_expect_tx(bar, static_cast<uint32_t>(raw_slot_bytes));
@@ -304,7 +318,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             uint32_t phase = 1;
             bool ok = true, first_pass = true;
             for (int i = 0; i < my_tiles && ok; ++i) {
-                const int m0 = tile_m0(i), kb0 = unit_kb0(i);
+                const int m0 = tile_m0(i), kb0 = unit_kb0(i), nkb = unit_len(i);
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!first_pass && !mbar_wait(smem_u32(&hd->x_empty[slot]), phase, STATUS_GEMM_WAIT)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&hd->x_full[slot]);
@@ -347,12 +361,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 if (!ok) break;
                 const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>((buf * p.nmma + t) * p.BN);
                 uint32_t accumulate = 0u;
-                int kb = next - i * nkb;
+                const int nkb = unit_len(i), base = unit_base(i);
+                int kb = next - base;
                 for (; kb < nkb; kb += p.nmma) {
-                    GM_TRACE(5, i * nkb + kb);
+                    GM_TRACE(5, base + kb);
                     if (!ready) ok = mbar_wait(full0 + a_bar, a_par, STATUS_GEMM_WAIT) && mbar_wait(xfull0 + x_bar, x_par, STATUS_GEMM_WAIT);
                     if (!ok) break;
-                    GM_TRACE(3, i * nkb + kb);
+                    GM_TRACE(3, base + kb);
                     tc_fence_after();
                     tc_mma_f16(tmem_acc, da, db, idesc, accumulate);
                     tc_mma_f16(tmem_acc, da + 2, db + 2, idesc, 1u);
@@ -368,13 +383,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     da = umma_desc_sw128(stages_u32 + a_off); db = umma_desc_sw128(xring_u32 + x_off);
                     tc_mma_f16(tmem_acc, da_cur + 4, db_cur + 4, idesc, 1u);
                     tc_mma_f16(tmem_acc, da_cur + 6, db_cur + 6, idesc, 1u);
-                    GM_TRACE(6, i * nkb + kb);
+                    GM_TRACE(6, base + kb);
                     tc_commit(cur_empty);             // both slots are free once these MMAs have read them
                     tc_commit(cur_xempty);
-                    GM_TRACE(4, i * nkb + kb);
+                    GM_TRACE(4, base + kb);
                     accumulate = 1u;
                 }
-                next = i * nkb + kb;
+                next = base + kb;
                 if (ok) tc_commit(smem_u32(&hd->acc_full[buf]));
             }
         }
@@ -514,7 +529,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 }
             }
             // this group's k-blocks inside the tile: first, first + NG, ... (nloc of them)
-            const int first = done - i * nkb;
+            const int nkb = unit_len(i), ubase = unit_base(i);
+            const int first = done - ubase;
             const int nloc = first < nkb ? (nkb - first + GM_NG - 1) / GM_NG : 0;
             const int kabs = unit_kb0(i) + first;                                  // absolute k-block of the group's first one
             const uint32_t half_off = (p.rb == 2 && (kabs & 1)) ? 64u : 0u;        // NG is even: the parity of kb is fixed
@@ -567,7 +583,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_rfull, rpar, STATUS_GEMM_WAIT));
                     if (ok && !fresh) ok = __all_sync(0xffffffffu, mbar_wait(bar_empty, apar ^ 1u, STATUS_GEMM_WAIT));
                     if (!ok) continue;
-                    if (tg == 0) GM_TRACE(1, i * nkb + first + (l0 + j) * GM_NG);
+                    if (tg == 0) GM_TRACE(1, ubase + first + (l0 + j) * GM_NG);
                     // all loads, then all conversions, then all stores: the rows of a thread are
                     // independent, and kept apart like this their latencies overlap
                     uint32_t h[RPT][8];
@@ -635,10 +651,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         gm_sts128(st + aoff0[h2], h[h2][0], h[h2][1], h[h2][2], h[h2][3]);
                         gm_sts128(st + aoff1[h2], h[h2][4], h[h2][5], h[h2][6], h[h2][7]);
                     }
-                    if (tg == 0) GM_TRACE(7, i * nkb + first + (l0 + j) * GM_NG);
+                    if (tg == 0) GM_TRACE(7, ubase + first + (l0 + j) * GM_NG);
                     fence_proxy_async_smem();        // generic-proxy stores -> visible to the tensor core
                     __syncwarp();
-                    if (tg == 0) GM_TRACE(2, i * nkb + first + (l0 + j) * GM_NG);
+                    if (tg == 0) GM_TRACE(2, ubase + first + (l0 + j) * GM_NG);
                     if (lane == 0) {
                         mbar_arrive(bar_full);
                         mbar_arrive(bar_rempty);     // this warp has read its part of the raw slot
@@ -1009,6 +1025,7 @@ static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, con
     // plus a fixed turn-over per unit; it splits only where that clearly pays (fewer tiles than
     // half the SMs and a long K).
     p.ks = 1; p.nkbu = nkb; p.ws = nullptr;
+    p.span = 0; p.span_total = 0; p.nkbt = nkb;
     int dev = 0;
     {
         cudaError_t e = cudaGetDevice(&dev);
@@ -1027,6 +1044,26 @@ static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, con
                 cost(ks) * 6 < cost(1) * 5)                     // only for a clear gain: the split costs determinism
                 best = ks;
         if (best > 1) { p.ks = best; p.nkbu = nkb / best; p.ws = workspace; p.ntiles *= best; }
+        // At least one tile per SM, but a tile count that fills the last round badly (224 tiles on
+        // 148 SMs: two rounds, the second half empty): split by spans instead. The k-blocks of all
+        // tiles, tile after tile, are dealt out in equal contiguous spans, one per SM; a span is at
+        // least one tile long, so a tile gets its sum from at most two CTAs and the result does not
+        // depend on which of them adds first. Span ends are even: raw slots hold k-block pairs,
+        // and two issuing threads take alternate k-blocks.
+        static const int use_spans = [] { const char* v = getenv("TFP8B_GEMM_SPANS"); return !(v && v[0] == '0'); }();
+        if (use_spans && best == 1 && p.ntiles >= sms && nkb % 2 == 0 && K % GM_BK == 0) {
+            const long long total = static_cast<long long>(p.ntiles) * nkb;
+            long long span = (total + sms - 1) / sms;
+            span += span & 1;
+            const long long rounds = (p.ntiles + sms - 1) / sms;
+            // a span costs its k-blocks, two turn-overs and the two extra passes
+            if (total < (1ll << 30) && span >= nkb && (span + 2 * 4 + EXTRA_PASSES / 2) * 8 < rounds * nkb * 7) {
+                p.span = static_cast<int>(span); p.span_total = static_cast<int>(total); p.nkbt = nkb;
+                p.ks = 2;                                    // marks the split forms below: workspace, final pass
+                p.ws = workspace;
+                p.ntiles = static_cast<int>((total + span - 1) / span);   // = CTAs
+            }
+        }
     }
     p.nmma = (bn <= 128 && p.nkbu >= 4) ? 2 : 1;
     p.tmem_cols = 2 * p.nmma * bn < 32 ? 32 : 2 * p.nmma * bn;

@@ -282,8 +282,12 @@ TFP8B_API int tfp8b_gemm_scatter(const void* x16, const float* xs, const uint8_t
  * run on different SMs, adds their partial results into the workspace (atomic adds: the last
  * bits of a result can differ from run to run) and applies activation scale and bias in a final
  * pass; whether and how far it splits follows a cost model, and TFP8B_GEMM_SPLITK=0 in the
- * environment turns it off. Without a split the workspace is not touched and the result is
- * tfp8b_gemm's, bit for bit. No counterpart in the reference. */
+ * environment turns it off. With at least one tile per SM but a badly filled last round (224
+ * tiles on 148 SMs) it splits by spans instead: the k-blocks of all tiles, tile after tile, are
+ * dealt out in equal contiguous spans, one per SM; a tile then gets its sum from at most two
+ * CTAs, so this form gives the same bits on every run (TFP8B_GEMM_SPANS=0 turns it off).
+ * Without a split the workspace is not touched and the result is tfp8b_gemm's, bit for bit.
+ * No counterpart in the reference. */
 TFP8B_API int tfp8b_gemm_splitk(const void* x16, const float* xs, const uint8_t* codes, const void* scale,
                   int scale_kind, const float* bias, void* y, int y_dtype, int M, int N, int K, int G,
                   int fmt, float* workspace, long long workspace_floats, tfp8b_stream_t stream);

@@ -147,6 +147,36 @@ def test_split_k_matches_whole_k():
         assert torch.equal(y_none, y_whole)
 
 
+def test_split_k_by_spans_full_width():
+    """28672 weight rows are 224 tiles for 148 SMs: with a workspace the library deals the k-blocks
+    of all tiles out in equal spans (a tile may get its sum from two CTAs). Against the whole-K
+    kernel on the same inputs: within float32 rounding; the same bits on every run (two addends
+    commute); a ragged last tile and M that is no multiple of 16 included."""
+    from tfp8 import _ext
+    lib, st = _ext.load(), torch.cuda.current_stream().cuda_stream
+    torch.manual_seed(11)
+    K, G = 8192, 128
+    for (M, N) in ((16, 28672), (40, 28600), (64, 28672)):
+        codes = torch.randint(0, 256, (N, K), dtype=torch.uint8, device="cuda")
+        codes[(codes & 0x7F) == 0x7F] = 0x30                           # no NaN codes
+        e8 = torch.randint(110, 122, (N, K // G), dtype=torch.uint8, device="cuda")
+        bias = torch.randn(N, device="cuda")
+        x = torch.randn(M, K, device="cuda", dtype=torch.float16)
+        x16, xs = _ext.prepare_activations(x)
+        ws = torch.empty(M * N, dtype=torch.float32, device="cuda")
+        args = (x16.data_ptr(), xs.data_ptr(), codes.data_ptr(), e8.data_ptr(), 1, bias.data_ptr())
+        tail = (2, M, N, K, G, 0)
+        outs = [torch.empty(M, N, dtype=torch.float32, device="cuda") for _ in range(3)]
+        assert lib.tfp8b_gemm(*args, outs[0].data_ptr(), *tail, st) == 0
+        for y in outs[1:]:
+            ws.fill_(float("nan"))                                      # the library clears what it uses
+            assert lib.tfp8b_gemm_splitk(*args, y.data_ptr(), *tail, ws.data_ptr(), ws.numel(), st) == 0
+        torch.cuda.synchronize()
+        assert _ext.device_status() == 0
+        assert torch.allclose(outs[1], outs[0], rtol=2e-5, atol=2e-5 * float(outs[0].abs().max()))
+        assert torch.equal(outs[1], outs[2])
+
+
 def test_folded_group_scales():
     """Random codes, scales spanning 2^-20: power-of-two scales must stay at FP32-accumulation
     error, arbitrary scales within one fp16 rounding of the folded weight."""
