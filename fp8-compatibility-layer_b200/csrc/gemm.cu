@@ -52,7 +52,7 @@ constexpr int GM_EPI_WARP0 = GM_DEC_WARP0 + GM_DEC_WARPS;
 constexpr int GM_THREADS = (GM_EPI_WARP0 + 4) * 32;
 constexpr int GM_MAX_SLOTS = 8;     // per ring (decoded tiles, raw codes)
 constexpr int GM_MAX_XSLOTS = 8;    // activation ring
-constexpr int GM_NA = 4;            // decoded-tile slots: the groups' tiles in decode, the one in the MMA, one spare
+constexpr int GM_NA = GM_NG == 4 ? 8 : 4;   // decoded-tile slots: the groups' tiles in decode, the one in the MMA, one spare
 constexpr int GM_MAX_DST = 8;       // output destinations of one launch (one per GPU of a tensor-parallel group)
 constexpr int GM_HEADER = 2048;     // barriers, TMEM base, per-row scale reciprocals
 constexpr int GM_A_BYTES = GM_BM * GM_BK * 2;    // decoded fp16 tile
@@ -87,6 +87,7 @@ struct GemmHeader {
     uint64_t x_full[GM_MAX_XSLOTS], x_empty[GM_MAX_XSLOTS];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
+    uint64_t sc_full[2], sc_empty[2];   // the tile's K-group scales in shared memory, double-buffered by unit parity
     uint32_t tmem_base;
     uint32_t tiles_stored;    // epilogue warps that have finished writing a tile to the local output (4 per tile)
     float binv[2][GM_BM];   // per weight row: 1 / max_g scale[n,g], double-buffered by tile parity
@@ -94,11 +95,12 @@ struct GemmHeader {
 static_assert(sizeof(GemmHeader) <= GM_HEADER, "header too large");
 
 // Build with -DTFP8B_GM_TRACE to record, for CTA 0, the SM clock at which each role passes each
-// k-block (a diagnostic for pipeline tuning; the array is read with cudaMemcpyFromSymbol). Row 0
+// k-block (a diagnostic for pipeline tuning; the array is read with cudaMemcpyFromSymbol; rows 8
+// and 9: when each raw slot's copy, and each k-block's MMAs, were seen complete by an idle warp). Row 0
 // also holds, at indices 250 - 255: kernel entry, end of set-up, first epilogue's start and end,
 // (unused), TMEM release.
 #ifdef TFP8B_GM_TRACE
-__device__ long long g_trace[8][256];
+__device__ long long g_trace[10][256];
 #define GM_TRACE(ev, idx) do { if (blockIdx.x == 0 && (idx) < 256) g_trace[ev][idx] = clock64(); } while (0)
 #else
 #define GM_TRACE(ev, idx) do { } while (0)
@@ -269,6 +271,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&hd->acc_full[b]), p.nmma);
             mbar_init(smem_u32(&hd->acc_empty[b]), 4);
+            mbar_init(smem_u32(&hd->sc_full[b]), 1);                    // the scale copy (bytes counted)
+            mbar_init(smem_u32(&hd->sc_empty[b]), GM_DEC_WARPS);
         }
         hd->tiles_stored = 0u;
         mbar_fence_init();
@@ -297,6 +301,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             bool ok = true, first_pass = true;
             for (int i = 0; i < my_tiles && ok; ++i) {
                 const int n0 = tile_n0(i), kb0 = unit_kb0(i), nkb = unit_len(i);
+                if (SC) {
+                    // The K-group scales of the unit's weight rows, one bulk copy into the buffer of
+                    // the unit's parity, issued before the unit's codes: a dozen k-blocks ahead of
+                    // the decode warps, which then never wait for a scale. (Fetched by the decode
+                    // warps themselves at the start of a tile, the loads -- demand misses queued
+                    // behind the megabytes of codes this kernel keeps in flight -- cost 5 us per tile.)
+                    const int b = i & 1;
+                    if (i >= 2 && !mbar_wait(smem_u32(&hd->sc_empty[b]), static_cast<uint32_t>(((i >> 1) - 1) & 1), STATUS_GEMM_WAIT)) { ok = false; break; }
+                    const uint32_t bytes = static_cast<uint32_t>(min(GM_BM, p.N - n0) * p.sc_row);
+                    const uint32_t bar = smem_u32(&hd->sc_full[b]);
+                    mbar_expect_tx(bar, bytes);
+                    bulk_g2s(smem_u32(sc_cache + static_cast<size_t>(b) * GM_BM * p.sc_row),
+                             reinterpret_cast<const uint8_t*>(p.scale) + static_cast<size_t>(n0) * p.sc_row, bytes, bar, l2_policy_evict_normal());
+                }
                 for (int kb = 0; kb < nkb; kb += p.rb) {
                     if (!first_pass && !mbar_wait(smem_u32(&hd->raw_empty[slot]), phase, STATUS_GEMM_WAIT)) { ok = false; break; }
                     GM_TRACE(0, unit_base(i) + kb);
@@ -456,56 +474,57 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             // measured, it comes back about 2.4 us later, and with the ratios fetched eight k-blocks
             // ahead that latency -- not HBM bandwidth, not the tensor core -- set the pace of narrow
             // tiles (0.3 us per k-block whatever the width). So where a row's scales are short
-            // enough, the decode warps copy the tile's scales into shared memory once, at the start
-            // of the tile (double-buffered by tile parity: a group may already be in the next tile
-            // while the other finishes this one), and the k-loop reads them from there.
+            // enough, the producer copies the unit's scales into shared memory ahead of its codes
+            // (double-buffered by unit parity: a group may already be in the next unit while the
+            // other finishes this one), and the k-loop reads them from there. Rows past N (the last
+            // tile) read the last row's scales.
             const uint8_t* sc = sc_cache + static_cast<size_t>(i & 1) * GM_BM * p.sc_row;
+            uint32_t sc_off[RPT];                                                   // this thread's rows in it
+#pragma unroll
+            for (int h2 = 0; h2 < RPT; ++h2) sc_off[h2] = static_cast<uint32_t>(min(r0 + RSTEP * h2, p.N - 1 - n0) * p.sc_row);
             // UE8M0 scales cached for the tile: whether EVERY ratio of the warp's rows is a normal
             // fp16 power of two (exponent bytes within 14 of the row maximum) is known once per
             // tile, and the k-loop needs neither the range test nor a vote per k-block.
             bool tile_fast = true;
             if (ng > 1 && SC) {
                 const int vpr = p.sc_row >> 4;                                      // 16-byte vectors per row
-                for (int v = td; v < GM_BM * vpr; v += GM_DEC_THREADS) {
-                    const int row = v / vpr, j = v - row * vpr;
-                    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.scale) + static_cast<size_t>(min(n0 + row, p.N - 1)) * p.sc_row + j * 16;
-                    *reinterpret_cast<uint4*>(const_cast<uint8_t*>(sc) + row * p.sc_row + j * 16) = __ldg(reinterpret_cast<const uint4*>(src));
-                }
-                named_barrier_sync(1, GM_DEC_THREADS);
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->sc_full[i & 1]), static_cast<uint32_t>((i >> 1) & 1), STATUS_GEMM_WAIT));
+                if (tg == 0) GM_TRACE(1, 200 + 2 * i);
+                // Row maximum (and, UE8M0, minimum) of the scales: the four threads that share a
+                // row (c = 0..3, neighbouring lanes) take every fourth 16-byte piece and combine by
+                // shuffles; bytes are reduced four at a time.
 #pragma unroll
                 for (int h2 = 0; h2 < RPT; ++h2) {
-                    const uint8_t* rowp = sc + (r0 + RSTEP * h2) * p.sc_row;
+                    const uint8_t* rowp = sc + sc_off[h2];
                     float mx = 0.f;
-                    uint32_t bm = 0u;
-                    for (int j = 0; j < vpr; ++j) {
+                    uint32_t m4 = 0u, n4 = 0xFFFFFFFFu;
+                    for (int j = c; j < vpr; j += 4) {
                         const uint4 t = *reinterpret_cast<const uint4*>(rowp + j * 16);
-                        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            if (e8) {
-                                const uint32_t m4 = __vmaxu4(w[e], __byte_perm(w[e], 0u, 0x4321));
-                                bm = max(bm, max(m4 & 0xFFu, (m4 >> 16) & 0xFFu));
-                            } else {
-                                mx = fmaxf(mx, __uint_as_float(w[e]));
-                            }
+                        if (e8) {
+                            m4 = __vmaxu4(m4, __vmaxu4(__vmaxu4(t.x, t.y), __vmaxu4(t.z, t.w)));
+                            n4 = __vminu4(n4, __vminu4(__vminu4(t.x, t.y), __vminu4(t.z, t.w)));
+                        } else {
+                            mx = fmaxf(mx, fmaxf(fmaxf(__uint_as_float(t.x), __uint_as_float(t.y)), fmaxf(__uint_as_float(t.z), __uint_as_float(t.w))));
                         }
                     }
+#pragma unroll
+                    for (int o = 1; o < 4; o <<= 1) {
+                        if (e8) {
+                            m4 = __vmaxu4(m4, __shfl_xor_sync(0xffffffffu, m4, o));
+                            n4 = __vminu4(n4, __shfl_xor_sync(0xffffffffu, n4, o));
+                        } else {
+                            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                        }
+                    }
+                    m4 = __vmaxu4(m4, m4 >> 16); m4 = __vmaxu4(m4, m4 >> 8);
+                    n4 = __vminu4(n4, n4 >> 16); n4 = __vminu4(n4, (n4 >> 8) | 0xFF000000u);
+                    const uint32_t bm = m4 & 0xFFu, bn = n4 & 0xFFu;
                     binv[h2] = e8 ? __uint_as_float(bm) : (mx > 0.f ? 1.f / mx : 0.f);
                     bmax[h2] = static_cast<int>(bm);
-                    if (e8) {                                 // smallest exponent byte of the row: decides the fold form for the tile
-                        uint32_t bn = 255u;
-                        for (int j = 0; j < vpr; ++j) {
-                            const uint4 t = *reinterpret_cast<const uint4*>(rowp + j * 16);
-                            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const uint32_t m4 = __vminu4(w[e], __byte_perm(w[e], 0u, 0x4321));
-                                bn = min(bn, min(m4 & 0xFFu, (m4 >> 16) & 0xFFu));
-                            }
-                        }
-                        tile_fast = tile_fast && static_cast<int>(bm) - static_cast<int>(bn) <= 14;
-                    }
+                    // smallest exponent byte of the row against the largest: decides the fold form for the tile
+                    if (e8) tile_fast = tile_fast && static_cast<int>(bm) - static_cast<int>(bn) <= 14;
                 }
+                if (tg == 0) GM_TRACE(1, 201 + 2 * i);
                 tile_fast = e8 && __all_sync(0xffffffffu, tile_fast);
             } else if (ng > 1) {
                 // row maxima of the K-group scales: GM_DEC_THREADS / 128 threads share a row
@@ -549,7 +568,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         if (SC) {
 #pragma unroll
                             for (int h2 = 0; h2 < RPT; ++h2) {
-                                const uint8_t* rowp = sc + (r0 + RSTEP * h2) * p.sc_row;
+                                const uint8_t* rowp = sc + sc_off[h2];
                                 if (e8) dst[j][h2] = static_cast<uint32_t>(static_cast<int>(rowp[gi]) - bmax[h2]);
                                 else dst[j][h2] = __float_as_uint(reinterpret_cast<const float*>(rowp)[gi] * binv[h2]);
                             }
@@ -665,6 +684,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 #pragma unroll
                     for (int h2 = 0; h2 < RPT; ++h2) rcur[j][h2] = rnext[j][h2];
             }
+            if (SC) {                                    // this warp has read the unit's scales for the last time
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&hd->sc_empty[i & 1]));
+            }
         }
     } else if (OUT == GM_OUT_PUSH && warp == 3) {
         // ---------------------------------------------------------------- push warp (fused gather)
@@ -722,6 +745,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         const bool wide16 = OUT == GM_OUT_PLAIN && p.y_dt != TFP8B_F32 && (p.N & 7) == 0 && (reinterpret_cast<uintptr_t>(y0) & 15u) == 0;
         const bool b0 = lane & 1, b1 = lane & 2, b2 = lane & 4;
         bool ok = true;
+#ifdef TFP8B_GM_TRACE
+        // Two of these warps, idle until the first unit's accumulator is complete, watch that
+        // unit's barriers: row 8 = when each raw slot's copy landed, row 9 = when the MMAs of each
+        // k-block had finished (its decoded tile was free again).
+        if (blockIdx.x == 0 && my_tiles > 0) {
+            const int total = unit_len(0);
+            if (warp == GM_EPI_WARP0) {
+                int slot = 0;
+                uint32_t phase = 0;
+                for (int n = 0; n < total && n < 256; n += p.rb) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->raw_full[slot]), phase, STATUS_GEMM_WAIT))) break;
+                    if (lane == 0) g_trace[8][n] = clock64();
+                    if (++slot == p.sr) { slot = 0; phase ^= 1u; }
+                }
+            } else if (warp == GM_EPI_WARP0 + 1) {
+                for (int n = 0; n < total && n < 256; ++n) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&hd->empty[n % p.ns]), static_cast<uint32_t>((n / p.ns) & 1), STATUS_GEMM_WAIT))) break;
+                    if (lane == 0) g_trace[9][n] = clock64();
+                }
+            }
+        }
+#endif
         for (int i = 0; i < my_tiles; ++i) {
             const int buf = i & 1;
             const int m0 = tile_m0(i), n0 = tile_n0(i);
@@ -1034,9 +1079,9 @@ static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, con
     const int sms = device_sms(dev);
     static const int use_splitk = [] { const char* v = getenv("TFP8B_GEMM_SPLITK"); return !(v && v[0] == '0'); }();
     if (use_splitk && workspace && n_dst == 1 && p.m_tiles == 1 && workspace_floats >= static_cast<long long>(M) * N) {
-        // measured on B200: a unit costs about 32 k-blocks of turn-over (scale scan, pipeline fill
-        // and drain, atomics), and the extra memset + final pass as much again
-        constexpr int TURNOVER = 32, EXTRA_PASSES = 32;
+        // measured on B200: a unit costs about 8 k-blocks of turn-over (scale scan, pipeline fill
+        // and drain, atomics), and the extra memset + final pass about 16
+        constexpr int TURNOVER = 8, EXTRA_PASSES = 16;
         auto cost = [&](int ks) { return ((p.ntiles * ks + sms - 1) / sms) * (nkb / ks + TURNOVER) + (ks > 1 ? EXTRA_PASSES : 0); };
         int best = 1;
         for (int ks = 2; ks <= 16; ks <<= 1)
@@ -1056,8 +1101,8 @@ static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, con
             long long span = (total + sms - 1) / sms;
             span += span & 1;
             const long long rounds = (p.ntiles + sms - 1) / sms;
-            // a span costs its k-blocks, two turn-overs and the two extra passes
-            if (total < (1ll << 30) && span >= nkb && (span + 2 * 4 + EXTRA_PASSES / 2) * 8 < rounds * nkb * 7) {
+            // a span costs its k-blocks, two more turn-overs than a whole tile and the two extra passes
+            if (total < (1ll << 30) && span >= nkb && (span + 2 * TURNOVER + EXTRA_PASSES) * 20 < rounds * nkb * 19) {
                 p.span = static_cast<int>(span); p.span_total = static_cast<int>(total); p.nkbt = nkb;
                 p.ks = 2;                                    // marks the split forms below: workspace, final pass
                 p.ws = workspace;
@@ -1081,7 +1126,7 @@ static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, con
     // TFP8B_GEMM_NS=<4|6|8> overrides the number of decoded-tile slots (tuning).
     static const int ns_env = [] { const char* v = getenv("TFP8B_GEMM_NS"); return v ? atoi(v) : 0; }();
     p.ns = (ns_env == 4 || ns_env == 6 || ns_env == 8) ? ns_env : GM_NA;
-    static_assert(GM_NA % GM_NG == 0 && GM_NA % 2 == 0 && GM_NG == 2, "decoded-tile ring: a multiple of the decode groups and of the issuing threads");
+    static_assert(GM_NA % GM_NG == 0 && GM_NA % 2 == 0, "decoded-tile ring: a multiple of the decode groups and of the issuing threads");
     p.nx = bn >= 256 ? 4 : (bn == 128 ? 6 : GM_MAX_XSLOTS);          // even: two issuing threads walk it with stride 2
     if (p.ns > 4 && bn >= 64) p.nx = 4;
     const int raw_slot = p.rb * GM_RAW_BYTES;
