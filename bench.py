@@ -640,6 +640,25 @@ def llama_decode_measurements(device, peaks, world, batches=(1, 4, 8), prompt=20
     keep = {}
     rows = _decode_rows(model, device, peaks, world, batches, prompt, new_tokens, stream_bytes, keep=keep)
     result["runs"] = rows
+    if world == 1:
+        # The same model and workload with the KV cache held as FP8 codes + one scale per token and KV
+        # head (FP8Config(kv_cache="fp8")): the decode attention then reads half the bytes. Beside it,
+        # for a like-for-like comparison of the cache formats, the library's attention kernel over the
+        # 16-bit cache (the default rows above use torch's attention).
+        cfg = LLAMA3_8B
+        def kv_bytes(B, per_elem):        # K and V of every layer, read once per step at mid-run length
+            return 2 * cfg.n_layers * cfg.n_kv_heads * (prompt + new_tokens // 2) * B * (cfg.head_dim * per_elem + (4 if per_elem == 1 else 0))
+        model.attn_kernel = True
+        result["runs_attn_kernel_fp16_cache"] = _decode_rows(model, device, peaks, world, batches, prompt, new_tokens, stream_bytes)
+        model.attn_kernel, model.kv_fmt = False, "e4m3fn"
+        keep8 = {}
+        result["runs_kv_cache_fp8"] = _decode_rows(model, device, peaks, world, batches, prompt, new_tokens, stream_bytes, keep=keep8)
+        model.kv_fmt = None
+        for r16, r8 in zip(result["runs_attn_kernel_fp16_cache"], result["runs_kv_cache_fp8"]):
+            r16["kv_bytes_per_step"], r8["kv_bytes_per_step"] = kv_bytes(r16["batch"], 2), kv_bytes(r8["batch"], 1)
+            pre16, _ = keep[r8["batch"]]
+            pre8, _ = keep8[r8["batch"]]
+            r8["prefill_logits_cosine_vs_fp16_cache"] = float(torch.nn.functional.cosine_similarity(pre8, pre16, dim=-1).min())
     if world > 1:
         # scaling against the one-GPU run of this process
         result["scaling"] = [{"batch": r["batch"], "tp": world, "decode_tok_s": r["decode_tok_s"], "one_gpu_decode_tok_s": o["decode_tok_s"],

@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <float.h>
 #include <stdint.h>
 
 #include "../../include/tfp8b.h"
@@ -213,6 +214,31 @@ __host__ __device__ __forceinline__ uint32_t encode1(float x, int nan_mode) {
 
 __host__ __device__ __forceinline__ uint32_t encode1(float x, int fmt, int nan_mode) {
     return fmt == TFP8B_E5M2 ? encode1<TFP8B_E5M2>(x, nan_mode) : encode1<TFP8B_E4M3FN>(x, nan_mode);
+}
+
+// Two floats -> two codes (lo in bits 0-7) by the conversion instruction: round to nearest even,
+// saturate to the largest finite code (+-inf included). A NaN comes back as some NaN code of the
+// format, never as a finite one, which is all `encode16` relies on.
+template <int FMT>
+__device__ __forceinline__ uint32_t enc2_hw(float lo, float hi) {
+    unsigned short r;
+    if (FMT == TFP8B_E4M3FN) asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// Scale of a group from its largest magnitude, the rule of the reference's quantize_weight
+// (tfp8/quantize.py:27-33): amax / fmax, at least the smallest normal float, rounded up to a power
+// of two on request; 1 for an all-zero group.
+__device__ __forceinline__ float scale_from_amax(float amax, float fmax, int pow2) {
+    if (amax == 0.f) return 1.f;
+    float s = fmaxf(__fdiv_rn(amax, fmax), FLT_MIN);
+    if (pow2) {
+        uint32_t u = __float_as_uint(s);
+        if (u & 0x007FFFFFu) u = (u & 0x7F800000u) + 0x00800000u;   // next power of two
+        s = __uint_as_float(u);
+    }
+    return s;
 }
 
 // ------------------------------------------------------------------ mbarrier / bulk copy

@@ -8,7 +8,9 @@
 //   add_rmsnorm    residual += delta, then RMSNorm of the residual -- one launch instead of 2;
 //   argmax         greedy token choice over the vocabulary, one CTA per row;
 //   attn_decode    one-query attention over the static KV cache (grouped-query heads), the KV
-//                  range split across CTAs and merged by a second small kernel.
+//                  range split across CTAs and merged by a second small kernel;
+//   rope_kv_store_fp8 / attn_decode_fp8  the same two over an FP8 KV cache (codes + one scale per
+//                  token and KV head): half the cache, half the bytes an attention step reads.
 // All are plain bandwidth- or latency-bound kernels on 16-bit activations. They are launched
 // with programmatic stream serialization and release their dependents at once: the FP8 GEMV
 // that follows starts streaming its weights while the helper is still running, and waits for
@@ -71,6 +73,81 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const T* __restrict__ qkv,
         else dst = v_cache + ((static_cast<size_t>(b) * KV + (h - H - KV)) * max_seq + p) * hd;
         *reinterpret_cast<P*>(dst + 2 * ip) = pack2(o1.x, o1.y, P());
         *reinterpret_cast<P*>(dst + half + 2 * ip) = pack2(o2.x, o2.y, P());
+    }
+}
+
+// The same step for an FP8 KV cache: K (rotated) and V are rounded to the activation type, as the
+// 16-bit cache would hold them, and then quantized per token and KV head exactly as
+// quantize_weight quantizes a row (tfp8/quantize.py:15-36 of the reference: power-of-two scale
+// 2^ceil(log2(amax / fmax)), 1 for an all-zero row, round to nearest even, saturating): codes
+// k_codes / v_codes u8 [B, KV, max_seq, hd] and one FP32 scale per (sequence, KV head, position).
+// One warp per (sequence, token, head); hd = 128: lane l holds elements 2l, 2l + 1 of both halves.
+template <typename T, int FMT>
+__global__ void __launch_bounds__(256) rope_kv_fp8_kernel(const T* __restrict__ qkv, const long long* __restrict__ pos,
+                                                          const float* __restrict__ cosv, const float* __restrict__ sinv,
+                                                          T* __restrict__ q_out, uint8_t* __restrict__ k_codes,
+                                                          float* __restrict__ k_scale, uint8_t* __restrict__ v_codes,
+                                                          float* __restrict__ v_scale, int B, int Tn, int H, int KV, int max_seq) {
+    using P = typename pair_of<T>::type;
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int hd = 128, half = 64;
+    constexpr float fmax = FMT == TFP8B_E4M3FN ? 448.f : 57344.f;
+    const int heads = H + 2 * KV, lane = threadIdx.x & 31;
+    const long long total = static_cast<long long>(B) * Tn * heads;
+    const long long w0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const long long wstep = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+    for (long long idx = w0; idx < total; idx += wstep) {
+        const int h = static_cast<int>(idx % heads);
+        const int t = static_cast<int>((idx / heads) % Tn);
+        const int b = static_cast<int>(idx / (static_cast<long long>(heads) * Tn));
+        const long long p = pos[t];
+        if (p < 0 || p >= max_seq) {                           // outside the cache: skipped and reported
+            if (lane == 0 && h == 0) atomicOr(&g_status, STATUS_GLUE_POS);
+            continue;
+        }
+        const T* src = qkv + ((static_cast<size_t>(b) * Tn + t) * heads + h) * hd;
+        const float2 x1 = unpack2(*reinterpret_cast<const P*>(src + 2 * lane));
+        const float2 x2 = unpack2(*reinterpret_cast<const P*>(src + half + 2 * lane));
+        float2 o1 = x1, o2 = x2;
+        if (h < H + KV) {                                      // Q and K heads are rotated
+            const float2 c = *reinterpret_cast<const float2*>(cosv + p * half + 2 * lane);
+            const float2 sn = *reinterpret_cast<const float2*>(sinv + p * half + 2 * lane);
+            o1 = make_float2(x1.x * c.x - x2.x * sn.x, x1.y * c.y - x2.y * sn.y);
+            o2 = make_float2(x2.x * c.x + x1.x * sn.x, x2.y * c.y + x1.y * sn.y);
+        }
+        const P r1 = pack2(o1.x, o1.y, P()), r2 = pack2(o2.x, o2.y, P());
+        if (h < H) {
+            T* dst = q_out + ((static_cast<size_t>(b) * H + h) * Tn + t) * hd;
+            *reinterpret_cast<P*>(dst + 2 * lane) = r1;
+            *reinterpret_cast<P*>(dst + half + 2 * lane) = r2;
+            continue;
+        }
+        const bool is_k = h < H + KV;
+        const size_t row = (static_cast<size_t>(b) * KV + (is_k ? h - H : h - H - KV)) * max_seq + p;
+        const float2 a = unpack2(r1), c2 = unpack2(r2);
+        float v[4] = {a.x, a.y, c2.x, c2.y};
+        float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const float sc = scale_from_amax(m, fmax, 1);
+        const uint32_t sb = __float_as_uint(sc);
+        if (sb >= 0x00800000u && sb <= 0x7E800000u) {          // a power of two by construction: its reciprocal is exact
+            const float inv = __uint_as_float(0x7F000000u - sb);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] *= inv;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] = __fdiv_rn(v[i], sc);
+        }
+        uint32_t c01 = enc2_hw<FMT>(v[0], v[1]), c23 = enc2_hw<FMT>(v[2], v[3]);
+        constexpr uint32_t NAN_PROBE = FMT == TFP8B_E4M3FN ? 0x0101u : 0x0404u;
+        if (((c01 & 0x7F7Fu) + NAN_PROBE) & 0x8080u) c01 = encode1<FMT>(v[0], TFP8B_NAN_CAST) | (encode1<FMT>(v[1], TFP8B_NAN_CAST) << 8);
+        if (((c23 & 0x7F7Fu) + NAN_PROBE) & 0x8080u) c23 = encode1<FMT>(v[2], TFP8B_NAN_CAST) | (encode1<FMT>(v[3], TFP8B_NAN_CAST) << 8);
+        uint8_t* dst = (is_k ? k_codes : v_codes) + row * hd;
+        *reinterpret_cast<uint16_t*>(dst + 2 * lane) = static_cast<uint16_t>(c01);
+        *reinterpret_cast<uint16_t*>(dst + half + 2 * lane) = static_cast<uint16_t>(c23);
+        if (lane == 0) (is_k ? k_scale : v_scale)[row] = sc;
     }
 }
 
@@ -516,6 +593,147 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_kernel(const T* __re
     }
 }
 
+// The same kernel over an FP8 KV cache (codes u8 [B, KV, S, 128], one FP32 scale per position):
+// half the bytes per position. A score is the dot product with the decoded codes times the
+// position's K scale; the position's V scale rides on its softmax weight.
+template <typename T, int FMT>
+__global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* __restrict__ q, const uint8_t* __restrict__ kc,
+                                                                       const float* __restrict__ ksc, const uint8_t* __restrict__ vc,
+                                                                       const float* __restrict__ vsc, const long long* __restrict__ pos,
+                                                                       float* __restrict__ part, int H, int KV, int S, int nsplit,
+                                                                       float scale_log2e) {
+    using P = typename pair_of<T>::type;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int G = H / KV, ngrp = (G + ATT_G - 1) / ATT_G;
+    int id = blockIdx.x;
+    const int split = id % nsplit; id /= nsplit;
+    const int grp = id % ngrp; id /= ngrp;
+    const int kvh = id % KV, b = id / KV;
+    const int h0 = kvh * G + grp * ATT_G, nh = min(ATT_G, G - grp * ATT_G);
+    const int len = static_cast<int>(min(static_cast<long long>(S), pos[0] + 1));
+    const int chunk = min(ATT_CHUNK, (len + nsplit - 1) / nsplit);
+    const int s0 = split * chunk, n = max(0, min(len, s0 + chunk) - s0);
+    __shared__ float s_sc[ATT_G][ATT_CHUNK];
+    __shared__ float s_m[ATT_G], s_l[ATT_G];
+    __shared__ float s_acc[ATT_THREADS / 32][ATT_G][ATT_HD];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t row0 = (static_cast<size_t>(b) * KV + kvh) * S + s0;
+    const uint8_t* kbase = kc + row0 * ATT_HD;
+    const uint8_t* vbase = vc + row0 * ATT_HD;
+    // ---- scores: warp w takes positions [16 w, 16 w + 16); 8 lanes per position, 16 codes per lane
+    {
+        const int sub = lane & 7, slot = lane >> 3;
+        uint4 kr[ATT_PW / 4];
+        float kscale[ATT_PW / 4];
+#pragma unroll
+        for (int it = 0; it < ATT_PW / 4; ++it) {
+            const int j = warp * ATT_PW + it * 4 + slot;
+            if (j < n) {
+                kr[it] = *reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(j) * ATT_HD + sub * 16);
+                kscale[it] = ksc[row0 + j];
+            } else {
+                kr[it] = make_uint4(0u, 0u, 0u, 0u);
+                kscale[it] = 0.f;
+            }
+        }
+        float qf[ATT_G][16];
+#pragma unroll
+        for (int g = 0; g < ATT_G; ++g) {
+            const T* qp = q + (static_cast<size_t>(b) * H + h0 + min(g, nh - 1)) * ATT_HD + sub * 16;
+            const uint4 a0 = reinterpret_cast<const uint4*>(qp)[0], a1 = reinterpret_cast<const uint4*>(qp)[1];
+            const P* p0 = reinterpret_cast<const P*>(&a0);
+            const P* p1 = reinterpret_cast<const P*>(&a1);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f0 = unpack2(p0[i]), f1 = unpack2(p1[i]);
+                qf[g][2 * i] = f0.x * scale_log2e; qf[g][2 * i + 1] = f0.y * scale_log2e;
+                qf[g][8 + 2 * i] = f1.x * scale_log2e; qf[g][9 + 2 * i] = f1.y * scale_log2e;
+            }
+        }
+#pragma unroll
+        for (int it = 0; it < ATT_PW / 4; ++it) {
+            const int j = warp * ATT_PW + it * 4 + slot;
+            float kf[16];
+            const uint32_t w[4] = {kr[it].x, kr[it].y, kr[it].z, kr[it].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t p01, p23;
+                dec4<FMT, false>(w[i], p01, p23);
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&p01));
+                const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&p23));
+                kf[4 * i] = f0.x; kf[4 * i + 1] = f0.y; kf[4 * i + 2] = f1.x; kf[4 * i + 3] = f1.y;
+            }
+#pragma unroll
+            for (int g = 0; g < ATT_G; ++g) {
+                float d = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) d = fmaf(qf[g][i], kf[i], d);
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                if (sub == 0 && j < n) s_sc[g][j] = d * kscale[it];
+            }
+        }
+    }
+    // ---- the V codes of this warp's positions, requested now, used after the softmax
+    uint32_t vr[ATT_PW];                               // lane owns dims 4 lane .. 4 lane + 3
+#pragma unroll
+    for (int it = 0; it < ATT_PW; ++it) {
+        const int j = warp * ATT_PW + it;
+        vr[it] = j < n ? *reinterpret_cast<const uint32_t*>(vbase + static_cast<size_t>(j) * ATT_HD + lane * 4) : 0u;
+    }
+    __syncthreads();
+    // ---- per head: maximum, exponentials, sum (warp g serves head g); the weight kept for the
+    // V pass carries the position's V scale
+    if (warp < nh) {
+        const int g = warp;
+        float m = -INFINITY;
+        for (int j = lane; j < n; j += 32) m = fmaxf(m, s_sc[g][j]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float l = 0.f;
+        for (int j = lane; j < n; j += 32) {
+            const float e = exp2f(s_sc[g][j] - m);
+            s_sc[g][j] = e * vsc[row0 + j];
+            l += e;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        if (lane == 0) { s_m[g] = m; s_l[g] = l; }
+    }
+    __syncthreads();
+    // ---- weighted V over this warp's positions, then the four warps' sums are added
+    float acc[ATT_G][4];
+#pragma unroll
+    for (int g = 0; g < ATT_G; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+#pragma unroll
+    for (int it = 0; it < ATT_PW; ++it) {
+        const int j = warp * ATT_PW + it;
+        if (j < n) {
+            uint32_t p01, p23;
+            dec4<FMT, false>(vr[it], p01, p23);
+            const float2 v01 = __half22float2(*reinterpret_cast<const __half2*>(&p01));
+            const float2 v23 = __half22float2(*reinterpret_cast<const __half2*>(&p23));
+#pragma unroll
+            for (int g = 0; g < ATT_G; ++g) {
+                const float w = s_sc[g][j];
+                acc[g][0] = fmaf(w, v01.x, acc[g][0]); acc[g][1] = fmaf(w, v01.y, acc[g][1]);
+                acc[g][2] = fmaf(w, v23.x, acc[g][2]); acc[g][3] = fmaf(w, v23.y, acc[g][3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < ATT_G; ++g)
+        *reinterpret_cast<float4*>(&s_acc[warp][g][lane * 4]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    __syncthreads();
+    for (int g = 0; g < nh; ++g) {
+        float* rec = part + ((static_cast<size_t>(b) * H + h0 + g) * nsplit + split) * (ATT_HD + 2);
+        rec[2 + threadIdx.x] = s_acc[0][g][threadIdx.x] + s_acc[1][g][threadIdx.x] + s_acc[2][g][threadIdx.x] + s_acc[3][g][threadIdx.x];
+        if (threadIdx.x == 0) { rec[0] = n > 0 ? s_m[g] : -INFINITY; rec[1] = n > 0 ? s_l[g] : 0.f; }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(ATT_HD) attn_merge_kernel(const float* __restrict__ part, T* __restrict__ out, int nsplit) {
     pdl_launch_dependents();
@@ -619,6 +837,36 @@ extern "C" int tfp8b_rope_kv_store(const void* qkv, int dtype, const long long* 
                       static_cast<__nv_bfloat16*>(v_cache), B, T, H, KV, hd, max_seq);
 }
 
+template <typename T>
+static int rope_kv_fp8_launch(int fmt, int grid, cudaStream_t st, const void* qkv, const long long* pos, const float* cosv,
+                              const float* sinv, void* q_out, uint8_t* k_codes, float* k_scale, uint8_t* v_codes, float* v_scale,
+                              int B, int Tn, int H, int KV, int max_seq) {
+    if (fmt == TFP8B_E4M3FN)
+        return launch_pdl("tfp8b_rope_kv_store_fp8", rope_kv_fp8_kernel<T, TFP8B_E4M3FN>, grid, 256, st, static_cast<const T*>(qkv), pos,
+                          cosv, sinv, static_cast<T*>(q_out), k_codes, k_scale, v_codes, v_scale, B, Tn, H, KV, max_seq);
+    return launch_pdl("tfp8b_rope_kv_store_fp8", rope_kv_fp8_kernel<T, TFP8B_E5M2>, grid, 256, st, static_cast<const T*>(qkv), pos, cosv,
+                      sinv, static_cast<T*>(q_out), k_codes, k_scale, v_codes, v_scale, B, Tn, H, KV, max_seq);
+}
+
+extern "C" int tfp8b_rope_kv_store_fp8(const void* qkv, int dtype, const long long* pos, const float* cosv, const float* sinv,
+                                       void* q_out, uint8_t* k_codes, float* k_scale, uint8_t* v_codes, float* v_scale, int B, int T,
+                                       int H, int KV, int hd, int max_seq, int fmt, tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(dtype == TFP8B_F16 || dtype == TFP8B_BF16, TFP8B_ERR_UNSUPPORTED, "tfp8b_rope_kv_store_fp8: f16 / bf16 only");
+    TFP8B_REQUIRE(fmt == TFP8B_E4M3FN || fmt == TFP8B_E5M2, TFP8B_ERR_INVALID, "tfp8b_rope_kv_store_fp8: bad fmt %d", fmt);
+    TFP8B_REQUIRE(hd == 128, TFP8B_ERR_UNSUPPORTED, "tfp8b_rope_kv_store_fp8: head_dim %d (only 128 is built)", hd);
+    TFP8B_REQUIRE(B >= 0 && T >= 0 && H > 0 && KV > 0 && max_seq > 0, TFP8B_ERR_INVALID, "tfp8b_rope_kv_store_fp8: bad shape");
+    if (B == 0 || T == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(qkv && pos && cosv && sinv && q_out && k_codes && k_scale && v_codes && v_scale, TFP8B_ERR_INVALID,
+                  "tfp8b_rope_kv_store_fp8: null pointer");
+    const long long work = static_cast<long long>(B) * T * (H + 2 * KV) * 32;      // one warp per head
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == TFP8B_F16)
+        return rope_kv_fp8_launch<__half>(fmt, grid_of(work), st, qkv, pos, cosv, sinv, q_out, k_codes, k_scale, v_codes, v_scale, B, T,
+                                          H, KV, max_seq);
+    return rope_kv_fp8_launch<__nv_bfloat16>(fmt, grid_of(work), st, qkv, pos, cosv, sinv, q_out, k_codes, k_scale, v_codes, v_scale, B,
+                                             T, H, KV, max_seq);
+}
+
 extern "C" int tfp8b_silu_mul(const void* gate_up, void* out, int dtype, long long rows, int F, tfp8b_stream_t stream) {
     TFP8B_REQUIRE(dtype == TFP8B_F16 || dtype == TFP8B_BF16, TFP8B_ERR_UNSUPPORTED, "tfp8b_silu_mul: f16 / bf16 only");
     TFP8B_REQUIRE(rows >= 0 && F > 0 && F % 8 == 0, TFP8B_ERR_INVALID, "tfp8b_silu_mul: need F %% 8 == 0");
@@ -686,6 +934,51 @@ extern "C" int tfp8b_attn_decode(const void* q, const void* k_cache, const void*
     if (rc != TFP8B_OK) return rc;
     return launch_pdl("tfp8b_attn_decode", attn_merge_kernel<__nv_bfloat16>, B * H, ATT_HD, st, static_cast<const float*>(scratch),
                       static_cast<__nv_bfloat16*>(out), nsplit);
+}
+
+template <typename T>
+static int attn_fp8_launch(int fmt, int grid, cudaStream_t st, const void* q, const uint8_t* k_codes, const float* k_scale,
+                           const uint8_t* v_codes, const float* v_scale, const long long* pos, float* scratch, void* out, int B, int H,
+                           int KV, int max_seq, int nsplit, float scale_log2e) {
+    int rc;
+    if (fmt == TFP8B_E4M3FN)
+        rc = launch_pdl("tfp8b_attn_decode_fp8", attn_partial_fp8_kernel<T, TFP8B_E4M3FN>, grid, ATT_THREADS, st, static_cast<const T*>(q),
+                        k_codes, k_scale, v_codes, v_scale, pos, scratch, H, KV, max_seq, nsplit, scale_log2e);
+    else
+        rc = launch_pdl("tfp8b_attn_decode_fp8", attn_partial_fp8_kernel<T, TFP8B_E5M2>, grid, ATT_THREADS, st, static_cast<const T*>(q),
+                        k_codes, k_scale, v_codes, v_scale, pos, scratch, H, KV, max_seq, nsplit, scale_log2e);
+    if (rc != TFP8B_OK) return rc;
+    return launch_pdl("tfp8b_attn_decode_fp8", attn_merge_kernel<T>, B * H, ATT_HD, st, static_cast<const float*>(scratch),
+                      static_cast<T*>(out), nsplit);
+}
+
+extern "C" int tfp8b_attn_decode_fp8(const void* q, const uint8_t* k_codes, const float* k_scale, const uint8_t* v_codes,
+                                     const float* v_scale, const long long* pos, void* out, float* scratch, long long scratch_floats,
+                                     int dtype, int B, int H, int KV, int hd, int max_seq, int fmt, tfp8b_stream_t stream) {
+    TFP8B_REQUIRE(dtype == TFP8B_F16 || dtype == TFP8B_BF16, TFP8B_ERR_UNSUPPORTED, "tfp8b_attn_decode_fp8: f16 / bf16 only");
+    TFP8B_REQUIRE(fmt == TFP8B_E4M3FN || fmt == TFP8B_E5M2, TFP8B_ERR_INVALID, "tfp8b_attn_decode_fp8: bad fmt %d", fmt);
+    TFP8B_REQUIRE(hd == ATT_HD, TFP8B_ERR_UNSUPPORTED, "tfp8b_attn_decode_fp8: head_dim %d (only %d is built)", hd, ATT_HD);
+    TFP8B_REQUIRE(B >= 0 && H > 0 && KV > 0 && H % KV == 0 && max_seq > 0, TFP8B_ERR_INVALID,
+                  "tfp8b_attn_decode_fp8: bad shape (H=%d KV=%d)", H, KV);
+    if (B == 0) return TFP8B_OK;
+    TFP8B_REQUIRE(q && k_codes && k_scale && v_codes && v_scale && pos && out && scratch, TFP8B_ERR_INVALID,
+                  "tfp8b_attn_decode_fp8: null pointer");
+    TFP8B_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_codes)) & 15u) == 0 &&
+                  (reinterpret_cast<uintptr_t>(v_codes) & 3u) == 0, TFP8B_ERR_INVALID,
+                  "tfp8b_attn_decode_fp8: q and k_codes must be 16-byte aligned, v_codes 4-byte aligned");
+    const int nsplit = (max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
+    TFP8B_REQUIRE(nsplit <= 128, TFP8B_ERR_UNSUPPORTED, "tfp8b_attn_decode_fp8: max_seq %d (at most %d is built)", max_seq, 128 * ATT_CHUNK);
+    const int ngrp = (H / KV + ATT_G - 1) / ATT_G;
+    const long long need = static_cast<long long>(B) * H * nsplit * (ATT_HD + 2);
+    TFP8B_REQUIRE(scratch_floats >= need, TFP8B_ERR_INVALID, "tfp8b_attn_decode_fp8: scratch of %lld floats, %lld needed", scratch_floats, need);
+    const float scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(hd));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = B * KV * ngrp * nsplit;
+    if (dtype == TFP8B_F16)
+        return attn_fp8_launch<__half>(fmt, grid, st, q, k_codes, k_scale, v_codes, v_scale, pos, scratch, out, B, H, KV, max_seq, nsplit,
+                                       scale_log2e);
+    return attn_fp8_launch<__nv_bfloat16>(fmt, grid, st, q, k_codes, k_scale, v_codes, v_scale, pos, scratch, out, B, H, KV, max_seq,
+                                          nsplit, scale_log2e);
 }
 
 extern "C" int tfp8b_allreduce_add_rmsnorm(void* x, const float* partial, const void* weight, void* out, int dtype, int rows,

@@ -89,17 +89,6 @@ __device__ __forceinline__ float scalar_f32(__half v) { return half_bits_to_f32(
 __device__ __forceinline__ float scalar_f32(__nv_bfloat16 v) { return __uint_as_float(static_cast<uint32_t>(__bfloat16_as_ushort(v)) << 16); }
 __device__ __forceinline__ float scalar_f32(float v) { return v; }
 
-// Two floats -> two codes (lo in bits 0-7) by the conversion instruction: round to nearest even,
-// saturate to the largest finite code (+-inf included). A NaN comes back as some NaN code of the
-// format, never as a finite one, which is all `encode16` relies on.
-template <int FMT>
-__device__ __forceinline__ uint32_t enc2_hw(float lo, float hi) {
-    unsigned short r;
-    if (FMT == TFP8B_E4M3FN) asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-    else asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-
 // 16 floats -> 16 codes. The conversion instruction does the rounding; a word that holds a NaN
 // code (E4M3FN: 0x7F; E5M2: anything above the largest finite 0x7B, as saturation leaves no
 // infinity) is redone by the integer encoder, which knows the NaN convention asked for.
@@ -242,16 +231,6 @@ __global__ void __launch_bounds__(EW_THREADS) dequant_kernel(const uint8_t* __re
 // keeping it in shared memory instead measured slower). 16 contiguous elements per thread per step.
 // (Reducing the amax among the lanes of a group by shuffles before the atomic was measured too:
 // 12 - 20 % slower than letting all lanes hit the shared-memory word.)
-__device__ __forceinline__ float scale_from_amax(float amax, float fmax, int pow2) {
-    if (amax == 0.f) return 1.f;
-    float s = fmaxf(__fdiv_rn(amax, fmax), FLT_MIN);
-    if (pow2) {
-        uint32_t u = __float_as_uint(s);
-        if (u & 0x007FFFFFu) u = (u & 0x7F800000u) + 0x00800000u;   // next power of two
-        s = __uint_as_float(u);
-    }
-    return s;
-}
 
 // R > 0 (16-bit inputs, K <= R * 4096): the row stays in registers between the two passes -- all
 // of a thread's loads are issued before the first is used, and nothing is read twice. R == 0:

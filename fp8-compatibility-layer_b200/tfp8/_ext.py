@@ -60,6 +60,8 @@ _SIGNATURES = {
     "tfp8b_allreduce_add_rmsnorm": ([_P, _P, _P, _P, _I, _I, _I, ctypes.c_float, _P, _P, _P, _I, _I, _I, _P], _I),
     "tfp8b_attn_decode": ([_P, _P, _P, _P, _P, _P, ctypes.c_longlong, _I, _I, _I, _I, _I, _I, _P], _I),
     "tfp8b_argmax": ([_P, _I, _P, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _P], _I),
+    "tfp8b_rope_kv_store_fp8": ([_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P], _I),
+    "tfp8b_attn_decode_fp8": ([_P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_longlong, _I, _I, _I, _I, _I, _I, _I, _P], _I),
 }
 
 
@@ -528,6 +530,40 @@ def attn_decode(q, k_cache, v_cache, pos, scratch=None):
         rc = load().tfp8b_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(), out.data_ptr(),
                                       scratch.data_ptr(), scratch.numel(), _DT[q.dtype], B, H, KV, hd, S, _stream(dev))
     _check(rc, "tfp8b_attn_decode")
+    return out
+
+
+def rope_kv_store_fp8(qkv, pos, cos, sin, k_codes, k_scale, v_codes, v_scale, n_heads, n_kv_heads, fmt="e4m3fn"):
+    """`rope_kv_store` into an FP8 KV cache: k_codes / v_codes uint8 [B, KV, max_seq, 128], k_scale /
+    v_scale float32 [B, KV, max_seq]. K (rotated) and V are rounded to the activation type and then
+    quantized per token and KV head like a row of `quantize_weight` (power-of-two scale). Returns Q
+    as [B, H, T, hd]."""
+    dev = _need_cuda(qkv, pos, cos, sin, k_codes, k_scale, v_codes, v_scale)
+    B, T = qkv.shape[0], qkv.shape[1]
+    hd = k_codes.shape[-1]
+    q = torch.empty(B, n_heads, T, hd, dtype=qkv.dtype, device=qkv.device)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_rope_kv_store_fp8(qkv.data_ptr(), _DT[qkv.dtype], pos.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                            q.data_ptr(), k_codes.data_ptr(), k_scale.data_ptr(), v_codes.data_ptr(),
+                                            v_scale.data_ptr(), B, T, n_heads, n_kv_heads, hd, k_codes.shape[2], FMT_ID[fmt],
+                                            _stream(dev))
+    _check(rc, "tfp8b_rope_kv_store_fp8")
+    return q
+
+
+def attn_decode_fp8(q, k_codes, k_scale, v_codes, v_scale, pos, scratch=None, fmt="e4m3fn"):
+    """`attn_decode` over an FP8 KV cache (see `rope_kv_store_fp8` for its layout). Returns [B, H, hd]."""
+    dev = _need_cuda(q, k_codes, k_scale, v_codes, v_scale, pos, scratch)
+    B, H, hd = q.shape[0], q.shape[1], q.shape[-1]
+    KV, S = k_codes.shape[1], k_codes.shape[2]
+    if scratch is None:
+        scratch = torch.empty(attn_scratch_floats(B, H, S, hd), dtype=torch.float32, device=q.device)
+    out = torch.empty(B, H, hd, dtype=q.dtype, device=q.device)
+    with torch.cuda.device(dev):
+        rc = load().tfp8b_attn_decode_fp8(q.data_ptr(), k_codes.data_ptr(), k_scale.data_ptr(), v_codes.data_ptr(),
+                                          v_scale.data_ptr(), pos.data_ptr(), out.data_ptr(), scratch.data_ptr(), scratch.numel(),
+                                          _DT[q.dtype], B, H, KV, hd, S, FMT_ID[fmt], _stream(dev))
+    _check(rc, "tfp8b_attn_decode_fp8")
     return out
 
 

@@ -17,6 +17,11 @@ class FP8Config:
     # cores; needs weight_group=32 and scale_format="ue8m0" (the MX layout). The reference reserves
     # the field and raises for anything but "fp16" (tfp8/config.py:25-26 there).
     activation: str = "fp16"
+    # "fp16": the KV cache of a decoder is left as the model keeps it. "fp8": the serving harness
+    # (tfp8.examples.llama) keeps K and V as codes of `fmt` with one power-of-two scale per token and
+    # KV head, quantized like a row of quantize_weight, and attends over the codes. prepare_model
+    # itself never touches a cache: the field travels with the plan for whoever owns the attention.
+    # The reference reserves the field and raises for anything but "fp16" (tfp8/config.py:27-28 there).
     kv_cache: str = "fp16"
     fallback: str = "tbf16"              # owner recorded for modules that are left alone
     min_features: int | None = None      # None: 1024 (llm_safe) / 256 (image_safe)
@@ -40,8 +45,8 @@ class FP8Config:
             raise NotImplementedError("activation must be 'fp16' (W8A16) or 'fp8' (W8A8 with 32-wide block scales)")
         if self.activation == "fp8" and (self.weight_group != 32 or self.scale_format != "ue8m0"):
             raise NotImplementedError("activation='fp8' is the MX layout: weight_group=32 and scale_format='ue8m0'")
-        if self.kv_cache != "fp16":
-            raise NotImplementedError("an FP8 KV cache is not implemented")
+        if self.kv_cache not in ("fp16", "fp8"):
+            raise NotImplementedError("kv_cache must be 'fp16' or 'fp8'")
         if self.large_m_backend not in ("fused", "chunked"):
             raise ValueError("large_m_backend must be 'fused' or 'chunked'")
         if self.scale_format not in SCALE_FORMATS:

@@ -18,7 +18,9 @@ import torch.nn.functional as F
 
 from .. import _ext
 from ..config import FP8Config
+from ..formats import decode as decode_codes
 from ..linear import FP8Linear
+from ..quantize import quantize_weight
 from ..parallel import ColumnParallelFP8Linear, RowParallelFP8Linear
 
 
@@ -97,26 +99,76 @@ class Block(nn.Module):
         self.input_layernorm = RMSNorm(d, cfg.eps, device, dtype)
         self.post_attention_layernorm = RMSNorm(d, cfg.eps, device, dtype)
         self.k_cache = self.v_cache = None
+        self.kv_fmt = None                          # "e4m3fn" / "e5m2": the cache holds FP8 codes + one scale per token and KV head
+        self.k_scale = self.v_scale = None
         self.cos_table = self.sin_table = None      # the model's [max_seq, hd/2] tables, shared by all blocks
         self.comm = None                            # FusedAllReduceNorm of a tensor-parallel decode, set by the model
 
-    def alloc_cache(self, batch, device, dtype):
+    def alloc_cache(self, batch, device, dtype, kv_fmt=None):
         shape = (batch, self.kv_local, self.cfg.max_seq, self.cfg.head_dim)
-        self.k_cache = torch.zeros(shape, device=device, dtype=dtype)
-        self.v_cache = torch.zeros(shape, device=device, dtype=dtype)
+        self.kv_fmt = kv_fmt
+        if kv_fmt is None:
+            self.k_cache = torch.zeros(shape, device=device, dtype=dtype)
+            self.v_cache = torch.zeros(shape, device=device, dtype=dtype)
+            self.k_scale = self.v_scale = None
+        else:               # FP8 codes (zero decodes to 0) and the scale of every (sequence, KV head, position)
+            self.k_cache = torch.zeros(shape, device=device, dtype=torch.uint8)
+            self.v_cache = torch.zeros(shape, device=device, dtype=torch.uint8)
+            self.k_scale = torch.ones(shape[:3], device=device, dtype=torch.float32)
+            self.v_scale = torch.ones(shape[:3], device=device, dtype=torch.float32)
         # split-KV partial results of the decode attention; one buffer can serve all blocks
         self.attn_scratch = None
+
+    def _kv_store(self, qkv, pos):
+        """Fused rotary embedding + cache write of a QKV projection output; returns head-major Q."""
+        if self.kv_fmt is None:
+            return _ext.rope_kv_store(qkv, pos, self.cos_table, self.sin_table, self.k_cache, self.v_cache, self.h_local, self.kv_local)
+        return _ext.rope_kv_store_fp8(qkv, pos, self.cos_table, self.sin_table, self.k_cache, self.k_scale, self.v_cache,
+                                      self.v_scale, self.h_local, self.kv_local, self.kv_fmt)
+
+    def _kv_attend(self, q, pos):
+        """One query token per sequence over the cache (the library's split-KV kernel)."""
+        if self.kv_fmt is None:
+            return _ext.attn_decode(q, self.k_cache, self.v_cache, pos, self.attn_scratch)
+        return _ext.attn_decode_fp8(q, self.k_cache, self.k_scale, self.v_cache, self.v_scale, pos, self.attn_scratch, self.kv_fmt)
+
+    def _kv_dense(self, upto=None, dtype=torch.float16):
+        """The cache as 16-bit tensors (an FP8 cache decoded: codes * scale, exact in fp32 and then
+        rounded to `dtype`), positions [0, upto)."""
+        k, v = self.k_cache, self.v_cache
+        if upto is not None:
+            k, v = k[:, :, :upto], v[:, :, :upto]
+        if self.kv_fmt is None:
+            return k, v
+        ks, vs = self.k_scale, self.v_scale
+        if upto is not None:
+            ks, vs = ks[:, :, :upto], vs[:, :, :upto]
+        return ((decode_codes(k.contiguous(), self.kv_fmt) * ks[..., None]).to(dtype),
+                (decode_codes(v.contiguous(), self.kv_fmt) * vs[..., None]).to(dtype))
+
+    def _kv_write_torch(self, pos, k, v):
+        """Cache write without the fused kernel (CPU, fp32): k, v [B, KV, T, hd] already rotated."""
+        if self.kv_fmt is None:
+            self.k_cache.index_copy_(2, pos, k)
+            self.v_cache.index_copy_(2, pos, v)
+            return
+        hd = k.shape[-1]
+        for t, codes, scale in ((k, self.k_cache, self.k_scale), (v, self.v_cache, self.v_scale)):
+            q8, s8, _ = quantize_weight(t.reshape(-1, hd), self.kv_fmt, None, True)      # one row per token and KV head
+            codes.index_copy_(2, pos, q8.view(t.shape))
+            scale.index_copy_(2, pos, s8.view(t.shape[:3]))
 
     def _decode_few_rows(self, x, delta, pos, mask):
         """Block.forward for one or two decode rows on one GPU: 7 kernels instead of 10."""
         B, T, _ = x.shape
         hd, eps = self.cfg.head_dim, self.cfg.eps
         x, qkv = _w8(self.qkv_proj, _ext.gemv_normed, x, delta, self.input_layernorm.weight, eps)
-        q = _ext.rope_kv_store(qkv, pos, self.cos_table, self.sin_table, self.k_cache, self.v_cache, self.h_local, self.kv_local)
+        q = self._kv_store(qkv, pos)
         if mask is False:
-            a = _ext.attn_decode(q, self.k_cache, self.v_cache, pos, self.attn_scratch).view(B, 1, self.h_local * hd)
+            a = self._kv_attend(q, pos).view(B, 1, self.h_local * hd)
         else:
-            a = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask, enable_gqa=True)
+            kd, vd = self._kv_dense(dtype=x.dtype)
+            a = F.scaled_dot_product_attention(q, kd, vd, attn_mask=mask, enable_gqa=True)
             a = a.transpose(1, 2).reshape(B, T, self.h_local * hd)
         o = self.o_proj(a)
         x, gu = _w8(self.gate_up_proj, _ext.gemv_normed, x, o, self.post_attention_layernorm.weight, eps)
@@ -147,23 +199,24 @@ class Block(nn.Module):
             h = self.input_layernorm(x)
         qkv = self.qkv_proj(h).to(x.dtype)
         if fused:      # one kernel: rotate Q and K, write K and V into the cache, lay Q out head-major
-            q = _ext.rope_kv_store(qkv.contiguous(), pos, self.cos_table, self.sin_table, self.k_cache, self.v_cache,
-                                   self.h_local, self.kv_local)
-            k, v = self.k_cache[:, :, :T], self.v_cache[:, :, :T]           # prefill starts at position 0
+            q = self._kv_store(qkv.contiguous(), pos)
         else:
             qkv = qkv.view(B, T, self.h_local + 2 * self.kv_local, hd).transpose(1, 2)
             q, k, v = qkv.split((self.h_local, self.kv_local, self.kv_local), dim=1)
             q, k = _rope(q, cos, sin), _rope(k, cos, sin)
-            self.k_cache.index_copy_(2, pos, k)
-            self.v_cache.index_copy_(2, pos, v)
+            self._kv_write_torch(pos, k, v)
         if mask is None:
+            # prefill starts at position 0 and attends over what the cache now holds (an FP8 cache: the
+            # quantized K and V, as every later step will see them)
+            k, v = self._kv_dense(T, x.dtype)
             a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
             a = a.transpose(1, 2).reshape(B, T, self.h_local * hd)
         elif mask is False:
             # decode step: split-KV attention over the static cache, [B, H, hd] is already [B, 1, H * hd]
-            a = _ext.attn_decode(q, self.k_cache, self.v_cache, pos, self.attn_scratch).view(B, 1, self.h_local * hd)
+            a = self._kv_attend(q, pos).view(B, 1, self.h_local * hd)
         else:
-            a = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask, enable_gqa=True)
+            kd, vd = self._kv_dense(dtype=x.dtype)
+            a = F.scaled_dot_product_attention(q, kd, vd, attn_mask=mask, enable_gqa=True)
             a = a.transpose(1, 2).reshape(B, T, self.h_local * hd)
         if comm is not None:
             h = comm.add_rmsnorm(x, self.o_proj.partial(a), self.post_attention_layernorm.weight, self.cfg.eps)
@@ -194,6 +247,10 @@ class Llama(nn.Module):
         self.cfg, self.tp = cfg, tp
         # decode attention: torch SDPA (cuDNN) by default; True selects the library's split-KV kernel
         self.attn_kernel = False
+        # None: the KV cache holds activations as they are. "e4m3fn" / "e5m2": FP8 codes + one scale per
+        # token and KV head (FP8Config(kv_cache="fp8")); the decode step then always uses the library's
+        # attention kernel, which reads the codes (torch's would need the whole cache decoded first).
+        self.kv_fmt = None
         self.embed = nn.Embedding(cfg.vocab, cfg.d_model, device=device, dtype=dtype)
         self.layers = nn.ModuleList([Block(cfg, tp, device, dtype) for _ in range(cfg.n_layers)])
         self.norm = RMSNorm(cfg.d_model, cfg.eps, device, dtype)
@@ -210,7 +267,7 @@ class Llama(nn.Module):
             scratch = torch.empty(_ext.attn_scratch_floats(batch, self.cfg.n_heads // self.tp, self.cfg.max_seq, self.cfg.head_dim),
                                   dtype=torch.float32, device=p.device)
         for l in self.layers:
-            l.alloc_cache(batch, p.device, p.dtype)
+            l.alloc_cache(batch, p.device, p.dtype, self.kv_fmt)
             l.cos_table, l.sin_table = self.cos, self.sin
             l.attn_scratch = scratch
 
@@ -229,7 +286,7 @@ class Llama(nn.Module):
         mask = None
         if not prefill:
             hd, blk = self.cfg.head_dim, self.layers[0]
-            if self.attn_kernel and fused and tokens.shape[1] == 1 and hd == 128:
+            if (self.attn_kernel or self.kv_fmt is not None) and fused and tokens.shape[1] == 1 and hd == 128:
                 mask = False             # decode attention kernel: reads the position itself, no mask tensor
             else:
                 seq = torch.arange(self.cfg.max_seq, device=pos.device)
@@ -299,6 +356,7 @@ def build_fp8_llama(cfg: LlamaConfig, device, dtype=torch.float16, fp8: FP8Confi
     ang = torch.arange(cfg.max_seq, device=device).float()[:, None] * inv[None, :]
     model.register_buffer("cos", ang.cos(), persistent=False)
     model.register_buffer("sin", ang.sin(), persistent=False)
+    model.kv_fmt = fp8.fmt if fp8.kv_cache == "fp8" else None
     return model
 
 

@@ -333,6 +333,22 @@ TFP8B_API int tfp8b_attn_decode(const void* q, const void* k_cache, const void* 
                   void* out, float* scratch, long long scratch_floats, int dtype, int B, int H, int KV, int hd,
                   int max_seq, tfp8b_stream_t stream);
 
+/* The two calls above over an FP8 KV cache -- the mode the reference's FP8Config reserves and
+ * refuses (kv_cache != "fp16": tfp8/config.py:27-28). k_codes / v_codes u8 [B, KV, max_seq, hd],
+ * k_scale / v_scale f32 [B, KV, max_seq]: K (after the rotation) and V are rounded to the
+ * activation type, as the 16-bit cache holds them, and then quantized per token and KV head the way
+ * quantize_weight quantizes a row (tfp8/quantize.py:15-36: scale 2^ceil(log2(amax / fmax)), 1 for
+ * an all-zero row; round to nearest even, saturating) -- tfp8b_quantize on the 16-bit cache rows
+ * gives the same bytes. The attention decodes the codes in registers: score = (q . codes) * k_scale,
+ * softmax weight * v_scale on the V side, FP32 throughout. hd = 128; fmt E4M3FN or E5M2.
+ * k_codes 16-byte aligned. Same scratch as tfp8b_attn_decode. */
+TFP8B_API int tfp8b_rope_kv_store_fp8(const void* qkv, int dtype, const long long* pos, const float* cos_table,
+                  const float* sin_table, void* q_out, uint8_t* k_codes, float* k_scale, uint8_t* v_codes,
+                  float* v_scale, int B, int T, int H, int KV, int hd, int max_seq, int fmt, tfp8b_stream_t stream);
+TFP8B_API int tfp8b_attn_decode_fp8(const void* q, const uint8_t* k_codes, const float* k_scale, const uint8_t* v_codes,
+                  const float* v_scale, const long long* pos, void* out, float* scratch, long long scratch_floats,
+                  int dtype, int B, int H, int KV, int hd, int max_seq, int fmt, tfp8b_stream_t stream);
+
 /* out[r] = argmax over logits[r, 0:n] (row pitch in elements), int64; the lowest index among equal
  * values, NaN counts as largest -- the greedy sampling step of the reference's demo
  * (tfp8/examples/demo_llm.py:149). f16 or bf16. */

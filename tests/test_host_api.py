@@ -156,8 +156,9 @@ def test_config_validation():
         tfp8.FP8Config(profile="anything")
     with pytest.raises(NotImplementedError):
         tfp8.FP8Config(activation="fp8")
+    assert tfp8.FP8Config(kv_cache="fp8").kv_cache == "fp8"           # the serving harness's FP8 KV cache
     with pytest.raises(NotImplementedError):
-        tfp8.FP8Config(kv_cache="fp8")
+        tfp8.FP8Config(kv_cache="int4")
     with pytest.raises(ValueError):
         tfp8.FP8Config(large_m_backend="x")
     with pytest.raises(ValueError):
