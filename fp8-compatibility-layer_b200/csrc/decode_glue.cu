@@ -15,6 +15,11 @@
 // with programmatic stream serialization and release their dependents at once: the FP8 GEMV
 // that follows starts streaming its weights while the helper is still running, and waits for
 // it (griddepcontrol.wait) only before it reads the activations.
+// A kernel launched that way is alive while its predecessor still writes, so nothing it reads
+// is "read-only for the lifetime of the kernel": no pointer here is __restrict__ and nothing is
+// loaded through the non-coherent path (__ldg / ld.global.nc). With them the compiler used that
+// path for the FP8 cache's per-position scales, whose 128-byte lines are shared by 32 positions:
+// a line cached when the previous token's step read it came back without the newest scale.
 #include <stdlib.h>
 
 #include "common.cuh"
@@ -34,9 +39,9 @@ __device__ __forceinline__ __nv_bfloat162 pack2(float a, float b, __nv_bfloat162
 // element i pairs with element i + hd/2); q_out [B, H, T, hd]; k_cache / v_cache [B, KV, max_seq, hd].
 // One thread handles two neighbouring i (a 32-bit pair) of both halves of one head.
 template <typename T>
-__global__ void __launch_bounds__(256) rope_kv_kernel(const T* __restrict__ qkv, const long long* __restrict__ pos,
-                                                      const float* __restrict__ cosv, const float* __restrict__ sinv,
-                                                      T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+__global__ void __launch_bounds__(256) rope_kv_kernel(const T* qkv, const long long* pos,
+                                                      const float* cosv, const float* sinv,
+                                                      T* q_out, T* k_cache, T* v_cache,
                                                       int B, int Tn, int H, int KV, int hd, int max_seq) {
     using P = typename pair_of<T>::type;
     pdl_launch_dependents();
@@ -83,11 +88,11 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const T* __restrict__ qkv,
 // k_codes / v_codes u8 [B, KV, max_seq, hd] and one FP32 scale per (sequence, KV head, position).
 // One warp per (sequence, token, head); hd = 128: lane l holds elements 2l, 2l + 1 of both halves.
 template <typename T, int FMT>
-__global__ void __launch_bounds__(256) rope_kv_fp8_kernel(const T* __restrict__ qkv, const long long* __restrict__ pos,
-                                                          const float* __restrict__ cosv, const float* __restrict__ sinv,
-                                                          T* __restrict__ q_out, uint8_t* __restrict__ k_codes,
-                                                          float* __restrict__ k_scale, uint8_t* __restrict__ v_codes,
-                                                          float* __restrict__ v_scale, int B, int Tn, int H, int KV, int max_seq) {
+__global__ void __launch_bounds__(256) rope_kv_fp8_kernel(const T* qkv, const long long* pos,
+                                                          const float* cosv, const float* sinv,
+                                                          T* q_out, uint8_t* k_codes,
+                                                          float* k_scale, uint8_t* v_codes,
+                                                          float* v_scale, int B, int Tn, int H, int KV, int max_seq) {
     using P = typename pair_of<T>::type;
     pdl_launch_dependents();
     pdl_wait();
@@ -153,7 +158,7 @@ __global__ void __launch_bounds__(256) rope_kv_fp8_kernel(const T* __restrict__ 
 
 // gu [rows, 2F] -> out [rows, F] = silu(gu[:, :F]) * gu[:, F:]; eight elements per thread.
 template <typename T>
-__global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int F) {
+__global__ void __launch_bounds__(256) silu_mul_kernel(const T* gu, T* out, long long rows, int F) {
     using P = typename pair_of<T>::type;
     pdl_launch_dependents();
     pdl_wait();
@@ -184,8 +189,8 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu,
 constexpr int ADD_NORM_THREADS = 256;
 constexpr int ADD_NORM_KEEP = 4;
 template <typename T>
-__global__ void __launch_bounds__(ADD_NORM_THREADS) add_rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta,
-                                                                       const T* __restrict__ w, T* __restrict__ out,
+__global__ void __launch_bounds__(ADD_NORM_THREADS) add_rmsnorm_kernel(T* x, const T* delta,
+                                                                       const T* w, T* out,
                                                                        int dim, float eps) {
     using P = typename pair_of<T>::type;
     pdl_launch_dependents();
@@ -284,8 +289,8 @@ struct ArParams {
 };
 constexpr int AR_THREADS = 256;
 template <typename T>
-__global__ void __launch_bounds__(AR_THREADS) allreduce_add_rmsnorm_kernel(T* __restrict__ x, const float* __restrict__ part,
-                                                                           const T* __restrict__ w, T* __restrict__ out,
+__global__ void __launch_bounds__(AR_THREADS) allreduce_add_rmsnorm_kernel(T* x, const float* part,
+                                                                           const T* w, T* out,
                                                                            int dim, float eps, const ArParams ar) {
     using P = typename pair_of<T>::type;
     pdl_launch_dependents();
@@ -404,7 +409,7 @@ __device__ __forceinline__ bool argmax_better(float v, long long i, float bv, lo
     return v > bv || (v == bv && i < bi);
 }
 template <typename T>
-__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const T* __restrict__ logits, long long* __restrict__ out,
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const T* logits, long long* out,
                                                                 long long n, long long row_pitch) {
     using P = typename pair_of<T>::type;
     pdl_launch_dependents();
@@ -458,18 +463,21 @@ __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const T* __restr
 // maximum, sum, weighted V) that attn_merge_kernel combines. Every global load of a phase is
 // issued before its first use (the chunk is short: one memory round trip per phase). FP32
 // arithmetic throughout. hd = 128.
-constexpr int ATT_THREADS = 128;
+#ifndef TFP8B_ATT_THREADS
+#define TFP8B_ATT_THREADS 128
+#endif
+constexpr int ATT_THREADS = TFP8B_ATT_THREADS;
 constexpr int ATT_HD = 128;
 constexpr int ATT_G = 4;             // query heads per CTA (a KV head with more is served by several CTAs)
 constexpr int ATT_CHUNK = 64;        // positions per CTA at most
 constexpr int ATT_PW = ATT_CHUNK / (ATT_THREADS / 32);      // positions per warp: 16
 template <typename T>
-__global__ void __launch_bounds__(ATT_THREADS) attn_partial_kernel(const T* __restrict__ q, const T* __restrict__ kc,
-                                                                   const T* __restrict__ vc, const long long* __restrict__ pos,
-                                                                   float* __restrict__ part, int H, int KV, int S, int nsplit,
-                                                                   float scale_log2e) {
+__global__ void __launch_bounds__(ATT_THREADS) attn_partial_kernel(const T* q, const T* kc,
+                                                                   const T* vc, const long long* pos,
+                                                                   float* part, int H, int KV, int S, int nsplit,
+                                                                   float scale_log2e, int early) {
     using P = typename pair_of<T>::type;
-    pdl_launch_dependents();
+    if (early) pdl_launch_dependents();
     pdl_wait();
     const int G = H / KV, ngrp = (G + ATT_G - 1) / ATT_G;
     int id = blockIdx.x;
@@ -588,22 +596,28 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_kernel(const T* __re
     // partial record per (b, head, split): [m, l, acc[128]]
     for (int g = 0; g < nh; ++g) {
         float* rec = part + ((static_cast<size_t>(b) * H + h0 + g) * nsplit + split) * (ATT_HD + 2);
-        rec[2 + threadIdx.x] = s_acc[0][g][threadIdx.x] + s_acc[1][g][threadIdx.x] + s_acc[2][g][threadIdx.x] + s_acc[3][g][threadIdx.x];
+        if (threadIdx.x < ATT_HD) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < ATT_THREADS / 32; ++w) sum += s_acc[w][g][threadIdx.x];
+            rec[2 + threadIdx.x] = sum;
+        }
         if (threadIdx.x == 0) { rec[0] = n > 0 ? s_m[g] : -INFINITY; rec[1] = n > 0 ? s_l[g] : 0.f; }
     }
+    if (!early) pdl_launch_dependents();
 }
 
 // The same kernel over an FP8 KV cache (codes u8 [B, KV, S, 128], one FP32 scale per position):
 // half the bytes per position. A score is the dot product with the decoded codes times the
 // position's K scale; the position's V scale rides on its softmax weight.
 template <typename T, int FMT>
-__global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* __restrict__ q, const uint8_t* __restrict__ kc,
-                                                                       const float* __restrict__ ksc, const uint8_t* __restrict__ vc,
-                                                                       const float* __restrict__ vsc, const long long* __restrict__ pos,
-                                                                       float* __restrict__ part, int H, int KV, int S, int nsplit,
-                                                                       float scale_log2e) {
+__global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* q, const uint8_t* kc,
+                                                                       const float* ksc, const uint8_t* vc,
+                                                                       const float* vsc, const long long* pos,
+                                                                       float* part, int H, int KV, int S, int nsplit,
+                                                                       float scale_log2e, int early) {
     using P = typename pair_of<T>::type;
-    pdl_launch_dependents();
+    if (early) pdl_launch_dependents();
     pdl_wait();
     const int G = H / KV, ngrp = (G + ATT_G - 1) / ATT_G;
     int id = blockIdx.x;
@@ -630,8 +644,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* 
         for (int it = 0; it < ATT_PW / 4; ++it) {
             const int j = warp * ATT_PW + it * 4 + slot;
             if (j < n) {
-                kr[it] = *reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(j) * ATT_HD + sub * 16);
-                kscale[it] = ksc[row0 + j];
+                kr[it] = __ldcg(reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(j) * ATT_HD + sub * 16));
+                kscale[it] = __ldcg(ksc + row0 + j);
             } else {
                 kr[it] = make_uint4(0u, 0u, 0u, 0u);
                 kscale[it] = 0.f;
@@ -681,7 +695,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* 
 #pragma unroll
     for (int it = 0; it < ATT_PW; ++it) {
         const int j = warp * ATT_PW + it;
-        vr[it] = j < n ? *reinterpret_cast<const uint32_t*>(vbase + static_cast<size_t>(j) * ATT_HD + lane * 4) : 0u;
+        vr[it] = j < n ? __ldcg(reinterpret_cast<const uint32_t*>(vbase + static_cast<size_t>(j) * ATT_HD + lane * 4)) : 0u;
     }
     __syncthreads();
     // ---- per head: maximum, exponentials, sum (warp g serves head g); the weight kept for the
@@ -695,7 +709,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* 
         float l = 0.f;
         for (int j = lane; j < n; j += 32) {
             const float e = exp2f(s_sc[g][j] - m);
-            s_sc[g][j] = e * vsc[row0 + j];
+            s_sc[g][j] = e * __ldcg(vsc + row0 + j);
             l += e;
         }
 #pragma unroll
@@ -729,14 +743,20 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* 
     __syncthreads();
     for (int g = 0; g < nh; ++g) {
         float* rec = part + ((static_cast<size_t>(b) * H + h0 + g) * nsplit + split) * (ATT_HD + 2);
-        rec[2 + threadIdx.x] = s_acc[0][g][threadIdx.x] + s_acc[1][g][threadIdx.x] + s_acc[2][g][threadIdx.x] + s_acc[3][g][threadIdx.x];
+        if (threadIdx.x < ATT_HD) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < ATT_THREADS / 32; ++w) sum += s_acc[w][g][threadIdx.x];
+            rec[2 + threadIdx.x] = sum;
+        }
         if (threadIdx.x == 0) { rec[0] = n > 0 ? s_m[g] : -INFINITY; rec[1] = n > 0 ? s_l[g] : 0.f; }
     }
+    if (!early) pdl_launch_dependents();
 }
 
 template <typename T>
-__global__ void __launch_bounds__(ATT_HD) attn_merge_kernel(const float* __restrict__ part, T* __restrict__ out, int nsplit) {
-    pdl_launch_dependents();
+__global__ void __launch_bounds__(ATT_HD) attn_merge_kernel(const float* part, T* out, int nsplit, int early) {
+    if (early) pdl_launch_dependents();
     pdl_wait();
     const float* rec = part + static_cast<size_t>(blockIdx.x) * nsplit * (ATT_HD + 2);     // blockIdx.x = b * H + h
     __shared__ float s_w[128];                          // weight of each chunk (nsplit <= 128)
@@ -774,6 +794,7 @@ __global__ void __launch_bounds__(ATT_HD) attn_merge_kernel(const float* __restr
     }
     for (; s < nsplit; ++s) a = fmaf(s_w[s], col[static_cast<size_t>(s) * (ATT_HD + 2)], a);
     store_as(out + static_cast<size_t>(blockIdx.x) * ATT_HD + threadIdx.x, a * s_norm);
+    if (!early) pdl_launch_dependents();
 }
 
 // Launch with programmatic stream serialization (the kernel may start while its predecessor is
@@ -808,6 +829,15 @@ int glue_status(unsigned int* out, cudaStream_t st) {
 // loading, graph instantiation, a garbage-collection pause on its host thread) and still ends the
 // kernel if a peer is gone.
 static long long g_ar_wait_cycles = 1ll << 35;
+
+// The attention kernels release their dependents when their results are stored, not at once like
+// the other helpers: what follows them is the output projection's GEMV, whose weight prefetch
+// then competes with the KV cache for HBM -- measured inside a batch-1 decode step, releasing at
+// once costs 13 % of the step (8 blocks: 0.94 ms against 0.82). TFP8B_ATT_EARLY=1 restores it.
+static int att_early() {
+    static const int v = [] { const char* e = getenv("TFP8B_ATT_EARLY"); return (e && e[0] == '1') ? 1 : 0; }();
+    return v;
+}
 
 static int grid_of(long long work) {
     long long blocks = (work + 255) / 256;
@@ -923,17 +953,17 @@ extern "C" int tfp8b_attn_decode(const void* q, const void* k_cache, const void*
     if (dtype == TFP8B_F16) {
         rc = launch_pdl("tfp8b_attn_decode", attn_partial_kernel<__half>, B * KV * ngrp * nsplit, ATT_THREADS, st, static_cast<const __half*>(q),
                         static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), pos, scratch, H, KV, max_seq, nsplit,
-                        scale_log2e);
+                        scale_log2e, att_early());
         if (rc != TFP8B_OK) return rc;
         return launch_pdl("tfp8b_attn_decode", attn_merge_kernel<__half>, B * H, ATT_HD, st, static_cast<const float*>(scratch),
-                          static_cast<__half*>(out), nsplit);
+                          static_cast<__half*>(out), nsplit, att_early());
     }
     rc = launch_pdl("tfp8b_attn_decode", attn_partial_kernel<__nv_bfloat16>, B * KV * ngrp * nsplit, ATT_THREADS, st,
                     static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
-                    static_cast<const __nv_bfloat16*>(v_cache), pos, scratch, H, KV, max_seq, nsplit, scale_log2e);
+                    static_cast<const __nv_bfloat16*>(v_cache), pos, scratch, H, KV, max_seq, nsplit, scale_log2e, att_early());
     if (rc != TFP8B_OK) return rc;
     return launch_pdl("tfp8b_attn_decode", attn_merge_kernel<__nv_bfloat16>, B * H, ATT_HD, st, static_cast<const float*>(scratch),
-                      static_cast<__nv_bfloat16*>(out), nsplit);
+                      static_cast<__nv_bfloat16*>(out), nsplit, att_early());
 }
 
 template <typename T>
@@ -943,13 +973,13 @@ static int attn_fp8_launch(int fmt, int grid, cudaStream_t st, const void* q, co
     int rc;
     if (fmt == TFP8B_E4M3FN)
         rc = launch_pdl("tfp8b_attn_decode_fp8", attn_partial_fp8_kernel<T, TFP8B_E4M3FN>, grid, ATT_THREADS, st, static_cast<const T*>(q),
-                        k_codes, k_scale, v_codes, v_scale, pos, scratch, H, KV, max_seq, nsplit, scale_log2e);
+                        k_codes, k_scale, v_codes, v_scale, pos, scratch, H, KV, max_seq, nsplit, scale_log2e, att_early());
     else
         rc = launch_pdl("tfp8b_attn_decode_fp8", attn_partial_fp8_kernel<T, TFP8B_E5M2>, grid, ATT_THREADS, st, static_cast<const T*>(q),
-                        k_codes, k_scale, v_codes, v_scale, pos, scratch, H, KV, max_seq, nsplit, scale_log2e);
+                        k_codes, k_scale, v_codes, v_scale, pos, scratch, H, KV, max_seq, nsplit, scale_log2e, att_early());
     if (rc != TFP8B_OK) return rc;
     return launch_pdl("tfp8b_attn_decode_fp8", attn_merge_kernel<T>, B * H, ATT_HD, st, static_cast<const float*>(scratch),
-                      static_cast<T*>(out), nsplit);
+                      static_cast<T*>(out), nsplit, att_early());
 }
 
 extern "C" int tfp8b_attn_decode_fp8(const void* q, const uint8_t* k_codes, const float* k_scale, const uint8_t* v_codes,

@@ -67,6 +67,7 @@ struct GemvParams {
     void* y;
     int M, N, K, G, scale_kind, y_dt;
     int nstages, wpitch, xpitch, wstage_bytes, stage_bytes, x_resident, xres_bytes, ntiles, pdl;
+    int trig;                 // when the kernel releases its dependents: 0 at its start, 1 once its last weight stage is requested
     // Activations computed by the kernel itself instead of copied (16-bit types, resident rows):
     //   xmode 1  x = RMSNorm(xa + xb) * xw: the residual update (xb may be null) and the norm of a
     //            decoder block; the CTA with index 0 also stores the updated residual to xout
@@ -345,7 +346,7 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         if (TMA) { tma_prefetch_desc(&tm_w); tma_prefetch_desc(&tm_x); }
     }
     __syncthreads();
-    if (p.pdl) pdl_launch_dependents();
+    if (p.pdl && p.trig == 0) pdl_launch_dependents();
 
     if (warp == GV_WARPS) {
         // ---------------------------------------------------------------- producer warp
@@ -417,6 +418,9 @@ gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             if (++c == nchunks) { c = 0; ++t; }
             if (++slot == S) { slot = 0; phase ^= 1u; }
         }
+        // every byte this CTA will ask of HBM has been requested: from here on a successor's
+        // weight prefetch competes with nothing of this kernel
+        if (p.pdl && p.trig == 1) pdl_launch_dependents();
     } else if (warp < GV_WARPS) {
         // ---------------------------------------------------------------- consumer warps
         const int g = lane >> 2, tig = lane & 3;
@@ -799,6 +803,10 @@ static int gemv_run(const GemvSetup& g, const void* x, void* y, unsigned int fla
     GemvParams p = g.p;
     p.x = x; p.y = y; p.xa = xa; p.xb = xb; p.xw = xw; p.xout = xout; p.xeps = xeps;
     p.pdl = pdl_mode_of(flags);
+    // TFP8B_GEMV_TRIGGER=1: release the dependents once the last weight stage is requested instead of
+    // at the kernel's start (tuning; measured inside a decode step: no gain at batch 1 and 8, 7 % slower at 4)
+    static const int trig = [] { const char* v = getenv("TFP8B_GEMV_TRIGGER"); return (v && v[0] == '1') ? 1 : 0; }();
+    p.trig = trig;
     CUtensorMap tx = {};
     if (g.tma && !p.x_resident) {                 // activations that travel with the stages: their own tensor map
         const int rc = gemv_x_map(&tx, x, g.x_dtype, p.M, p.K);
