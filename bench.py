@@ -644,14 +644,13 @@ def llama_decode_measurements(device, peaks, world, batches=(1, 4, 8), prompt=20
         # The same model and workload with the KV cache held as FP8 codes + one scale per token and KV
         # head (FP8Config(kv_cache="fp8")): the decode attention then reads half the bytes. Beside it,
         # for a like-for-like comparison of the cache formats, the library's attention kernel over the
-        # 16-bit cache at every batch size (the default rows above use it for one sequence and torch's
-        # attention for a batch).
+        # 16-bit cache (the default rows above use torch's attention).
         cfg = LLAMA3_8B
         def kv_bytes(B, per_elem):        # K and V of every layer, read once per step at mid-run length
             return 2 * cfg.n_layers * cfg.n_kv_heads * (prompt + new_tokens // 2) * B * (cfg.head_dim * per_elem + (4 if per_elem == 1 else 0))
         model.attn_kernel = True
         result["runs_attn_kernel_fp16_cache"] = _decode_rows(model, device, peaks, world, batches, prompt, new_tokens, stream_bytes)
-        model.attn_kernel, model.kv_fmt = None, "e4m3fn"
+        model.attn_kernel, model.kv_fmt = False, "e4m3fn"
         keep8 = {}
         result["runs_kv_cache_fp8"] = _decode_rows(model, device, peaks, world, batches, prompt, new_tokens, stream_bytes, keep=keep8)
         model.kv_fmt = None
@@ -851,7 +850,7 @@ def run_probe(args):
         model = build_fp8_llama(cfg, device, torch.float16)
         # TFP8_PROBE_ATTN=kernel: the library's decode attention instead of torch's; =fp8: that kernel over an FP8 KV cache
         mode = os.environ.get("TFP8_PROBE_ATTN", "")
-        model.attn_kernel = {"kernel": True, "sdpa": False}.get(mode)       # default: the harness chooses
+        model.attn_kernel = mode == "kernel"
         model.kv_fmt = "e4m3fn" if mode == "fp8" else None
         run = DecodeRunner(model, B)
         run.prefill(torch.randint(0, cfg.vocab, (B, prompt), device=device))

@@ -832,8 +832,8 @@ static long long g_ar_wait_cycles = 1ll << 35;
 
 // The attention kernels release their dependents when their results are stored, not at once like
 // the other helpers: what follows them is the output projection's GEMV, whose weight prefetch
-// then competes with the KV cache for HBM -- measured inside a batch-1 decode step, releasing at
-// once costs 13 % of the step (8 blocks: 0.94 ms against 0.82). TFP8B_ATT_EARLY=1 restores it.
+// then competes with the KV cache for HBM -- measured inside a batch-1 decode step of 8 blocks,
+// releasing at once costs 13 % of the step (0.94 ms against 0.82). TFP8B_ATT_EARLY=1 restores it.
 static int att_early() {
     static const int v = [] { const char* e = getenv("TFP8B_ATT_EARLY"); return (e && e[0] == '1') ? 1 : 0; }();
     return v;

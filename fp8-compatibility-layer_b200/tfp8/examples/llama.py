@@ -245,9 +245,9 @@ class Llama(nn.Module):
     def __init__(self, cfg: LlamaConfig = LLAMA3_8B, device="cpu", dtype=torch.float16, tp=1):
         super().__init__()
         self.cfg, self.tp = cfg, tp
-        # decode attention: None = the library's split-KV kernel for a single sequence and torch SDPA
-        # (cuDNN) for a batch -- each where it measured faster inside the step --, True / False force one
-        self.attn_kernel = None
+        # decode attention: torch SDPA (cuDNN) by default; True selects the library's split-KV kernel
+        # (inside a full 32-block step it is 2 % slower for one sequence, 10 % for eight)
+        self.attn_kernel = False
         # None: the KV cache holds activations as they are. "e4m3fn" / "e5m2": FP8 codes + one scale per
         # token and KV head (FP8Config(kv_cache="fp8")); the decode step then always uses the library's
         # attention kernel, which reads the codes (torch's would need the whole cache decoded first).
@@ -287,8 +287,7 @@ class Llama(nn.Module):
         mask = None
         if not prefill:
             hd, blk = self.cfg.head_dim, self.layers[0]
-            use_kernel = self.kv_fmt is not None or (tokens.shape[0] == 1 if self.attn_kernel is None else self.attn_kernel)
-            if use_kernel and fused and tokens.shape[1] == 1 and hd == 128:
+            if (self.attn_kernel or self.kv_fmt is not None) and fused and tokens.shape[1] == 1 and hd == 128:
                 mask = False             # decode attention kernel: reads the position itself, no mask tensor
             else:
                 seq = torch.arange(self.cfg.max_seq, device=pos.device)
