@@ -846,7 +846,7 @@ def run_probe(args):
         # then `steps` graph-replayed decode steps (a launch list of one step under a profiler)
         from tfp8.examples.llama import LlamaConfig, DecodeRunner, build_fp8_llama
         B, layers, prompt = M, N, K
-        cfg = LlamaConfig(n_layers=layers, max_seq=prompt + 64)
+        cfg = LlamaConfig(n_layers=layers, max_seq=prompt + max(64, args.steps + 8))
         model = build_fp8_llama(cfg, device, torch.float16)
         # TFP8_PROBE_ATTN=kernel: the library's decode attention instead of torch's; =fp8: that kernel over an FP8 KV cache
         mode = os.environ.get("TFP8_PROBE_ATTN", "")
