@@ -490,7 +490,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_kernel(const T* q, c
     const int s0 = split * chunk, n = max(0, min(len, s0 + chunk) - s0);
     __shared__ float s_sc[ATT_G][ATT_CHUNK];
     __shared__ float s_m[ATT_G], s_l[ATT_G];
-    __shared__ float s_acc[ATT_THREADS / 32][ATT_G][ATT_HD];
+    __shared__ __align__(16) float s_acc[ATT_THREADS / 32][ATT_G][ATT_HD];     // written as float4
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const T* kbase = kc + ((static_cast<size_t>(b) * KV + kvh) * S + s0) * ATT_HD;
     const T* vbase = vc + ((static_cast<size_t>(b) * KV + kvh) * S + s0) * ATT_HD;
@@ -607,15 +607,43 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_kernel(const T* q, c
     if (!early) pdl_launch_dependents();
 }
 
-// The same kernel over an FP8 KV cache (codes u8 [B, KV, S, 128], one FP32 scale per position):
-// half the bytes per position. A score is the dot product with the decoded codes times the
-// position's K scale; the position's V scale rides on its softmax weight.
+// Decode attention over an FP8 KV cache (codes u8 [B, KV, S, 128], one FP32 scale per position),
+// both products on the tensor cores (mma.sync m16n8k16, fp16 operands, FP32 accumulate): with
+// scalar FP32 arithmetic the kernel issued 0.25 warp instructions per byte of cache, more than an
+// SM can issue in the time its share of HBM delivers that byte, and reading half the bytes of a
+// 16-bit cache bought nothing.
+//   scores^T [16 positions x 8 heads] = K [16 x 128] Q^T: A = codes decoded to fp16 (exact), one
+//     position per fragment row; B = Q, the KV head's query heads as columns (4 of 8 used). The
+//     128 dims are contracted in an order that lets a lane read its codes as two 16-byte loads:
+//     lane (g, t) holds bytes [32 t, 32 t + 32) of rows g and g + 8, and k-step c of 8 contracts
+//     dims 32 t + 4 c .. + 3; Q is loaded in the same order. The K scale and 1 / sqrt(hd) are
+//     applied to the FP32 scores.
+//   out^T [128 dims x 8 heads] = V^T [128 x 16 positions] P^T: the contraction now runs over
+//     positions, which is the slow index of the cache; a fragment register wants the same dim of
+//     two neighbouring positions, and a byte permute of the two positions' code words makes that
+//     pair before the conversion. P = exp2(score - max) is rounded to fp16 as a high and a low
+//     part (two MMAs), the V scale relative to the chunk's largest rides on the decoded V (a power
+//     of two: exact), the largest itself on the FP32 result.
+// A CTA serves one (sequence, KV head, up to four query heads, 128 positions); a warp 32 of them.
+constexpr int ATT8_CHUNK = 128;
+constexpr int ATT8_PW = ATT8_CHUNK / (ATT_THREADS / 32);       // positions per warp: 32
+static_assert(ATT_THREADS == 128 && ATT8_PW % 16 == 0, "four warps, whole 16-position blocks");
+
+__device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t to_f16x2(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ uint32_t to_f16x2(__nv_bfloat162 v) {      // every bf16 in fp16's range is exact in fp16
+    const float2 f = __bfloat1622float2(v);
+    __half2 h = __floats2half2_rn(f.x, f.y);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
 template <typename T, int FMT>
-__global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* q, const uint8_t* kc,
-                                                                       const float* ksc, const uint8_t* vc,
-                                                                       const float* vsc, const long long* pos,
-                                                                       float* part, int H, int KV, int S, int nsplit,
-                                                                       float scale_log2e, int early) {
+__global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* q, const uint8_t* kc, const float* ksc, const uint8_t* vc,
+                                                                       const float* vsc, const long long* pos, float* part, int H, int KV,
+                                                                       int S, int nsplit, float scale_log2e, int early) {
     using P = typename pair_of<T>::type;
     if (early) pdl_launch_dependents();
     pdl_wait();
@@ -626,130 +654,168 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* 
     const int kvh = id % KV, b = id / KV;
     const int h0 = kvh * G + grp * ATT_G, nh = min(ATT_G, G - grp * ATT_G);
     const int len = static_cast<int>(min(static_cast<long long>(S), pos[0] + 1));
-    const int chunk = min(ATT_CHUNK, (len + nsplit - 1) / nsplit);
+    const int chunk = min(ATT8_CHUNK, (len + nsplit - 1) / nsplit);
     const int s0 = split * chunk, n = max(0, min(len, s0 + chunk) - s0);
-    __shared__ float s_sc[ATT_G][ATT_CHUNK];
-    __shared__ float s_m[ATT_G], s_l[ATT_G];
-    __shared__ float s_acc[ATT_THREADS / 32][ATT_G][ATT_HD];
+    __shared__ __align__(16) float s_sc[ATT_G][ATT8_CHUNK];         // scores
+    __shared__ __align__(16) __half s_ph[ATT_G][ATT8_CHUNK];        // softmax weights, high part (read as pairs)
+    __shared__ __align__(16) __half s_pl[ATT_G][ATT8_CHUNK];        // ... and low part
+    __shared__ float s_m[ATT_G], s_l[ATT_G], s_vmax;
+    __shared__ __align__(16) float s_acc[ATT_THREADS / 32][ATT_G][ATT_HD];   // written as pairs of floats
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
     const size_t row0 = (static_cast<size_t>(b) * KV + kvh) * S + s0;
     const uint8_t* kbase = kc + row0 * ATT_HD;
     const uint8_t* vbase = vc + row0 * ATT_HD;
-    // ---- scores: warp w takes positions [16 w, 16 w + 16); 8 lanes per position, 16 codes per lane
+    // ---- scores
     {
-        const int sub = lane & 7, slot = lane >> 3;
-        uint4 kr[ATT_PW / 4];
-        float kscale[ATT_PW / 4];
+        // Q of head g (columns 4..7 of the B operand stay zero), dims [32 t, 32 t + 32) as 16 fp16 pairs
+        uint32_t qreg[16];
+        if (g < nh) {
+            const uint4* qp = reinterpret_cast<const uint4*>(q + (static_cast<size_t>(b) * H + h0 + g) * ATT_HD + t * 32);
 #pragma unroll
-        for (int it = 0; it < ATT_PW / 4; ++it) {
-            const int j = warp * ATT_PW + it * 4 + slot;
-            if (j < n) {
-                kr[it] = __ldcg(reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(j) * ATT_HD + sub * 16));
-                kscale[it] = __ldcg(ksc + row0 + j);
+            for (int i = 0; i < 4; ++i) {
+                const uint4 v = qp[i];
+                const P* pp = reinterpret_cast<const P*>(&v);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) qreg[4 * i + e] = to_f16x2(pp[e]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) qreg[i] = 0u;
+        }
+#pragma unroll
+        for (int blk = 0; blk < ATT8_PW / 16; ++blk) {
+            const int j0 = warp * ATT8_PW + blk * 16 + g, j1 = j0 + 8;
+            uint4 k0[2], k1[2];
+            float ks0 = 0.f, ks1 = 0.f;
+            if (j0 < n) {
+                const uint4* kp = reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(j0) * ATT_HD + t * 32);
+                k0[0] = __ldcg(kp); k0[1] = __ldcg(kp + 1);
+                ks0 = __ldcg(ksc + row0 + j0) * scale_log2e;
             } else {
-                kr[it] = make_uint4(0u, 0u, 0u, 0u);
-                kscale[it] = 0.f;
+                k0[0] = k0[1] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (j1 < n) {
+                const uint4* kp = reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(j1) * ATT_HD + t * 32);
+                k1[0] = __ldcg(kp); k1[1] = __ldcg(kp + 1);
+                ks1 = __ldcg(ksc + row0 + j1) * scale_log2e;
+            } else {
+                k1[0] = k1[1] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            const uint32_t w0[8] = {k0[0].x, k0[0].y, k0[0].z, k0[0].w, k0[1].x, k0[1].y, k0[1].z, k0[1].w};
+            const uint32_t w1[8] = {k1[0].x, k1[0].y, k1[0].z, k1[0].w, k1[1].x, k1[1].y, k1[1].z, k1[1].w};
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int cstep = 0; cstep < 8; ++cstep) {
+                uint32_t a0, a2, a1, a3;
+                dec4<FMT, false>(w0[cstep], a0, a2);          // row g: dims +0,+1 | +2,+3
+                dec4<FMT, false>(w1[cstep], a1, a3);          // row g + 8
+                mma16816(c, a0, a1, a2, a3, qreg[2 * cstep], qreg[2 * cstep + 1]);
+            }
+            // c0, c1: position j0, heads 2t, 2t + 1; c2, c3: position j1
+            if (t < 2) {
+                const int hA = 2 * t, hB = 2 * t + 1;
+                if (j0 < n) { if (hA < nh) s_sc[hA][j0] = c[0] * ks0; if (hB < nh) s_sc[hB][j0] = c[1] * ks0; }
+                if (j1 < n) { if (hA < nh) s_sc[hA][j1] = c[2] * ks1; if (hB < nh) s_sc[hB][j1] = c[3] * ks1; }
             }
         }
-        float qf[ATT_G][16];
-#pragma unroll
-        for (int g = 0; g < ATT_G; ++g) {
-            const T* qp = q + (static_cast<size_t>(b) * H + h0 + min(g, nh - 1)) * ATT_HD + sub * 16;
-            const uint4 a0 = reinterpret_cast<const uint4*>(qp)[0], a1 = reinterpret_cast<const uint4*>(qp)[1];
-            const P* p0 = reinterpret_cast<const P*>(&a0);
-            const P* p1 = reinterpret_cast<const P*>(&a1);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f0 = unpack2(p0[i]), f1 = unpack2(p1[i]);
-                qf[g][2 * i] = f0.x * scale_log2e; qf[g][2 * i + 1] = f0.y * scale_log2e;
-                qf[g][8 + 2 * i] = f1.x * scale_log2e; qf[g][9 + 2 * i] = f1.y * scale_log2e;
-            }
-        }
-#pragma unroll
-        for (int it = 0; it < ATT_PW / 4; ++it) {
-            const int j = warp * ATT_PW + it * 4 + slot;
-            float kf[16];
-            const uint32_t w[4] = {kr[it].x, kr[it].y, kr[it].z, kr[it].w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint32_t p01, p23;
-                dec4<FMT, false>(w[i], p01, p23);
-                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&p01));
-                const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&p23));
-                kf[4 * i] = f0.x; kf[4 * i + 1] = f0.y; kf[4 * i + 2] = f1.x; kf[4 * i + 3] = f1.y;
-            }
-#pragma unroll
-            for (int g = 0; g < ATT_G; ++g) {
-                float d = 0.f;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) d = fmaf(qf[g][i], kf[i], d);
-                d += __shfl_xor_sync(0xffffffffu, d, 1);
-                d += __shfl_xor_sync(0xffffffffu, d, 2);
-                d += __shfl_xor_sync(0xffffffffu, d, 4);
-                if (sub == 0 && j < n) s_sc[g][j] = d * kscale[it];
-            }
-        }
-    }
-    // ---- the V codes of this warp's positions, requested now, used after the softmax
-    uint32_t vr[ATT_PW];                               // lane owns dims 4 lane .. 4 lane + 3
-#pragma unroll
-    for (int it = 0; it < ATT_PW; ++it) {
-        const int j = warp * ATT_PW + it;
-        vr[it] = j < n ? __ldcg(reinterpret_cast<const uint32_t*>(vbase + static_cast<size_t>(j) * ATT_HD + lane * 4)) : 0u;
     }
     __syncthreads();
-    // ---- per head: maximum, exponentials, sum (warp g serves head g); the weight kept for the
-    // V pass carries the position's V scale
+    // ---- per head: maximum, exponentials (fp16 high + low part), sum; one warp also finds the
+    // chunk's largest V scale
     if (warp < nh) {
-        const int g = warp;
+        const int hh = warp;
         float m = -INFINITY;
-        for (int j = lane; j < n; j += 32) m = fmaxf(m, s_sc[g][j]);
+        for (int j = lane; j < n; j += 32) m = fmaxf(m, s_sc[hh][j]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         float l = 0.f;
-        for (int j = lane; j < n; j += 32) {
-            const float e = exp2f(s_sc[g][j] - m);
-            s_sc[g][j] = e * __ldcg(vsc + row0 + j);
-            l += e;
+        for (int j = lane; j < ATT8_CHUNK; j += 32) {
+            float e = 0.f;
+            if (j < n) { e = exp2f(s_sc[hh][j] - m); l += e; }
+            const __half hi = __float2half_rn(e);
+            s_ph[hh][j] = hi;
+            s_pl[hh][j] = __float2half_rn(e - __half2float(hi));
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-        if (lane == 0) { s_m[g] = m; s_l[g] = l; }
+        if (lane == 0) { s_m[hh] = m; s_l[hh] = l; }
+    }
+    if (warp == ATT_THREADS / 32 - 1) {
+        float vm = 0.f;
+        for (int j = lane; j < n; j += 32) vm = fmaxf(vm, __ldcg(vsc + row0 + j));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) vm = fmaxf(vm, __shfl_xor_sync(0xffffffffu, vm, o));
+        if (lane == 0) s_vmax = vm > 0.f ? vm : 1.f;
     }
     __syncthreads();
-    // ---- weighted V over this warp's positions, then the four warps' sums are added
-    float acc[ATT_G][4];
+    // ---- out^T = V^T P^T over this warp's positions
+    float o[8][4];
 #pragma unroll
-    for (int g = 0; g < ATT_G; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+    for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    const float inv_vmax = 1.f / s_vmax;                          // a power of two: exact
 #pragma unroll
-    for (int it = 0; it < ATT_PW; ++it) {
-        const int j = warp * ATT_PW + it;
-        if (j < n) {
-            uint32_t p01, p23;
-            dec4<FMT, false>(vr[it], p01, p23);
-            const float2 v01 = __half22float2(*reinterpret_cast<const __half2*>(&p01));
-            const float2 v23 = __half22float2(*reinterpret_cast<const __half2*>(&p23));
+    for (int blk = 0; blk < ATT8_PW / 16; ++blk) {
+        const int pb = warp * ATT8_PW + blk * 16;
+        const int pj[4] = {pb + 2 * t, pb + 2 * t + 1, pb + 2 * t + 8, pb + 2 * t + 9};
+        uint4 vv[4];
+        float vs[4];
 #pragma unroll
-            for (int g = 0; g < ATT_G; ++g) {
-                const float w = s_sc[g][j];
-                acc[g][0] = fmaf(w, v01.x, acc[g][0]); acc[g][1] = fmaf(w, v01.y, acc[g][1]);
-                acc[g][2] = fmaf(w, v23.x, acc[g][2]); acc[g][3] = fmaf(w, v23.y, acc[g][3]);
+        for (int u = 0; u < 4; ++u) {
+            if (pj[u] < n) {
+                vv[u] = __ldcg(reinterpret_cast<const uint4*>(vbase + static_cast<size_t>(pj[u]) * ATT_HD + g * 16));
+                vs[u] = __ldcg(vsc + row0 + pj[u]) * inv_vmax;     // <= 1; below 2^-24 it rounds to 0: such a row is noise beside the largest
+            } else {
+                vv[u] = make_uint4(0u, 0u, 0u, 0u);
+                vs[u] = 0.f;
             }
         }
-    }
+        const __half2 sAB = __floats2half2_rn(vs[0], vs[1]), sCD = __floats2half2_rn(vs[2], vs[3]);
+        // B operand: P of head g at positions (2t, 2t+1) and (2t+8, 2t+9) of the block
+        uint32_t bh0 = 0u, bh1 = 0u, bl0 = 0u, bl1 = 0u;
+        if (g < nh) {
+            bh0 = *reinterpret_cast<const uint32_t*>(&s_ph[g][pb + 2 * t]); bh1 = *reinterpret_cast<const uint32_t*>(&s_ph[g][pb + 2 * t + 8]);
+            bl0 = *reinterpret_cast<const uint32_t*>(&s_pl[g][pb + 2 * t]); bl1 = *reinterpret_cast<const uint32_t*>(&s_pl[g][pb + 2 * t + 8]);
+        }
+        const uint32_t wA[4] = {vv[0].x, vv[0].y, vv[0].z, vv[0].w}, wB[4] = {vv[1].x, vv[1].y, vv[1].z, vv[1].w};
+        const uint32_t wC[4] = {vv[2].x, vv[2].y, vv[2].z, vv[2].w}, wD[4] = {vv[3].x, vv[3].y, vv[3].z, vv[3].w};
 #pragma unroll
-    for (int g = 0; g < ATT_G; ++g)
-        *reinterpret_cast<float4*>(&s_acc[warp][g][lane * 4]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+        for (int i = 0; i < 8; ++i) {
+            // fragment rows g and g + 8 = dims 16 g + 2 i and 16 g + 2 i + 1: bytes (2i) & 3 and + 1 of word i / 2
+            const int w = i >> 1;
+            const uint32_t selA = (i & 1) ? 0x0062u : 0x0040u, selB = (i & 1) ? 0x0073u : 0x0051u;    // {x.b, y.b} as a 16-bit pair
+            uint32_t a0 = dec2_f16<FMT>(__byte_perm(wA[w], wB[w], selA) & 0xFFFFu);
+            uint32_t a1 = dec2_f16<FMT>(__byte_perm(wA[w], wB[w], selB) & 0xFFFFu);
+            uint32_t a2 = dec2_f16<FMT>(__byte_perm(wC[w], wD[w], selA) & 0xFFFFu);
+            uint32_t a3 = dec2_f16<FMT>(__byte_perm(wC[w], wD[w], selB) & 0xFFFFu);
+            __half2 x0 = __hmul2(*reinterpret_cast<__half2*>(&a0), sAB), x1 = __hmul2(*reinterpret_cast<__half2*>(&a1), sAB);
+            __half2 x2 = __hmul2(*reinterpret_cast<__half2*>(&a2), sCD), x3 = __hmul2(*reinterpret_cast<__half2*>(&a3), sCD);
+            a0 = *reinterpret_cast<uint32_t*>(&x0); a1 = *reinterpret_cast<uint32_t*>(&x1);
+            a2 = *reinterpret_cast<uint32_t*>(&x2); a3 = *reinterpret_cast<uint32_t*>(&x3);
+            mma16816(o[i], a0, a1, a2, a3, bh0, bh1);
+            mma16816(o[i], a0, a1, a2, a3, bl0, bl1);
+        }
+    }
+    // o[i][0], [1]: dim 16 g + 2 i, heads 2t, 2t + 1; o[i][2], [3]: dim 16 g + 2 i + 1
+    if (t < 2) {
+        const float vmax = s_vmax;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int d = 16 * g + 2 * i;
+            *reinterpret_cast<float2*>(&s_acc[warp][2 * t][d]) = make_float2(o[i][0] * vmax, o[i][2] * vmax);
+            *reinterpret_cast<float2*>(&s_acc[warp][2 * t + 1][d]) = make_float2(o[i][1] * vmax, o[i][3] * vmax);
+        }
+    }
     __syncthreads();
-    for (int g = 0; g < nh; ++g) {
-        float* rec = part + ((static_cast<size_t>(b) * H + h0 + g) * nsplit + split) * (ATT_HD + 2);
+    for (int hh = 0; hh < nh; ++hh) {
+        float* rec = part + ((static_cast<size_t>(b) * H + h0 + hh) * nsplit + split) * (ATT_HD + 2);
         if (threadIdx.x < ATT_HD) {
             float sum = 0.f;
 #pragma unroll
-            for (int w = 0; w < ATT_THREADS / 32; ++w) sum += s_acc[w][g][threadIdx.x];
+            for (int w = 0; w < ATT_THREADS / 32; ++w) sum += s_acc[w][hh][threadIdx.x];
             rec[2 + threadIdx.x] = sum;
         }
-        if (threadIdx.x == 0) { rec[0] = n > 0 ? s_m[g] : -INFINITY; rec[1] = n > 0 ? s_l[g] : 0.f; }
+        if (threadIdx.x == 0) { rec[0] = n > 0 ? s_m[hh] : -INFINITY; rec[1] = n > 0 ? s_l[hh] : 0.f; }
     }
     if (!early) pdl_launch_dependents();
 }
@@ -994,10 +1060,10 @@ extern "C" int tfp8b_attn_decode_fp8(const void* q, const uint8_t* k_codes, cons
     TFP8B_REQUIRE(q && k_codes && k_scale && v_codes && v_scale && pos && out && scratch, TFP8B_ERR_INVALID,
                   "tfp8b_attn_decode_fp8: null pointer");
     TFP8B_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_codes)) & 15u) == 0 &&
-                  (reinterpret_cast<uintptr_t>(v_codes) & 3u) == 0, TFP8B_ERR_INVALID,
-                  "tfp8b_attn_decode_fp8: q and k_codes must be 16-byte aligned, v_codes 4-byte aligned");
-    const int nsplit = (max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
-    TFP8B_REQUIRE(nsplit <= 128, TFP8B_ERR_UNSUPPORTED, "tfp8b_attn_decode_fp8: max_seq %d (at most %d is built)", max_seq, 128 * ATT_CHUNK);
+                  (reinterpret_cast<uintptr_t>(v_codes) & 15u) == 0, TFP8B_ERR_INVALID,
+                  "tfp8b_attn_decode_fp8: q, k_codes and v_codes must be 16-byte aligned");
+    const int nsplit = (max_seq + ATT8_CHUNK - 1) / ATT8_CHUNK;
+    TFP8B_REQUIRE(nsplit <= 128, TFP8B_ERR_UNSUPPORTED, "tfp8b_attn_decode_fp8: max_seq %d (at most %d is built)", max_seq, 128 * ATT8_CHUNK);
     const int ngrp = (H / KV + ATT_G - 1) / ATT_G;
     const long long need = static_cast<long long>(B) * H * nsplit * (ATT_HD + 2);
     TFP8B_REQUIRE(scratch_floats >= need, TFP8B_ERR_INVALID, "tfp8b_attn_decode_fp8: scratch of %lld floats, %lld needed", scratch_floats, need);
