@@ -830,6 +830,11 @@ __global__ void __launch_bounds__(ATT_HD) attn_merge_kernel(const float* part, T
     // the chunks' maxima and sums, one per thread, then the weights exp2(m_s - m) and the normaliser
     float ms = -INFINITY, ls = 0.f;
     if (static_cast<int>(threadIdx.x) < nsplit) { ms = rec[threadIdx.x * (ATT_HD + 2)]; ls = rec[threadIdx.x * (ATT_HD + 2) + 1]; }
+    constexpr int MERGE_PRE = 16;
+    const float* col = rec + 2 + threadIdx.x;
+    float pre[MERGE_PRE];
+#pragma unroll
+    for (int u = 0; u < MERGE_PRE; ++u) pre[u] = u < nsplit ? col[static_cast<size_t>(u) * (ATT_HD + 2)] : 0.f;
     float m = ms;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -847,18 +852,19 @@ __global__ void __launch_bounds__(ATT_HD) attn_merge_kernel(const float* part, T
     __syncthreads();
     if (threadIdx.x == 0) s_norm = 1.f / (s_red[0] + s_red[1] + s_red[2] + s_red[3]);
     __syncthreads();
-    // thread d: weighted sum of the chunks' dim d, loads eight at a time
+    // thread d: weighted sum of the chunks' dim d. The first 16 chunks were requested before the
+    // reductions above (they do not depend on the weights); the rest comes eight at a time, the
+    // last batch predicated -- never one dependent load after another.
     float a = 0.f;
-    const float* col = rec + 2 + threadIdx.x;
-    int s = 0;
-    for (; s + 8 <= nsplit; s += 8) {
+#pragma unroll
+    for (int u = 0; u < MERGE_PRE; ++u) a = fmaf(u < nsplit ? s_w[u] : 0.f, pre[u], a);
+    for (int s = MERGE_PRE; s < nsplit; s += 8) {
         float v[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = col[static_cast<size_t>(s + u) * (ATT_HD + 2)];
+        for (int u = 0; u < 8; ++u) v[u] = s + u < nsplit ? col[static_cast<size_t>(s + u) * (ATT_HD + 2)] : 0.f;
 #pragma unroll
-        for (int u = 0; u < 8; ++u) a = fmaf(s_w[s + u], v[u], a);
+        for (int u = 0; u < 8; ++u) a = fmaf(s + u < nsplit ? s_w[s + u] : 0.f, v[u], a);
     }
-    for (; s < nsplit; ++s) a = fmaf(s_w[s], col[static_cast<size_t>(s) * (ATT_HD + 2)], a);
     store_as(out + static_cast<size_t>(blockIdx.x) * ATT_HD + threadIdx.x, a * s_norm);
     if (!early) pdl_launch_dependents();
 }
