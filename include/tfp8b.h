@@ -339,9 +339,11 @@ TFP8B_API int tfp8b_attn_decode(const void* q, const void* k_cache, const void* 
  * activation type, as the 16-bit cache holds them, and then quantized per token and KV head the way
  * quantize_weight quantizes a row (tfp8/quantize.py:15-36: scale 2^ceil(log2(amax / fmax)), 1 for
  * an all-zero row; round to nearest even, saturating) -- tfp8b_quantize on the 16-bit cache rows
- * gives the same bytes. The attention decodes the codes in registers: score = (q . codes) * k_scale,
- * softmax weight * v_scale on the V side, FP32 throughout. hd = 128; fmt E4M3FN or E5M2.
- * k_codes 16-byte aligned. Same scratch as tfp8b_attn_decode. */
+ * gives the same bytes. The attention decodes the codes to fp16 in registers (exact) and runs both
+ * products on the tensor cores with FP32 accumulation: score = (q . codes) * k_scale in FP32, the
+ * softmax weights as an fp16 high + low part, the V scales as exact powers of two. hd = 128; fmt
+ * E4M3FN or E5M2. k_codes and v_codes 16-byte aligned. Scratch: B * H * ceil(max_seq / 128) * 130
+ * floats at least (tfp8b_attn_decode's size is enough). */
 TFP8B_API int tfp8b_rope_kv_store_fp8(const void* qkv, int dtype, const long long* pos, const float* cos_table,
                   const float* sin_table, void* q_out, uint8_t* k_codes, float* k_scale, uint8_t* v_codes,
                   float* v_scale, int B, int T, int H, int KV, int hd, int max_seq, int fmt, tfp8b_stream_t stream);
