@@ -40,25 +40,21 @@ constexpr int GM_BM = 128;          // weight rows per tile = UMMA M = TMEM lane
 constexpr int GM_BK = 64;           // K per k-block: one 128-byte swizzle atom of fp16
 constexpr int GM_DEC_WARPS = 16;
 constexpr int GM_DEC_THREADS = GM_DEC_WARPS * 32;
-#ifndef TFP8B_GM_GROUPS
-#define TFP8B_GM_GROUPS 2
-#endif
-constexpr int GM_NG = TFP8B_GM_GROUPS;                 // decode groups; group g decodes k-blocks g, g + NG, ...
-constexpr int GM_GROUP_THREADS = GM_DEC_THREADS / GM_NG;
-constexpr int GM_GROUP_WARPS = GM_DEC_WARPS / GM_NG;
-constexpr int GM_RPT = GM_NG;                          // rows per decode thread and k-block (128 rows x 4 chunks)
+// Decode groups (a kernel template parameter): group g decodes k-blocks g, g + NG, ...; a decode
+// thread handles NG rows of its k-block. Two groups of eight warps everywhere, except four groups
+// of four warps for tiles of at most 32 activation rows whose K-group scales sit in shared
+// memory: there a k-block is a few hundred instructions of fixed cost per warp, and half as
+// many warps per k-block pay it (eight decoded-tile slots, which only such narrow tiles leave room for).
 constexpr int GM_DEC_WARP0 = 4;                        // warps 0..3: raw producer, MMA, activation producer, second MMA
 constexpr int GM_EPI_WARP0 = GM_DEC_WARP0 + GM_DEC_WARPS;
 constexpr int GM_THREADS = (GM_EPI_WARP0 + 4) * 32;
 constexpr int GM_MAX_SLOTS = 8;     // per ring (decoded tiles, raw codes)
 constexpr int GM_MAX_XSLOTS = 8;    // activation ring
-constexpr int GM_NA = GM_NG == 4 ? 8 : 4;   // decoded-tile slots: the groups' tiles in decode, the one in the MMA, one spare
 constexpr int GM_MAX_DST = 8;       // output destinations of one launch (one per GPU of a tensor-parallel group)
 constexpr int GM_HEADER = 2048;     // barriers, TMEM base, per-row scale reciprocals
 constexpr int GM_A_BYTES = GM_BM * GM_BK * 2;    // decoded fp16 tile
 constexpr int GM_RAW_BYTES = GM_BM * GM_BK;      // raw FP8 tile of one k-block
 constexpr int GM_SMEM_MAX = 232448;              // 227 KB opt-in limit per CTA
-static_assert(GM_NG == 2 || GM_NG == 4, "two or four decode groups");
 
 struct GemmParams {
     int sc_row;               // bytes of one row's K-group scales kept in shared memory per tile, 0 = read from global
@@ -74,6 +70,7 @@ struct GemmParams {
     int ns, sr, nx;      // slots of the decoded-tile ring, of the raw-code ring, of the activation ring
     int rb;              // k-blocks per raw slot: 2 (128 bytes per weight row and copy) or 1
     int x_bytes;         // one activation tile: BN x 64 fp16
+    int ng;              // decode groups (the kernel's NG)
     int nmma;            // MMA-issuing threads; thread t takes k-blocks t, t + nmma, ... into its own accumulator
     int ks, nkbu;        // split-K: every tile is cut into ks units of nkbu k-blocks; ntiles counts units
     int span, span_total, nkbt;   // split-K by spans (span > 0): CTA b owns k-blocks [b * span, (b + 1) * span) of the
@@ -215,9 +212,11 @@ constexpr int GM_OUT_PLAIN = 0, GM_OUT_SPLITK = 1, GM_OUT_WINDOW = 2, GM_OUT_PUS
 // from shared memory one k-block ahead is enough, and the four-times smaller loop body matters:
 // the roles of this kernel together are ~7000 instructions, far more than an instruction cache
 // level close to the schedulers holds.
-template <int FMT, int OUT, int SC>
+template <int FMT, int OUT, int SC, int NG>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
+    static_assert(NG == 2 || NG == 4, "two or four decode groups");
+    constexpr int GROUP_THREADS = GM_DEC_THREADS / NG, GROUP_WARPS = GM_DEC_WARPS / NG;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment of the tile buffers is required by the swizzled layouts.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -257,7 +256,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.ns; ++s) {
-            mbar_init(smem_u32(&hd->full[s]), GM_GROUP_WARPS);          // the warps of the group that decoded it
+            mbar_init(smem_u32(&hd->full[s]), GROUP_WARPS);          // the warps of the group that decoded it
             mbar_init(smem_u32(&hd->empty[s]), 1);
         }
         for (int s = 0; s < p.nx; ++s) {
@@ -266,7 +265,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         }
         for (int s = 0; s < p.sr; ++s) {
             mbar_init(smem_u32(&hd->raw_full[s]), 1);
-            mbar_init(smem_u32(&hd->raw_empty[s]), GM_GROUP_WARPS * p.rb);
+            mbar_init(smem_u32(&hd->raw_empty[s]), GROUP_WARPS * p.rb);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&hd->acc_full[b]), p.nmma);
@@ -419,11 +418,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         // round trips, the proxy fence) overlap another group's work. The loop is kept lean on
         // purpose (32-bit shared addresses, per-thread offsets computed once, ring cursors
         // advanced by addition): with K-group scales this role is bound by instruction issue.
-        constexpr int RPT = GM_RPT;
+        constexpr int RPT = NG;                      // rows per decode thread and k-block (128 rows x 4 chunks)
         constexpr int RSTEP = GM_BM / RPT;           // distance between a thread's rows
         const int td = threadIdx.x - GM_DEC_WARP0 * 32;   // 0 .. GM_DEC_THREADS-1
-        const int group = td / GM_GROUP_THREADS;
-        const int tg = td % GM_GROUP_THREADS;
+        const int group = td / GROUP_THREADS;
+        const int tg = td % GROUP_THREADS;
         const int c = tg & 3;                        // 16-code chunk of the 64-wide K block
         // Rows r0 + RSTEP * h. The 8 threads of a quarter-warp (one shared-memory wavefront of
         // a 16-byte access) work on rows R and R ^ 5 of the warp's 8: the two rows differ in bit
@@ -445,8 +444,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         const uint32_t rfull0 = smem_u32(&hd->raw_full[0]), rempty0 = smem_u32(&hd->raw_empty[0]);
         // ring cursors of the group's next k-block: byte offset of its stage / raw slot, the offset
         // of their barriers, the parity to wait for
-        const uint32_t a_step = static_cast<uint32_t>(GM_NG * GM_A_BYTES), a_ring = static_cast<uint32_t>(p.ns * GM_A_BYTES);
-        const uint32_t r_slots = static_cast<uint32_t>(GM_NG / p.rb);           // raw slots between the group's k-blocks
+        const uint32_t a_step = static_cast<uint32_t>(NG * GM_A_BYTES), a_ring = static_cast<uint32_t>(p.ns * GM_A_BYTES);
+        const uint32_t r_slots = static_cast<uint32_t>(NG / p.rb);           // raw slots between the group's k-blocks
         const uint32_t r_step = r_slots * raw_slot_bytes, r_ring = static_cast<uint32_t>(p.sr) * raw_slot_bytes;
         uint32_t a_off = static_cast<uint32_t>(group * GM_A_BYTES), a_bar = static_cast<uint32_t>(group * 8), a_par = 0;
         uint32_t r_off = static_cast<uint32_t>(group / p.rb) * raw_slot_bytes, r_bar = static_cast<uint32_t>(group / p.rb) * 8u, r_par = 0;
@@ -550,7 +549,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             // this group's k-blocks inside the tile: first, first + NG, ... (nloc of them)
             const int nkb = unit_len(i), ubase = unit_base(i);
             const int first = done - ubase;
-            const int nloc = first < nkb ? (nkb - first + GM_NG - 1) / GM_NG : 0;
+            const int nloc = first < nkb ? (nkb - first + NG - 1) / NG : 0;
             const int kabs = unit_kb0(i) + first;                                  // absolute k-block of the group's first one
             const uint32_t half_off = (p.rb == 2 && (kabs & 1)) ? 64u : 0u;        // NG is even: the parity of kb is fixed
             // The fold factor scale / rowmax of this thread's rows for PF of the group's k-blocks,
@@ -563,7 +562,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 #pragma unroll
                     for (int h2 = 0; h2 < RPT; ++h2) dst[j][h2] = e8 ? 0u : 0x3F800000u;
                     if (ng > 1 && l0 + j < nloc) {
-                        const int u32 = (kabs + (l0 + j) * GM_NG) * 2 + (c >> 1);
+                        const int u32 = (kabs + (l0 + j) * NG) * 2 + (c >> 1);
                         const int gi = min(g_shift >= 0 ? (u32 >> g_shift) : (u32 / g32), ng - 1);
                         if (SC) {
 #pragma unroll
@@ -594,15 +593,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     const uint32_t bar_rfull = rfull0 + r_bar, bar_rempty = rempty0 + r_bar;
                     const uint32_t apar = a_par, rpar = r_par;
                     const bool fresh = done < p.ns;          // the stage's first use: nothing to wait for
-                    done += GM_NG;
-                    a_off += a_step; a_bar += GM_NG * 8;
+                    done += NG;
+                    a_off += a_step; a_bar += NG * 8;
                     if (a_off >= a_ring) { a_off -= a_ring; a_bar -= static_cast<uint32_t>(p.ns * 8); a_par ^= 1u; }
                     r_off += r_step; r_bar += r_slots * 8u;
                     if (r_off >= r_ring) { r_off -= r_ring; r_bar -= static_cast<uint32_t>(p.sr * 8); r_par ^= 1u; }
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_rfull, rpar, STATUS_GEMM_WAIT));
                     if (ok && !fresh) ok = __all_sync(0xffffffffu, mbar_wait(bar_empty, apar ^ 1u, STATUS_GEMM_WAIT));
                     if (!ok) continue;
-                    if (tg == 0) GM_TRACE(1, ubase + first + (l0 + j) * GM_NG);
+                    if (tg == 0) GM_TRACE(1, ubase + first + (l0 + j) * NG);
                     // all loads, then all conversions, then all stores: the rows of a thread are
                     // independent, and kept apart like this their latencies overlap
                     uint32_t h[RPT][8];
@@ -670,10 +669,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         gm_sts128(st + aoff0[h2], h[h2][0], h[h2][1], h[h2][2], h[h2][3]);
                         gm_sts128(st + aoff1[h2], h[h2][4], h[h2][5], h[h2][6], h[h2][7]);
                     }
-                    if (tg == 0) GM_TRACE(7, ubase + first + (l0 + j) * GM_NG);
+                    if (tg == 0) GM_TRACE(7, ubase + first + (l0 + j) * NG);
                     fence_proxy_async_smem();        // generic-proxy stores -> visible to the tensor core
                     __syncwarp();
-                    if (tg == 0) GM_TRACE(2, ubase + first + (l0 + j) * GM_NG);
+                    if (tg == 0) GM_TRACE(2, ubase + first + (l0 + j) * NG);
                     if (lane == 0) {
                         mbar_arrive(bar_full);
                         mbar_arrive(bar_rempty);     // this warp has read its part of the raw slot
@@ -931,23 +930,25 @@ static int device_sms(int dev) {
     return sms;
 }
 
-template <int FMT, int OUT, int SC>
+template <int FMT, int OUT, int SC, int NG = 2>
 static int launch_gemm_as(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, size_t smem, int dev, cudaStream_t st) {
     static unsigned long long configured = 0ull;             // one per instantiation: bit d = device d is set up
     if (dev >= 64 || !((configured >> dev) & 1ull)) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<FMT, OUT, SC>, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM_MAX);
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<FMT, OUT, SC, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM_MAX);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm)");
         if (dev < 64) __atomic_fetch_or(&configured, 1ull << dev, __ATOMIC_RELAXED);
     }
     const int sms = device_sms(dev);
     const int grid = p.ntiles < sms ? p.ntiles : sms;
-    gemm_kernel<FMT, OUT, SC><<<grid, GM_THREADS, smem, st>>>(tw, tx, p);
+    gemm_kernel<FMT, OUT, SC, NG><<<grid, GM_THREADS, smem, st>>>(tw, tx, p);
     TFP8B_LAUNCH_CHECK("tfp8b_gemm");
     return TFP8B_OK;
 }
 
 template <int FMT>
 static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, size_t smem, int dev, cudaStream_t st) {
+    if (p.ng == 4) return p.ks > 1 ? launch_gemm_as<FMT, GM_OUT_SPLITK, 1, 4>(tw, tx, p, smem, dev, st)
+                                   : launch_gemm_as<FMT, GM_OUT_PLAIN, 1, 4>(tw, tx, p, smem, dev, st);
     if (p.ks > 1) return p.sc_row > 0 ? launch_gemm_as<FMT, GM_OUT_SPLITK, 1>(tw, tx, p, smem, dev, st)
                                       : launch_gemm_as<FMT, GM_OUT_SPLITK, 0>(tw, tx, p, smem, dev, st);
     if (p.push) return launch_gemm_as<FMT, GM_OUT_PUSH, 0>(tw, tx, p, smem, dev, st);
@@ -1125,28 +1126,41 @@ static int gemm_impl(const void* x16, const float* xs, const uint8_t* codes, con
     const int budget = GM_SMEM_MAX - 1024 - GM_HEADER;
     // TFP8B_GEMM_NS=<4|6|8> overrides the number of decoded-tile slots (tuning).
     static const int ns_env = [] { const char* v = getenv("TFP8B_GEMM_NS"); return v ? atoi(v) : 0; }();
-    p.ns = (ns_env == 4 || ns_env == 6 || ns_env == 8) ? ns_env : GM_NA;
-    static_assert(GM_NA % GM_NG == 0 && GM_NA % 2 == 0, "decoded-tile ring: a multiple of the decode groups and of the issuing threads");
-    p.nx = bn >= 256 ? 4 : (bn == 128 ? 6 : GM_MAX_XSLOTS);          // even: two issuing threads walk it with stride 2
-    if (p.ns > 4 && bn >= 64) p.nx = 4;
     const int raw_slot = p.rb * GM_RAW_BYTES;
-    const int raw_stride = GM_NG / p.rb;                      // slots between a group's consecutive k-blocks
     // K-group scales of a tile in shared memory (two tiles' worth), where a row's scales are whole
     // 16-byte pieces of at most 128 bytes: see the decode warps. TFP8B_GEMM_SCALE_CACHE=0 turns it off.
+    int sc_row_wanted = 0;
     {
         static const int use_cache = [] { const char* v = getenv("TFP8B_GEMM_SCALE_CACHE"); return !(v && v[0] == '0'); }();
         const int row_bytes = (K / G) * (scale_kind == TFP8B_SCALE_UE8M0 ? 1 : 4);
         const bool plain_form = n_dst == 1 && ldy == N && col0 == 0;           // the other output forms keep the global path
-        p.sc_row = (use_cache && plain_form && G != K && row_bytes % 16 == 0 && row_bytes <= 128 &&
-                    (reinterpret_cast<uintptr_t>(scale) & 15u) == 0) ? row_bytes : 0;
+        sc_row_wanted = (use_cache && plain_form && G != K && row_bytes % 16 == 0 && row_bytes <= 128 &&
+                         (reinterpret_cast<uintptr_t>(scale) & 15u) == 0) ? row_bytes : 0;
     }
-    const int min_raw = raw_stride > 2 ? raw_stride : 2;
-    if ((budget - p.ns * GM_A_BYTES - p.nx * p.x_bytes - 2 * GM_BM * p.sc_row) / raw_slot < min_raw) p.sc_row = 0;   // no room at this tile width
+    // Ring sizes for `ng` decode groups; false if the raw ring would be shorter than its users need.
+    auto size_rings = [&](int ng) {
+        p.ng = ng;
+        p.ns = (ns_env == 4 || ns_env == 6 || ns_env == 8) && ns_env % ng == 0 ? ns_env : 2 * ng;     // a multiple of the groups and of the issuing threads
+        p.nx = bn >= 256 ? 4 : (bn == 128 ? 6 : GM_MAX_XSLOTS);      // even: two issuing threads walk it with stride 2
+        if (p.ns > 4 && bn >= 32) p.nx = 4;
+        const int raw_stride = ng / p.rb;                             // slots between a group's consecutive k-blocks
+        const int min_raw = raw_stride > 2 ? raw_stride : 2;
+        p.sc_row = sc_row_wanted;
+        if ((budget - p.ns * GM_A_BYTES - p.nx * p.x_bytes - 2 * GM_BM * p.sc_row) / raw_slot < min_raw) p.sc_row = 0;   // no room at this tile width
+        p.sr = (budget - p.ns * GM_A_BYTES - p.nx * p.x_bytes - 2 * GM_BM * p.sc_row) / raw_slot;
+        if (p.sr > GM_MAX_SLOTS) p.sr = GM_MAX_SLOTS;
+        p.sr -= p.sr % raw_stride;
+        return p.sr >= raw_stride && p.sr >= 2;
+    };
+    // Four groups where they pay (measured, 28672 x 8192 with 128-wide groups: 98 -> 92 us at 16 rows,
+    // 101 -> 95 at 32; 14336 x 4096 at 24 rows: 35 -> 31; units of 32 k-blocks: 7 % slower): narrow
+    // tiles, scales cached, plain or split-K output, units of at least 64 k-blocks, and at least
+    // four raw slots left. TFP8B_GEMM_GROUPS=2 turns it off.
+    static const int groups_env = [] { const char* v = getenv("TFP8B_GEMM_GROUPS"); return v ? atoi(v) : 0; }();
+    bool four = groups_env != 2 && bn <= 32 && p.nkbu >= 64 && sc_row_wanted > 0 && p.push == 0 && n_dst == 1 && size_rings(4) &&
+                p.sc_row > 0 && p.sr >= 4;
+    if (!four) TFP8B_REQUIRE(size_rings(2), TFP8B_ERR_INVALID, "tfp8b_gemm: ring sizes ns=%d nx=%d sr=%d do not fit", p.ns, p.nx, p.sr);
     const int sc_bytes = 2 * GM_BM * p.sc_row;
-    p.sr = (budget - p.ns * GM_A_BYTES - p.nx * p.x_bytes - sc_bytes) / raw_slot;
-    if (p.sr > GM_MAX_SLOTS) p.sr = GM_MAX_SLOTS;
-    p.sr -= p.sr % raw_stride;
-    TFP8B_REQUIRE(p.sr >= GM_NG / p.rb && p.sr >= 2, TFP8B_ERR_INVALID, "tfp8b_gemm: ring sizes ns=%d nx=%d sr=%d do not fit", p.ns, p.nx, p.sr);
     const size_t smem = 1024 + GM_HEADER + static_cast<size_t>(p.ns) * GM_A_BYTES + static_cast<size_t>(p.nx) * p.x_bytes +
                         static_cast<size_t>(p.sr) * raw_slot + sc_bytes;
 
