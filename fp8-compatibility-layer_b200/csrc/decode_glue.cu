@@ -624,10 +624,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_kernel(const T* q, c
 //     pair before the conversion. P = exp2(score - max) is rounded to fp16 as a high and a low
 //     part (two MMAs), the V scale relative to the chunk's largest rides on the decoded V (a power
 //     of two: exact), the largest itself on the FP32 result.
-// A CTA serves one (sequence, KV head, up to four query heads, 128 positions); a warp 32 of them.
-constexpr int ATT8_CHUNK = 128;
-constexpr int ATT8_PW = ATT8_CHUNK / (ATT_THREADS / 32);       // positions per warp: 32
-static_assert(ATT_THREADS == 128 && ATT8_PW % 16 == 0, "four warps, whole 16-position blocks");
+// A CTA serves one (sequence, KV head, up to four query heads, 128 or 256 positions); a warp 32 of them.
+constexpr int ATT8_PW = 32;                                    // positions per warp: two 16-position blocks
 
 __device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -640,11 +638,12 @@ __device__ __forceinline__ uint32_t to_f16x2(__nv_bfloat162 v) {      // every b
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <typename T, int FMT>
-__global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* q, const uint8_t* kc, const float* ksc, const uint8_t* vc,
+template <typename T, int FMT, int NW>
+__global__ void __launch_bounds__(32 * NW) attn_partial_fp8_kernel(const T* q, const uint8_t* kc, const float* ksc, const uint8_t* vc,
                                                                        const float* vsc, const long long* pos, float* part, int H, int KV,
                                                                        int S, int nsplit, float scale_log2e, int early) {
     using P = typename pair_of<T>::type;
+    constexpr int ATT8_CHUNK = ATT8_PW * NW;                       // positions per CTA: 128 (four warps) or 256 (eight)
     if (early) pdl_launch_dependents();
     pdl_wait();
     const int G = H / KV, ngrp = (G + ATT_G - 1) / ATT_G;
@@ -660,7 +659,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* 
     __shared__ __align__(16) __half s_ph[ATT_G][ATT8_CHUNK];        // softmax weights, high part (read as pairs)
     __shared__ __align__(16) __half s_pl[ATT_G][ATT8_CHUNK];        // ... and low part
     __shared__ float s_m[ATT_G], s_l[ATT_G], s_vmax;
-    __shared__ __align__(16) float s_acc[ATT_THREADS / 32][ATT_G][ATT_HD];   // written as pairs of floats
+    __shared__ __align__(16) float s_acc[NW][ATT_G][ATT_HD];   // written as pairs of floats
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const size_t row0 = (static_cast<size_t>(b) * KV + kvh) * S + s0;
@@ -720,6 +719,25 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* 
             }
         }
     }
+    // ---- the V codes and scales of this warp's positions, requested now, used after the softmax:
+    // lane (g, t) takes dims [16 g, 16 g + 16) of positions 2t, 2t + 1, 2t + 8, 2t + 9 of each block
+    uint4 vv[ATT8_PW / 16][4];
+    float vsr[ATT8_PW / 16][4];
+#pragma unroll
+    for (int blk = 0; blk < ATT8_PW / 16; ++blk) {
+        const int pb = warp * ATT8_PW + blk * 16;
+        const int pj[4] = {pb + 2 * t, pb + 2 * t + 1, pb + 2 * t + 8, pb + 2 * t + 9};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (pj[u] < n) {
+                vv[blk][u] = __ldcg(reinterpret_cast<const uint4*>(vbase + static_cast<size_t>(pj[u]) * ATT_HD + g * 16));
+                vsr[blk][u] = __ldcg(vsc + row0 + pj[u]);
+            } else {
+                vv[blk][u] = make_uint4(0u, 0u, 0u, 0u);
+                vsr[blk][u] = 0.f;
+            }
+        }
+    }
     __syncthreads();
     // ---- per head: maximum, exponentials (fp16 high + low part), sum; one warp also finds the
     // chunk's largest V scale
@@ -741,7 +759,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* 
         for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
         if (lane == 0) { s_m[hh] = m; s_l[hh] = l; }
     }
-    if (warp == ATT_THREADS / 32 - 1) {
+    if (warp == NW - 1) {
         float vm = 0.f;
         for (int j = lane; j < n; j += 32) vm = fmaxf(vm, __ldcg(vsc + row0 + j));
 #pragma unroll
@@ -757,28 +775,17 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* 
 #pragma unroll
     for (int blk = 0; blk < ATT8_PW / 16; ++blk) {
         const int pb = warp * ATT8_PW + blk * 16;
-        const int pj[4] = {pb + 2 * t, pb + 2 * t + 1, pb + 2 * t + 8, pb + 2 * t + 9};
-        uint4 vv[4];
-        float vs[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            if (pj[u] < n) {
-                vv[u] = __ldcg(reinterpret_cast<const uint4*>(vbase + static_cast<size_t>(pj[u]) * ATT_HD + g * 16));
-                vs[u] = __ldcg(vsc + row0 + pj[u]) * inv_vmax;     // <= 1; below 2^-24 it rounds to 0: such a row is noise beside the largest
-            } else {
-                vv[u] = make_uint4(0u, 0u, 0u, 0u);
-                vs[u] = 0.f;
-            }
-        }
-        const __half2 sAB = __floats2half2_rn(vs[0], vs[1]), sCD = __floats2half2_rn(vs[2], vs[3]);
+        // scales relative to the largest: <= 1; below 2^-24 they round to 0 -- such a row is noise beside the largest
+        const __half2 sAB = __floats2half2_rn(vsr[blk][0] * inv_vmax, vsr[blk][1] * inv_vmax);
+        const __half2 sCD = __floats2half2_rn(vsr[blk][2] * inv_vmax, vsr[blk][3] * inv_vmax);
         // B operand: P of head g at positions (2t, 2t+1) and (2t+8, 2t+9) of the block
         uint32_t bh0 = 0u, bh1 = 0u, bl0 = 0u, bl1 = 0u;
         if (g < nh) {
             bh0 = *reinterpret_cast<const uint32_t*>(&s_ph[g][pb + 2 * t]); bh1 = *reinterpret_cast<const uint32_t*>(&s_ph[g][pb + 2 * t + 8]);
             bl0 = *reinterpret_cast<const uint32_t*>(&s_pl[g][pb + 2 * t]); bl1 = *reinterpret_cast<const uint32_t*>(&s_pl[g][pb + 2 * t + 8]);
         }
-        const uint32_t wA[4] = {vv[0].x, vv[0].y, vv[0].z, vv[0].w}, wB[4] = {vv[1].x, vv[1].y, vv[1].z, vv[1].w};
-        const uint32_t wC[4] = {vv[2].x, vv[2].y, vv[2].z, vv[2].w}, wD[4] = {vv[3].x, vv[3].y, vv[3].z, vv[3].w};
+        const uint32_t wA[4] = {vv[blk][0].x, vv[blk][0].y, vv[blk][0].z, vv[blk][0].w}, wB[4] = {vv[blk][1].x, vv[blk][1].y, vv[blk][1].z, vv[blk][1].w};
+        const uint32_t wC[4] = {vv[blk][2].x, vv[blk][2].y, vv[blk][2].z, vv[blk][2].w}, wD[4] = {vv[blk][3].x, vv[blk][3].y, vv[blk][3].z, vv[blk][3].w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             // fragment rows g and g + 8 = dims 16 g + 2 i and 16 g + 2 i + 1: bytes (2i) & 3 and + 1 of word i / 2
@@ -812,7 +819,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_fp8_kernel(const T* 
         if (threadIdx.x < ATT_HD) {
             float sum = 0.f;
 #pragma unroll
-            for (int w = 0; w < ATT_THREADS / 32; ++w) sum += s_acc[w][hh][threadIdx.x];
+            for (int w = 0; w < NW; ++w) sum += s_acc[w][hh][threadIdx.x];
             rec[2 + threadIdx.x] = sum;
         }
         if (threadIdx.x == 0) { rec[0] = n > 0 ? s_m[hh] : -INFINITY; rec[1] = n > 0 ? s_l[hh] : 0.f; }
@@ -1038,20 +1045,26 @@ extern "C" int tfp8b_attn_decode(const void* q, const void* k_cache, const void*
                       static_cast<__nv_bfloat16*>(out), nsplit, att_early());
 }
 
-template <typename T>
-static int attn_fp8_launch(int fmt, int grid, cudaStream_t st, const void* q, const uint8_t* k_codes, const float* k_scale,
-                           const uint8_t* v_codes, const float* v_scale, const long long* pos, float* scratch, void* out, int B, int H,
-                           int KV, int max_seq, int nsplit, float scale_log2e) {
-    int rc;
-    if (fmt == TFP8B_E4M3FN)
-        rc = launch_pdl("tfp8b_attn_decode_fp8", attn_partial_fp8_kernel<T, TFP8B_E4M3FN>, grid, ATT_THREADS, st, static_cast<const T*>(q),
-                        k_codes, k_scale, v_codes, v_scale, pos, scratch, H, KV, max_seq, nsplit, scale_log2e, att_early());
-    else
-        rc = launch_pdl("tfp8b_attn_decode_fp8", attn_partial_fp8_kernel<T, TFP8B_E5M2>, grid, ATT_THREADS, st, static_cast<const T*>(q),
-                        k_codes, k_scale, v_codes, v_scale, pos, scratch, H, KV, max_seq, nsplit, scale_log2e, att_early());
+template <typename T, int FMT, int NW>
+static int attn_fp8_launch_as(int grid, cudaStream_t st, const void* q, const uint8_t* k_codes, const float* k_scale,
+                              const uint8_t* v_codes, const float* v_scale, const long long* pos, float* scratch, void* out, int B,
+                              int H, int KV, int max_seq, int nsplit, float scale_log2e) {
+    const int rc = launch_pdl("tfp8b_attn_decode_fp8", attn_partial_fp8_kernel<T, FMT, NW>, grid, 32 * NW, st, static_cast<const T*>(q),
+                              k_codes, k_scale, v_codes, v_scale, pos, scratch, H, KV, max_seq, nsplit, scale_log2e, att_early());
     if (rc != TFP8B_OK) return rc;
     return launch_pdl("tfp8b_attn_decode_fp8", attn_merge_kernel<T>, B * H, ATT_HD, st, static_cast<const float*>(scratch),
                       static_cast<T*>(out), nsplit, att_early());
+}
+
+template <typename T>
+static int attn_fp8_launch(int fmt, int nw, int grid, cudaStream_t st, const void* q, const uint8_t* k_codes, const float* k_scale,
+                           const uint8_t* v_codes, const float* v_scale, const long long* pos, float* scratch, void* out, int B, int H,
+                           int KV, int max_seq, int nsplit, float scale_log2e) {
+#define ATT8_CASE(F, W) if (fmt == F && nw == W) return attn_fp8_launch_as<T, F, W>(grid, st, q, k_codes, k_scale, v_codes, v_scale, pos, \
+                                                                                    scratch, out, B, H, KV, max_seq, nsplit, scale_log2e)
+    ATT8_CASE(TFP8B_E4M3FN, 4); ATT8_CASE(TFP8B_E4M3FN, 8); ATT8_CASE(TFP8B_E5M2, 4); ATT8_CASE(TFP8B_E5M2, 8);
+#undef ATT8_CASE
+    return TFP8B_ERR_INVALID;
 }
 
 extern "C" int tfp8b_attn_decode_fp8(const void* q, const uint8_t* k_codes, const float* k_scale, const uint8_t* v_codes,
@@ -1068,18 +1081,29 @@ extern "C" int tfp8b_attn_decode_fp8(const void* q, const uint8_t* k_codes, cons
     TFP8B_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_codes)) & 15u) == 0 &&
                   (reinterpret_cast<uintptr_t>(v_codes) & 15u) == 0, TFP8B_ERR_INVALID,
                   "tfp8b_attn_decode_fp8: q, k_codes and v_codes must be 16-byte aligned");
-    const int nsplit = (max_seq + ATT8_CHUNK - 1) / ATT8_CHUNK;
-    TFP8B_REQUIRE(nsplit <= 128, TFP8B_ERR_UNSUPPORTED, "tfp8b_attn_decode_fp8: max_seq %d (at most %d is built)", max_seq, 128 * ATT8_CHUNK);
     const int ngrp = (H / KV + ATT_G - 1) / ATT_G;
+    // 128 positions per CTA (four warps) while that leaves the machine short of CTAs, 256 (eight warps)
+    // beyond: half the partial records and half the merge work (prompt 2100: 10.0 -> 9.5 us per call
+    // at batch 4, 17.2 -> 16.4 at batch 8). TFP8B_ATT8_WARPS=4|8 forces one.
+    static const int nw_env = [] { const char* v = getenv("TFP8B_ATT8_WARPS"); return v ? atoi(v) : 0; }();
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+    int sms = 148;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    const long long ctas128 = static_cast<long long>(B) * KV * ngrp * ((max_seq + 127) / 128);
+    const int nw = (nw_env == 4 || nw_env == 8) ? nw_env : (ctas128 >= 2ll * sms ? 8 : 4);
+    const int chunk = ATT8_PW * nw;
+    const int nsplit = (max_seq + chunk - 1) / chunk;
+    TFP8B_REQUIRE(nsplit <= 128, TFP8B_ERR_UNSUPPORTED, "tfp8b_attn_decode_fp8: max_seq %d (at most %d is built)", max_seq, 128 * chunk);
     const long long need = static_cast<long long>(B) * H * nsplit * (ATT_HD + 2);
     TFP8B_REQUIRE(scratch_floats >= need, TFP8B_ERR_INVALID, "tfp8b_attn_decode_fp8: scratch of %lld floats, %lld needed", scratch_floats, need);
     const float scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(hd));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int grid = B * KV * ngrp * nsplit;
     if (dtype == TFP8B_F16)
-        return attn_fp8_launch<__half>(fmt, grid, st, q, k_codes, k_scale, v_codes, v_scale, pos, scratch, out, B, H, KV, max_seq, nsplit,
+        return attn_fp8_launch<__half>(fmt, nw, grid, st, q, k_codes, k_scale, v_codes, v_scale, pos, scratch, out, B, H, KV, max_seq, nsplit,
                                        scale_log2e);
-    return attn_fp8_launch<__nv_bfloat16>(fmt, grid, st, q, k_codes, k_scale, v_codes, v_scale, pos, scratch, out, B, H, KV, max_seq,
+    return attn_fp8_launch<__nv_bfloat16>(fmt, nw, grid, st, q, k_codes, k_scale, v_codes, v_scale, pos, scratch, out, B, H, KV, max_seq,
                                           nsplit, scale_log2e);
 }
 
