@@ -827,6 +827,165 @@ __global__ void __launch_bounds__(32 * NW) attn_partial_fp8_kernel(const T* q, c
     if (!early) pdl_launch_dependents();
 }
 
+// The same formulation over a 16-bit (fp16) cache: the K rows are MMA fragments as they are loaded,
+// the V pairs of neighbouring positions are made by a permute of 16-bit halves; no scales. A lane
+// holds 32 dims of a row as four 16-byte loads (scores) and 16 dims of four positions (output).
+template <int NW>
+__global__ void __launch_bounds__(32 * NW) attn_partial_f16tc_kernel(const __half* q, const __half* kc, const __half* vc,
+                                                                     const long long* pos, float* part, int H, int KV, int S, int nsplit,
+                                                                     float scale_log2e, int early) {
+    constexpr int CHUNK = ATT8_PW * NW;
+    if (early) pdl_launch_dependents();
+    pdl_wait();
+    const int G = H / KV, ngrp = (G + ATT_G - 1) / ATT_G;
+    int id = blockIdx.x;
+    const int split = id % nsplit; id /= nsplit;
+    const int grp = id % ngrp; id /= ngrp;
+    const int kvh = id % KV, b = id / KV;
+    const int h0 = kvh * G + grp * ATT_G, nh = min(ATT_G, G - grp * ATT_G);
+    const int len = static_cast<int>(min(static_cast<long long>(S), pos[0] + 1));
+    const int chunk = min(CHUNK, (len + nsplit - 1) / nsplit);
+    const int s0 = split * chunk, n = max(0, min(len, s0 + chunk) - s0);
+    __shared__ __align__(16) float s_sc[ATT_G][CHUNK];
+    __shared__ __align__(16) __half s_ph[ATT_G][CHUNK];
+    __shared__ __align__(16) __half s_pl[ATT_G][CHUNK];
+    __shared__ float s_m[ATT_G], s_l[ATT_G];
+    __shared__ __align__(16) float s_acc[NW][ATT_G][ATT_HD];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const size_t row0 = (static_cast<size_t>(b) * KV + kvh) * S + s0;
+    const __half* kbase = kc + row0 * ATT_HD;
+    const __half* vbase = vc + row0 * ATT_HD;
+    // ---- scores: lane (g, t) holds dims [32 t, 32 t + 32) of rows g and g + 8; k-step c contracts dims 32 t + 4 c .. + 3
+    {
+        uint32_t qreg[16];
+        if (g < nh) {
+            const uint4* qp = reinterpret_cast<const uint4*>(q + (static_cast<size_t>(b) * H + h0 + g) * ATT_HD + t * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 v = qp[i];
+                qreg[4 * i] = v.x; qreg[4 * i + 1] = v.y; qreg[4 * i + 2] = v.z; qreg[4 * i + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) qreg[i] = 0u;
+        }
+#pragma unroll
+        for (int blk = 0; blk < ATT8_PW / 16; ++blk) {
+            const int j0 = warp * ATT8_PW + blk * 16 + g, j1 = j0 + 8;
+            uint4 k0[4], k1[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                k0[i] = j0 < n ? __ldcg(reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(j0) * ATT_HD + t * 32) + i) : make_uint4(0u, 0u, 0u, 0u);
+                k1[i] = j1 < n ? __ldcg(reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(j1) * ATT_HD + t * 32) + i) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {                       // two k-steps per 16-byte piece
+                mma16816(c, k0[i].x, k1[i].x, k0[i].y, k1[i].y, qreg[4 * i], qreg[4 * i + 1]);
+                mma16816(c, k0[i].z, k1[i].z, k0[i].w, k1[i].w, qreg[4 * i + 2], qreg[4 * i + 3]);
+            }
+            if (t < 2) {
+                const int hA = 2 * t, hB = 2 * t + 1;
+                if (j0 < n) { if (hA < nh) s_sc[hA][j0] = c[0] * scale_log2e; if (hB < nh) s_sc[hB][j0] = c[1] * scale_log2e; }
+                if (j1 < n) { if (hA < nh) s_sc[hA][j1] = c[2] * scale_log2e; if (hB < nh) s_sc[hB][j1] = c[3] * scale_log2e; }
+            }
+        }
+    }
+    // ---- the V rows of the warp's first block, requested now, used after the softmax (the second
+    // block's are requested at the start of the output phase: registers)
+    uint4 vv0[4][2];
+    {
+        const int pb = warp * ATT8_PW;
+        const int pj[4] = {pb + 2 * t, pb + 2 * t + 1, pb + 2 * t + 8, pb + 2 * t + 9};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint4* vp = reinterpret_cast<const uint4*>(vbase + static_cast<size_t>(pj[u]) * ATT_HD + g * 16);
+            vv0[u][0] = pj[u] < n ? __ldcg(vp) : make_uint4(0u, 0u, 0u, 0u);
+            vv0[u][1] = pj[u] < n ? __ldcg(vp + 1) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+    __syncthreads();
+    // ---- per head: maximum, exponentials (fp16 high + low part), sum
+    if (warp < nh) {
+        const int hh = warp;
+        float m = -INFINITY;
+        for (int j = lane; j < n; j += 32) m = fmaxf(m, s_sc[hh][j]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float l = 0.f;
+        for (int j = lane; j < CHUNK; j += 32) {
+            float e = 0.f;
+            if (j < n) { e = exp2f(s_sc[hh][j] - m); l += e; }
+            const __half hi = __float2half_rn(e);
+            s_ph[hh][j] = hi;
+            s_pl[hh][j] = __float2half_rn(e - __half2float(hi));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        if (lane == 0) { s_m[hh] = m; s_l[hh] = l; }
+    }
+    __syncthreads();
+    // ---- out^T = V^T P^T: lane (g, t) takes dims [16 g, 16 g + 16) of positions 2t, 2t + 1, 2t + 8, 2t + 9 of each block
+    float o[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+#pragma unroll
+    for (int blk = 0; blk < ATT8_PW / 16; ++blk) {
+        const int pb = warp * ATT8_PW + blk * 16;
+        const int pj[4] = {pb + 2 * t, pb + 2 * t + 1, pb + 2 * t + 8, pb + 2 * t + 9};
+        uint4 vv[4][2];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (blk == 0) {
+                vv[u][0] = vv0[u][0]; vv[u][1] = vv0[u][1];
+            } else {
+                const uint4* vp = reinterpret_cast<const uint4*>(vbase + static_cast<size_t>(pj[u]) * ATT_HD + g * 16);
+                vv[u][0] = pj[u] < n ? __ldcg(vp) : make_uint4(0u, 0u, 0u, 0u);
+                vv[u][1] = pj[u] < n ? __ldcg(vp + 1) : make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        uint32_t bh0 = 0u, bh1 = 0u, bl0 = 0u, bl1 = 0u;
+        if (g < nh) {
+            bh0 = *reinterpret_cast<const uint32_t*>(&s_ph[g][pb + 2 * t]); bh1 = *reinterpret_cast<const uint32_t*>(&s_ph[g][pb + 2 * t + 8]);
+            bl0 = *reinterpret_cast<const uint32_t*>(&s_pl[g][pb + 2 * t]); bl1 = *reinterpret_cast<const uint32_t*>(&s_pl[g][pb + 2 * t + 8]);
+        }
+        const uint32_t wA[8] = {vv[0][0].x, vv[0][0].y, vv[0][0].z, vv[0][0].w, vv[0][1].x, vv[0][1].y, vv[0][1].z, vv[0][1].w};
+        const uint32_t wB[8] = {vv[1][0].x, vv[1][0].y, vv[1][0].z, vv[1][0].w, vv[1][1].x, vv[1][1].y, vv[1][1].z, vv[1][1].w};
+        const uint32_t wC[8] = {vv[2][0].x, vv[2][0].y, vv[2][0].z, vv[2][0].w, vv[2][1].x, vv[2][1].y, vv[2][1].z, vv[2][1].w};
+        const uint32_t wD[8] = {vv[3][0].x, vv[3][0].y, vv[3][0].z, vv[3][0].w, vv[3][1].x, vv[3][1].y, vv[3][1].z, vv[3][1].w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            // fragment rows g and g + 8 = dims 16 g + 2 i and + 1: the low and the high half of word i; the two
+            // positions of a pair come from two rows of the cache
+            const uint32_t a0 = __byte_perm(wA[i], wB[i], 0x5410), a1 = __byte_perm(wA[i], wB[i], 0x7632);
+            const uint32_t a2 = __byte_perm(wC[i], wD[i], 0x5410), a3 = __byte_perm(wC[i], wD[i], 0x7632);
+            mma16816(o[i], a0, a1, a2, a3, bh0, bh1);
+            mma16816(o[i], a0, a1, a2, a3, bl0, bl1);
+        }
+    }
+    if (t < 2) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int d = 16 * g + 2 * i;
+            *reinterpret_cast<float2*>(&s_acc[warp][2 * t][d]) = make_float2(o[i][0], o[i][2]);
+            *reinterpret_cast<float2*>(&s_acc[warp][2 * t + 1][d]) = make_float2(o[i][1], o[i][3]);
+        }
+    }
+    __syncthreads();
+    for (int hh = 0; hh < nh; ++hh) {
+        float* rec = part + ((static_cast<size_t>(b) * H + h0 + hh) * nsplit + split) * (ATT_HD + 2);
+        if (threadIdx.x < ATT_HD) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) sum += s_acc[w][hh][threadIdx.x];
+            rec[2 + threadIdx.x] = sum;
+        }
+        if (threadIdx.x == 0) { rec[0] = n > 0 ? s_m[hh] : -INFINITY; rec[1] = n > 0 ? s_l[hh] : 0.f; }
+    }
+    if (!early) pdl_launch_dependents();
+}
+
 template <typename T>
 __global__ void __launch_bounds__(ATT_HD) attn_merge_kernel(const float* part, T* out, int nsplit, int early) {
     if (early) pdl_launch_dependents();
@@ -1020,6 +1179,31 @@ extern "C" int tfp8b_attn_decode(const void* q, const void* k_cache, const void*
     TFP8B_REQUIRE(q && k_cache && v_cache && pos && out && scratch, TFP8B_ERR_INVALID, "tfp8b_attn_decode: null pointer");
     TFP8B_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache)) & 15u) == 0, TFP8B_ERR_INVALID,
                   "tfp8b_attn_decode: q and k_cache must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // fp16: both products on the tensor cores, 128 or 256 positions per CTA (TFP8B_ATT16_TC=0: the scalar kernel)
+    static const int use_tc = [] { const char* v = getenv("TFP8B_ATT16_TC"); return !(v && v[0] == '0'); }();
+    if (use_tc && dtype == TFP8B_F16 && (reinterpret_cast<uintptr_t>(v_cache) & 15u) == 0) {
+        const int ngrp_tc = (H / KV + ATT_G - 1) / ATT_G;
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        const int nw = static_cast<long long>(B) * KV * ngrp_tc * ((max_seq + 127) / 128) >= 2ll * sms ? 8 : 4;
+        const int chunk = ATT8_PW * nw, ns = (max_seq + chunk - 1) / chunk;
+        TFP8B_REQUIRE(ns <= 128, TFP8B_ERR_UNSUPPORTED, "tfp8b_attn_decode: max_seq %d (at most %d is built)", max_seq, 128 * chunk);
+        TFP8B_REQUIRE(scratch_floats >= static_cast<long long>(B) * H * ns * (ATT_HD + 2), TFP8B_ERR_INVALID,
+                      "tfp8b_attn_decode: scratch of %lld floats, %lld needed", scratch_floats, static_cast<long long>(B) * H * ns * (ATT_HD + 2));
+        const float sl2e = 1.4426950408889634f / sqrtf(static_cast<float>(hd));
+        const int grid = B * KV * ngrp_tc * ns;
+        const int rc = nw == 8 ? launch_pdl("tfp8b_attn_decode", attn_partial_f16tc_kernel<8>, grid, 256, st, static_cast<const __half*>(q),
+                                            static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), pos, scratch, H, KV,
+                                            max_seq, ns, sl2e, att_early())
+                                : launch_pdl("tfp8b_attn_decode", attn_partial_f16tc_kernel<4>, grid, 128, st, static_cast<const __half*>(q),
+                                            static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), pos, scratch, H, KV,
+                                            max_seq, ns, sl2e, att_early());
+        if (rc != TFP8B_OK) return rc;
+        return launch_pdl("tfp8b_attn_decode", attn_merge_kernel<__half>, B * H, ATT_HD, st, static_cast<const float*>(scratch),
+                          static_cast<__half*>(out), ns, att_early());
+    }
     // chunks of at most ATT_CHUNK positions cover the whole cache
     const int nsplit = (max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
     TFP8B_REQUIRE(nsplit <= 128, TFP8B_ERR_UNSUPPORTED, "tfp8b_attn_decode: max_seq %d (at most %d is built)", max_seq, 128 * ATT_CHUNK);
@@ -1027,7 +1211,6 @@ extern "C" int tfp8b_attn_decode(const void* q, const void* k_cache, const void*
     const long long need = static_cast<long long>(B) * H * nsplit * (ATT_HD + 2);
     TFP8B_REQUIRE(scratch_floats >= need, TFP8B_ERR_INVALID, "tfp8b_attn_decode: scratch of %lld floats, %lld needed", scratch_floats, need);
     const float scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(hd));
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     int rc;
     if (dtype == TFP8B_F16) {
         rc = launch_pdl("tfp8b_attn_decode", attn_partial_kernel<__half>, B * KV * ngrp * nsplit, ATT_THREADS, st, static_cast<const __half*>(q),

@@ -245,8 +245,9 @@ class Llama(nn.Module):
     def __init__(self, cfg: LlamaConfig = LLAMA3_8B, device="cpu", dtype=torch.float16, tp=1):
         super().__init__()
         self.cfg, self.tp = cfg, tp
-        # decode attention: torch SDPA (cuDNN) by default; True selects the library's split-KV kernel
-        # (inside a full 32-block step it is 2 % slower for one sequence, 10 % for eight)
+        # decode attention over a 16-bit cache: torch SDPA (cuDNN) by default; True selects the library's
+        # split-KV kernel (alone it is faster up to four sequences, inside a full step it ties at one
+        # and loses 4 - 6 % at four and eight)
         self.attn_kernel = False
         # None: the KV cache holds activations as they are. "e4m3fn" / "e5m2": FP8 codes + one scale per
         # token and KV head (FP8Config(kv_cache="fp8")); the decode step then always uses the library's
