@@ -327,8 +327,10 @@ TFP8B_API long long tfp8b_allreduce_wait_limit(long long cycles);
  * [B, H, hd]; the caches [B, KV, max_seq, hd]; pos is ONE int64 on the device (the cache position of
  * the current token, already written by tfp8b_rope_kv_store). scratch: at least
  * B * H * ceil(max_seq / 64) * (hd + 2) floats of device memory for the split-KV partial results
- * (one record per head and 64-position chunk of the cache). f16 or bf16, hd = 128. (Reference: the torch attention of
- * tfp8/examples/demo_llm.py:64-76.) */
+ * (one record per head and 64-position chunk of the cache). f16 or bf16, hd = 128. fp16 runs both
+ * products on the tensor cores (fp16 operands, FP32 accumulation, the softmax weights as an fp16
+ * high + low part; 128 or 256 positions per chunk); bf16 is scalar FP32. (Reference: the torch
+ * attention of tfp8/examples/demo_llm.py:64-76.) */
 TFP8B_API int tfp8b_attn_decode(const void* q, const void* k_cache, const void* v_cache, const long long* pos,
                   void* out, float* scratch, long long scratch_floats, int dtype, int B, int H, int KV, int hd,
                   int max_seq, tfp8b_stream_t stream);
