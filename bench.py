@@ -834,12 +834,40 @@ def run_probe(args):
     (a small, self-ending case for profiler captures). Prints one JSON line with the timing."""
     from tfp8 import _ext, synth
     kind, dims = args.probe.split(":")
-    M, N, K, G = (int(v) for v in (dims.split(",") + ["32"])[:4])
+    M, N, K, G = (int(v) for v in (dims.split(",") + ["32", "32", "32"])[:4])
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     lib = _ext.load()
     if kind == "w8a8":
         print(json.dumps({"probe": args.probe, **w8a8_row(device, M, N, K, args.steps, args.warmup)}))
+        return
+    if kind in ("attn", "attn8"):
+        # attn:B,S / attn8:B,S -- the decode attention of a Llama-3-8B block (32 query / 8 KV heads of 128)
+        # over a 16-bit / an FP8 KV cache of S positions, the query at position S - 200; eight distinct
+        # caches in turn so that L2 does not hold them
+        B, S = M, N
+        H, KV, hd = 32, 8, 128
+        pos = torch.tensor([S - 200], device=device)
+        q = torch.randn(B, H, hd, device=device).half()
+        scratch = torch.empty(_ext.attn_scratch_floats(B, H, S, hd), dtype=torch.float32, device=device)
+        if kind == "attn8":
+            ks = [torch.randint(0, 120, (B, KV, S, hd), device=device, dtype=torch.uint8) for _ in range(8)]
+            vs = [torch.randint(0, 120, (B, KV, S, hd), device=device, dtype=torch.uint8) for _ in range(8)]
+            sc = torch.full((B, KV, S), 2.0 ** -6, device=device)
+            call = lambda i: _ext.attn_decode_fp8(q, ks[i], sc, vs[i], sc, pos, scratch)
+            per_pos = 2 * (hd + 4)
+        else:
+            ks = [torch.randn(B, KV, S, hd, device=device).half() for _ in range(8)]
+            vs = [torch.randn(B, KV, S, hd, device=device).half() for _ in range(8)]
+            call = lambda i: _ext.attn_decode(q, ks[i], vs[i], pos, scratch)
+            per_pos = 4 * hd
+
+        def step():
+            for i in range(8):
+                call(i)
+        sec = time_steps_in_graphs(step, args.steps, args.warmup) / 8
+        byt = B * KV * (S - 199) * per_pos
+        print(json.dumps({"probe": args.probe, "us_per_call": sec * 1e6, "kv_bytes": byt, "gbs": byt / sec / 1e9}))
         return
     if kind == "decode":
         # decode:B,layers,prompt -- a Llama-3-8B-shaped decoder cut to `layers` blocks: prefill, capture,
@@ -983,7 +1011,7 @@ def main():
     ap.add_argument("--quick", action="store_true", help="headline only: skip the per-shape / GEMM / codec tables")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-llama", action="store_true", help="skip the Llama-3-8B decode measurement")
-    ap.add_argument("--probe", default=None, help="gemm:M,N,K,G, gemv:M,N,K,G or w8a8:M,N,K -- a few launches of one kernel (profiling)")
+    ap.add_argument("--probe", default=None, help="gemm:M,N,K,G, gemv:M,N,K,G, w8a8:M,N,K, attn:B,S, attn8:B,S or decode:B,layers,prompt -- a few launches of one kernel (profiling)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     rank = int(os.environ.get("RANK", "0"))
