@@ -397,6 +397,14 @@ def run_ours(args, rank, world, local_rank):
                 clocks["tp_gemm"] = c.summary()
             except Exception as e:
                 line["extra"]["tp_gemm"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        if world == 1:
+            try:        # one layer's decode attention at Llama-3-8B shapes: library kernels (16-bit and FP8 cache) and torch's
+                with ClockSampler(local_rank) as c:
+                    line["extra"]["attention"] = [attention_row(device, k, B, 2304, 20, 3) for B in (1, 4, 8) for k in ("sdpa", "attn", "attn8")]
+                clocks["attention"] = c.summary()
+            except Exception as e:
+                line["extra"]["attention"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            torch.cuda.empty_cache()
         if not args.no_llama:
             try:
                 with ClockSampler(local_rank) as c:
@@ -829,6 +837,42 @@ def w8a8_row(device, M, N, K, iters=20, warmup=3):
             "tflops_gemm_only": fl / sec_mm / 1e12, "iterations": iters}
 
 
+def attention_row(device, kind, B, S, steps, warmup):
+    """One decode-attention call of a Llama-3-8B block (32 query / 8 KV heads of 128) over a cache of S
+    positions, the query at position S - 200: kind "attn" = the library kernel over a 16-bit cache,
+    "attn8" = over an FP8 cache, "sdpa" = torch's attention with a mask over the 16-bit cache. Eight
+    distinct caches in turn so that L2 does not hold them."""
+    from tfp8 import _ext
+    H, KV, hd = 32, 8, 128
+    pos = torch.tensor([S - 200], device=device)
+    scratch = torch.empty(_ext.attn_scratch_floats(B, H, S, hd), dtype=torch.float32, device=device)
+    if kind == "attn8":
+        q = torch.randn(B, H, hd, device=device).half()
+        ks = [torch.randint(0, 120, (B, KV, S, hd), device=device, dtype=torch.uint8) for _ in range(8)]
+        vs = [torch.randint(0, 120, (B, KV, S, hd), device=device, dtype=torch.uint8) for _ in range(8)]
+        sc = torch.full((B, KV, S), 2.0 ** -6, device=device)
+        call = lambda i: _ext.attn_decode_fp8(q, ks[i], sc, vs[i], sc, pos, scratch)
+        per_pos = 2 * (hd + 4)
+    else:
+        ks = [torch.randn(B, KV, S, hd, device=device).half() for _ in range(8)]
+        vs = [torch.randn(B, KV, S, hd, device=device).half() for _ in range(8)]
+        per_pos = 4 * hd
+        if kind == "attn":
+            q = torch.randn(B, H, hd, device=device).half()
+            call = lambda i: _ext.attn_decode(q, ks[i], vs[i], pos, scratch)
+        else:
+            q = torch.randn(B, H, 1, hd, device=device).half()
+            mask = torch.where(torch.arange(S, device=device)[None, :] <= pos[:, None], 0.0, float("-inf")).half()
+            call = lambda i: torch.nn.functional.scaled_dot_product_attention(q, ks[i], vs[i], attn_mask=mask, enable_gqa=True)
+
+    def step():
+        for i in range(8):
+            call(i)
+    sec = time_steps_in_graphs(step, steps, warmup) / 8
+    byt = B * KV * (S - 199) * per_pos
+    return {"kind": kind, "batch": B, "cache_positions": S - 199, "us_per_call": sec * 1e6, "kv_bytes": byt, "gbs": byt / sec / 1e9}
+
+
 def run_probe(args):
     """`--probe gemm:M,N,K,G` / `--probe gemv:M,N,K,G`: a few launches of one kernel on one shape
     (a small, self-ending case for profiler captures). Prints one JSON line with the timing."""
@@ -841,33 +885,9 @@ def run_probe(args):
     if kind == "w8a8":
         print(json.dumps({"probe": args.probe, **w8a8_row(device, M, N, K, args.steps, args.warmup)}))
         return
-    if kind in ("attn", "attn8"):
-        # attn:B,S / attn8:B,S -- the decode attention of a Llama-3-8B block (32 query / 8 KV heads of 128)
-        # over a 16-bit / an FP8 KV cache of S positions, the query at position S - 200; eight distinct
-        # caches in turn so that L2 does not hold them
-        B, S = M, N
-        H, KV, hd = 32, 8, 128
-        pos = torch.tensor([S - 200], device=device)
-        q = torch.randn(B, H, hd, device=device).half()
-        scratch = torch.empty(_ext.attn_scratch_floats(B, H, S, hd), dtype=torch.float32, device=device)
-        if kind == "attn8":
-            ks = [torch.randint(0, 120, (B, KV, S, hd), device=device, dtype=torch.uint8) for _ in range(8)]
-            vs = [torch.randint(0, 120, (B, KV, S, hd), device=device, dtype=torch.uint8) for _ in range(8)]
-            sc = torch.full((B, KV, S), 2.0 ** -6, device=device)
-            call = lambda i: _ext.attn_decode_fp8(q, ks[i], sc, vs[i], sc, pos, scratch)
-            per_pos = 2 * (hd + 4)
-        else:
-            ks = [torch.randn(B, KV, S, hd, device=device).half() for _ in range(8)]
-            vs = [torch.randn(B, KV, S, hd, device=device).half() for _ in range(8)]
-            call = lambda i: _ext.attn_decode(q, ks[i], vs[i], pos, scratch)
-            per_pos = 4 * hd
-
-        def step():
-            for i in range(8):
-                call(i)
-        sec = time_steps_in_graphs(step, args.steps, args.warmup) / 8
-        byt = B * KV * (S - 199) * per_pos
-        print(json.dumps({"probe": args.probe, "us_per_call": sec * 1e6, "kv_bytes": byt, "gbs": byt / sec / 1e9}))
+    if kind in ("attn", "attn8", "sdpa"):
+        # attn:B,S / attn8:B,S / sdpa:B,S -- one decode-attention call, see attention_row
+        print(json.dumps({"probe": args.probe, **attention_row(device, kind, M, N, args.steps, args.warmup)}))
         return
     if kind == "decode":
         # decode:B,layers,prompt -- a Llama-3-8B-shaped decoder cut to `layers` blocks: prefill, capture,
