@@ -1068,6 +1068,18 @@ int glue_status(unsigned int* out, cudaStream_t st) {
 // kernel if a peer is gone.
 static long long g_ar_wait_cycles = 1ll << 35;
 
+// SM count of the current device, asked once per device (148 if the query fails).
+static int current_device_sms() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    if (dev >= 0 && dev < 64) cached[dev] = sms;
+    return sms;
+}
+
 // The attention kernels release their dependents when their results are stored, not at once like
 // the other helpers: what follows them is the output projection's GEMV, whose weight prefetch
 // then competes with the KV cache for HBM -- measured inside a batch-1 decode step of 8 blocks,
@@ -1184,9 +1196,7 @@ extern "C" int tfp8b_attn_decode(const void* q, const void* k_cache, const void*
     static const int use_tc = [] { const char* v = getenv("TFP8B_ATT16_TC"); return !(v && v[0] == '0'); }();
     if (use_tc && dtype == TFP8B_F16 && (reinterpret_cast<uintptr_t>(v_cache) & 15u) == 0) {
         const int ngrp_tc = (H / KV + ATT_G - 1) / ATT_G;
-        int dev = 0, sms = 148;
-        if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        const int sms = current_device_sms();
         const int nw = static_cast<long long>(B) * KV * ngrp_tc * ((max_seq + 127) / 128) >= 2ll * sms ? 8 : 4;
         const int chunk = ATT8_PW * nw, ns = (max_seq + chunk - 1) / chunk;
         TFP8B_REQUIRE(ns <= 128, TFP8B_ERR_UNSUPPORTED, "tfp8b_attn_decode: max_seq %d (at most %d is built)", max_seq, 128 * chunk);
@@ -1269,10 +1279,7 @@ extern "C" int tfp8b_attn_decode_fp8(const void* q, const uint8_t* k_codes, cons
     // beyond: half the partial records and half the merge work (prompt 2100: 10.0 -> 9.5 us per call
     // at batch 4, 17.2 -> 16.4 at batch 8). TFP8B_ATT8_WARPS=4|8 forces one.
     static const int nw_env = [] { const char* v = getenv("TFP8B_ATT8_WARPS"); return v ? atoi(v) : 0; }();
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
-    int sms = 148;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    const int sms = current_device_sms();
     const long long ctas128 = static_cast<long long>(B) * KV * ngrp * ((max_seq + 127) / 128);
     const int nw = (nw_env == 4 || nw_env == 8) ? nw_env : (ctas128 >= 2ll * sms ? 8 : 4);
     const int chunk = ATT8_PW * nw;
